@@ -1,0 +1,83 @@
+"""Builds the pieces of a running engine from a model folder: model, weights, cache, step function.
+
+The recipe of miniserve/api/bootstrap.py:40-183 without the service around it: read the
+configuration, pick the model through the registry, load the weights strictly, size and
+allocate the page pools once, wire the cache manager and the step function.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+from pathlib import Path
+from typing import Optional, Union
+
+import torch
+
+from .. import kernels
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..config.engine_config import EngineConfig
+from ..config.registry import load_model_config
+from ..parts.model import DecoderModel
+from ..weights.loader import load_tensors
+from .step import StepFunction
+
+_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclass
+class Runtime:
+    config: object
+    engine_config: EngineConfig
+    model: DecoderModel
+    storage: CacheStorage
+    manager: CacheManager
+    step_function: StepFunction
+    max_model_len: int
+    load_report: object
+
+
+def require_device(device: str) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("no CUDA device: this engine runs on an NVIDIA B200 only and has no CPU path")
+    dev = torch.device(device)
+    major, minor = torch.cuda.get_device_capability(dev)
+    if major != 10:
+        raise RuntimeError(f"device {dev} has compute capability {major}.{minor}; the kernels are built for sm_100a")
+    return dev
+
+
+def build_runtime(model_dir: Union[str, Path], engine_config: Optional[EngineConfig] = None) -> Runtime:
+    engine_config = engine_config or EngineConfig()
+    engine_config.validate()
+    device = require_device(engine_config.device)
+    torch.cuda.set_device(device)
+    kernels.library()          # build or load the CUDA library now; fail here if that is impossible
+    dtype = _DTYPES[engine_config.dtype]
+
+    architecture, config = load_model_config(model_dir)
+    spec = architecture.build_spec(config)
+    model = DecoderModel(spec, dtype, device)
+    tied = [(name, spec.embedding_name) for name in spec.optional_names] if spec.output_name is None else []
+    tensors, report = load_tensors(model_dir, model.param_specs(), dtype, device, spec.optional_names, tied)
+    model.load(tensors)
+    del tensors
+
+    max_model_len = engine_config.max_model_len or spec.max_positions
+    if max_model_len > spec.max_positions:
+        raise ValueError(f"max_model_len {max_model_len} exceeds the model's position limit {spec.max_positions}")
+    page_size = engine_config.kv_block_size
+    num_pages = engine_config.num_kv_blocks
+    if num_pages is None:
+        per_page = max(CacheStorage.bytes_per_page(model.cache_groups, page_size, dtype), 1)
+        free, _total = torch.cuda.mem_get_info(device)
+        by_memory = int(free * engine_config.gpu_memory_utilization) // per_page
+        by_need = engine_config.max_num_seqs * ((max_model_len + page_size - 1) // page_size)
+        num_pages = max(1, min(by_memory, by_need))
+    storage = CacheStorage(model.cache_groups, page_size, num_pages, engine_config.max_num_seqs, dtype, device)
+    namespace = f"{Path(model_dir).resolve()};{engine_config.dtype};page={page_size}"
+    manager = CacheManager(model.cache_groups, page_size, num_pages, engine_config.max_num_seqs,
+                           engine_config.enable_prefix_cache, engine_config.prefix_cache_max_entries, namespace)
+    step_function = StepFunction(model, storage, manager, max_model_len)
+    resolved = replace(engine_config, max_model_len=max_model_len, num_kv_blocks=num_pages)
+    return Runtime(config, resolved, model, storage, manager, step_function, max_model_len, report)

@@ -1,0 +1,259 @@
+"""ctypes bindings of the CUDA library: one Python function per kernel entry point.
+
+Every function takes CUDA tensors, checks types, shapes and contiguity on the host,
+launches on torch's current stream and returns nothing (outputs are arguments).  There
+is no CPU path: a call with a CPU tensor, or on a machine where the library cannot be
+built or loaded, raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+ABI_VERSION = 1
+_library: Optional[ctypes.CDLL] = None
+
+_DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    """A kernel entry point refused its arguments or failed to launch."""
+
+
+def library() -> ctypes.CDLL:
+    """The loaded CUDA library (built on first use)."""
+    global _library
+    if _library is None:
+        path = build.library_path()
+        lib = ctypes.CDLL(str(path))
+        lib.ms_last_error.restype = ctypes.c_char_p
+        lib.ms_abi_version.restype = ctypes.c_int
+        if lib.ms_abi_version() != ABI_VERSION:
+            raise KernelError(f"{path} reports ABI {lib.ms_abi_version()}, bindings expect {ABI_VERSION}; rebuild it")
+        _library = lib
+    return _library
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise KernelError(library().ms_last_error().decode())
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise KernelError(f"element type {dtype} is not supported (float32 and bfloat16 are)") from None
+
+
+def _want(tensor: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {tensor.dtype}")
+    if shape is not None and tuple(tensor.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(tensor.shape)}")
+
+
+def _i(value: int) -> ctypes.c_int:
+    return ctypes.c_int(int(value))
+
+
+def _f(value: float) -> ctypes.c_float:
+    return ctypes.c_float(float(value))
+
+
+# --------------------------------------------------------------------------- memory-bound kernels
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n] = float32(table[tokens[n]])``; tokens int32 ``[N]``, out float32 ``[N, H]``."""
+    n, hidden = tokens.numel(), table.shape[1]
+    _want(tokens, "tokens", torch.int32)
+    _want(table, "table")
+    _want(out, "out", torch.float32, (n, hidden))
+    _check(library().ms_embedding(_ptr(tokens), _ptr(table), _i(_code(table.dtype)), _ptr(out), _i(n), _i(hidden),
+                                  _stream()))
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """Adds ``delta`` into the float32 ``residual`` (in place) and writes its RMSNorm to ``out``.
+
+    With ``rows`` (int32 ``[K]``) only those rows are normalised, into ``out [K, H]``, and
+    the residual is left untouched.  ``weight`` may be float32 or bfloat16 whatever ``out`` is.
+    """
+    hidden = residual.shape[1]
+    n_out = residual.shape[0] if rows is None else rows.numel()
+    _want(residual, "residual", torch.float32)
+    _want(out, "out", None, (n_out, hidden))
+    _want(weight, "weight", None, (hidden,))
+    if delta is not None:
+        _want(delta, "delta", out.dtype, residual.shape)
+    if rows is not None:
+        _want(rows, "rows", torch.int32)
+    _check(library().ms_add_rmsnorm(_ptr(residual), _ptr(delta), _i(_code(out.dtype)), _ptr(weight),
+                                    _i(_code(weight.dtype)), _ptr(rows), _ptr(out), _i(n_out), _i(hidden), _f(eps),
+                                    _stream()))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """RMSNorm over the last dim of ``x [rows, size]`` into ``out`` of the same type and shape."""
+    _want(x, "x")
+    _want(out, "out", x.dtype, x.shape)
+    size = x.shape[-1]
+    _want(weight, "weight", None, (size,))
+    _check(library().ms_rmsnorm(_ptr(x), _i(_code(x.dtype)), _ptr(weight), _i(_code(weight.dtype)), _ptr(out),
+                                _i(x.numel() // size), _i(size), _f(eps), _stream()))
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, cos_sin: torch.Tensor) -> None:
+    """``cos_sin[n, j] = (cos, sin)(positions[n] * inv_freq[j])`` in float32; cos_sin ``[N, half, 2]``."""
+    n, half = positions.numel(), inv_freq.numel()
+    _want(positions, "positions", torch.int32)
+    _want(inv_freq, "inv_freq", torch.float32)
+    _want(cos_sin, "cos_sin", torch.float32, (n, half, 2))
+    _check(library().ms_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(cos_sin), _i(n), _i(half), _stream()))
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, slots: torch.Tensor, q_weight: Optional[torch.Tensor],
+                        k_weight: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                        rotary_dim: int, interleaved: bool, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                        n_q: int, n_kv: int, head_dim: int, q_out: torch.Tensor) -> None:
+    """Per-head RMSNorm of q and k, rotation, and the append of k and v to one layer's pools.
+
+    qkv ``[N, (n_q + 2 n_kv) * d]``; slots int32 ``[N]`` (page * page_size + offset, negative:
+    no write); pools ``[pages, n_kv, page_size, d]``; q_out ``[N, n_q, d]``; cos_sin float32
+    ``[N, rotary_dim / 2, 2]`` or None for no rotation; norm weights ``[d]`` or None.
+    """
+    n = qkv.shape[0]
+    _want(qkv, "qkv", None, (n, (n_q + 2 * n_kv) * head_dim))
+    _want(slots, "slots", torch.int32, (n,))
+    _want(k_pool, "k_pool", qkv.dtype)
+    _want(v_pool, "v_pool", qkv.dtype, k_pool.shape)
+    if k_pool.dim() != 4 or k_pool.shape[1] != n_kv or k_pool.shape[3] != head_dim:
+        raise KernelError(f"pool shape {tuple(k_pool.shape)} is not [pages, {n_kv}, page_size, {head_dim}]")
+    _want(q_out, "q_out", qkv.dtype, (n, n_q, head_dim))
+    weight_code = 0
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _want(weight, name, None, (head_dim,))
+            weight_code = _code(weight.dtype)
+    if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+        raise KernelError("q and k norm weights must share one element type")
+    if cos_sin is not None:
+        _want(cos_sin, "cos_sin", torch.float32, (n, rotary_dim // 2, 2))
+    else:
+        rotary_dim = 0
+    _check(library().ms_qk_norm_rope_append(
+        _ptr(qkv), _i(_code(qkv.dtype)), _ptr(slots), _ptr(q_weight), _ptr(k_weight), _i(weight_code), _f(eps),
+        _ptr(cos_sin), _i(rotary_dim), _i(1 if interleaved else 0), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[2]),
+        _i(n_q), _i(n_kv), _i(head_dim), _ptr(q_out), _i(n), _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[n, c] = silu(gate_up[n, c]) * gate_up[n, I + c]`` for gate_up ``[N, 2 I]``."""
+    n, inter = out.shape
+    _want(gate_up, "gate_up", None, (n, 2 * inter))
+    _want(out, "out", gate_up.dtype)
+    _check(library().ms_silu_mul(_ptr(gate_up), _i(_code(gate_up.dtype)), _ptr(out), _i(n), _i(inter), _stream()))
+
+
+# --------------------------------------------------------------------------- attention
+
+
+def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
+                    request_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
+                    out: torch.Tensor) -> None:
+    """Causal grouped-query attention of every token over its request's paged keys and values.
+
+    q, out ``[N, n_q, d]``; pools of one layer ``[pages, n_kv, page_size, d]``; block_tables
+    int32 ``[R, width]``; request_of_token, positions int32 ``[N]``.  A token at position p sees
+    keys ``max(0, p - window + 1) .. p`` of its own request, which must be in the pool already.
+    """
+    n, n_q, head_dim = q.shape
+    _want(q, "q")
+    _want(out, "out", q.dtype, q.shape)
+    _want(k_pool, "k_pool", q.dtype)
+    _want(v_pool, "v_pool", q.dtype, k_pool.shape)
+    if k_pool.dim() != 4 or k_pool.shape[3] != head_dim:
+        raise KernelError(f"pool shape {tuple(k_pool.shape)} is not [pages, n_kv, page_size, {head_dim}]")
+    _want(block_tables, "block_tables", torch.int32)
+    _want(request_of_token, "request_of_token", torch.int32, (n,))
+    _want(positions, "positions", torch.int32, (n,))
+    _check(library().ms_paged_attention_generic(
+        _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
+        _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(k_pool.shape[1]), _i(head_dim),
+        _f(scale), _i(window if window else 0), _ptr(out), _i(n), _stream()))
+
+
+# --------------------------------------------------------------------------- matrix products
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M, N] = x[M, K] @ weight[N, K]^T``.
+
+    float32 operands run through the library's own FFMA kernel (true 32-bit, no tensor-core
+    mode).  bfloat16 operands go to cuBLAS through ``torch.mm`` with float32 accumulation;
+    ``out`` may then be bfloat16 or float32.
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or tuple(out.shape) != (m, n):
+        raise KernelError(f"linear: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if x.dtype == torch.float32:
+        _want(x, "x", torch.float32)
+        _want(weight, "weight", torch.float32)
+        _want(out, "out", torch.float32)
+        _check(library().ms_gemm_f32(_ptr(x), _ptr(weight), _ptr(out), _i(m), _i(n), _i(k), _i(k), _i(k), _i(n),
+                                     _stream()))
+        return
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16)
+    if not x.is_cuda:
+        raise KernelError("linear: CUDA tensors only")
+    if out.dtype == torch.bfloat16:
+        torch.mm(x, weight.t(), out=out)
+    else:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+
+
+# --------------------------------------------------------------------------- sampling
+
+SAMPLING_RECORD_WORDS = 8
+
+
+def sample(logits: torch.Tensor, records: Optional[torch.Tensor], slot_of_row: Optional[torch.Tensor],
+           draw_index: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """Chooses one token per row of float32 ``logits [K, V]`` into int32 ``out [K]``.
+
+    ``records`` int32 ``[slots, 8]`` holds per state slot the bit patterns of (temperature,
+    top_p) and the integers (top_k, seed low word, seed high word); ``slot_of_row`` and
+    ``draw_index`` are int32 ``[K]``.  ``records=None`` means argmax for every row.
+    """
+    k, vocab = logits.shape
+    _want(logits, "logits", torch.float32)
+    _want(out, "out", torch.int32, (k,))
+    if records is not None:
+        _want(records, "records", torch.int32)
+        if records.dim() != 2 or records.shape[1] != SAMPLING_RECORD_WORDS:
+            raise KernelError(f"records must be [slots, {SAMPLING_RECORD_WORDS}] int32")
+        _want(slot_of_row, "slot_of_row", torch.int32, (k,))
+        _want(draw_index, "draw_index", torch.int32, (k,))
+    _check(library().ms_sample(_ptr(logits), _i(logits.stride(0)), _i(vocab), _ptr(records), _ptr(slot_of_row),
+                               _ptr(draw_index), _ptr(out), _i(k), _stream()))

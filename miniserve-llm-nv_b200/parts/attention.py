@@ -1,0 +1,110 @@
+"""The attention mixer: grouped-query attention over a paged cache.
+
+Computes what miniserve/model/qwen3.py:144-250 computes for one layer: q/k/v projections
+without bias, optional RMSNorm of every q and k head over the head size before the rotation
+(qwen3.py:177-178), the position encoding, the append of k and v to the cache, causal
+attention by absolute position with softmax in float32 scaled by ``head_dim ** -0.5``
+(qwen3.py:66, 243-248), and the output projection.  Differences in form: the three
+projections run as one matrix product over a row-concatenated weight, and norm, rotation and
+append are one kernel.
+
+All sizes are arguments.  ``window`` limits a query to the last ``window`` keys; ``scale``
+overrides the score scale; ``position`` is a :class:`~.spec.PartSpec` of the position family.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from .base import POSITIONS, PagedKVNeed, ParamSpec, Part, register_mixer
+from .context import PagedKVView, StepContext
+from .spec import PartSpec
+
+
+@register_mixer("attention")
+class Attention(Part):
+    def __init__(self, *, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 qk_norm: bool, eps: float, position: PartSpec, window: Optional[int] = None,
+                 scale: Optional[float] = None, q_name: str = "q_proj.weight", k_name: str = "k_proj.weight",
+                 v_name: str = "v_proj.weight", o_name: str = "o_proj.weight", q_norm_name: str = "q_norm.weight",
+                 k_norm_name: str = "k_norm.weight") -> None:
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise ValueError(f"head size {head_dim} is not a multiple of 16 in 16..256")
+        self.prefix = prefix
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
+        self.qk_norm, self.eps = bool(qk_norm), float(eps)
+        self.window = window
+        self.scale = float(scale) if scale is not None else head_dim ** -0.5
+        self.position = POSITIONS.build(position, head_dim=head_dim) if "head_dim" not in position.args \
+            else POSITIONS.build(position)
+        self.names = dict(q=prefix + q_name, k=prefix + k_name, v=prefix + v_name, o=prefix + o_name,
+                          q_norm=prefix + q_norm_name, k_norm=prefix + k_norm_name)
+        self.qkv_weight: Optional[torch.Tensor] = None
+        self.o_weight: Optional[torch.Tensor] = None
+        self.q_norm_weight: Optional[torch.Tensor] = None
+        self.k_norm_weight: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ declaration
+    def param_specs(self) -> list[ParamSpec]:
+        h, d = self.hidden_size, self.head_dim
+        specs = [ParamSpec(self.names["q"], (self.num_heads * d, h)),
+                 ParamSpec(self.names["k"], (self.num_kv_heads * d, h)),
+                 ParamSpec(self.names["v"], (self.num_kv_heads * d, h)),
+                 ParamSpec(self.names["o"], (h, self.num_heads * d))]
+        if self.qk_norm:
+            specs += [ParamSpec(self.names["q_norm"], (d,), "vector"), ParamSpec(self.names["k_norm"], (d,), "vector")]
+        return specs
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(self.num_kv_heads, self.head_dim, self.window)
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        n = self.names
+        self.qkv_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0).contiguous()
+        self.o_weight = tensors[n["o"]]
+        if self.qk_norm:
+            self.q_norm_weight, self.k_norm_weight = tensors[n["q_norm"]], tensors[n["k_norm"]]
+            if self.q_norm_weight.dtype != self.k_norm_weight.dtype:
+                self.q_norm_weight = self.q_norm_weight.float()
+                self.k_norm_weight = self.k_norm_weight.float()
+
+    # ------------------------------------------------------------------ work
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
+        n, d = x.shape[0], self.head_dim
+        n_q, n_kv = self.num_heads, self.num_kv_heads
+        qkv = torch.empty((n, (n_q + 2 * n_kv) * d), dtype=x.dtype, device=x.device)
+        kernels.linear(x, self.qkv_weight, qkv)
+        q = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
+        slots = cache.slots if cache.writable else torch.full_like(cache.slots, -1)
+        fused = self.position.fused_args(ctx)
+        if fused is not None:
+            cos_sin, rotary_dim, interleaved = fused
+            kernels.qk_norm_rope_append(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, cos_sin,
+                                        rotary_dim, interleaved, cache.key_pool, cache.value_pool, n_q, n_kv, d, q)
+        else:
+            self._append_with_external_position(qkv, slots, ctx, cache, q)
+        attended = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
+        kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
+                                ctx.positions, self.scale, self.window, attended)
+        out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
+        return out
+
+    def _append_with_external_position(self, qkv, slots, ctx, cache, q_out) -> None:
+        """Position parts without a fused form: norm, ``position.apply``, then a plain append."""
+        n, d, n_q, n_kv = qkv.shape[0], self.head_dim, self.num_heads, self.num_kv_heads
+        heads = qkv.view(n, n_q + 2 * n_kv, d)
+        q = heads[:, :n_q].contiguous()
+        k = heads[:, n_q:n_q + n_kv].contiguous()
+        if self.qk_norm:
+            kernels.rmsnorm(q, self.q_norm_weight, self.eps, q)
+            kernels.rmsnorm(k, self.k_norm_weight, self.eps, k)
+        q, k = self.position.apply(q, k, ctx)
+        packed = torch.cat([q, k, heads[:, n_q + n_kv:]], dim=1).contiguous().view(n, -1)
+        kernels.qk_norm_rope_append(packed, slots, None, None, self.eps, None, 0, False, cache.key_pool,
+                                    cache.value_pool, n_q, n_kv, d, q_out)

@@ -1,0 +1,45 @@
+"""Feed-forward parts.  ``gated_mlp``: ``down(act(gate(x)) * up(x))`` without biases
+(miniserve/model/layers.py:71-87) with ``silu`` as the activation; gate and up run as one
+matrix product over a row-concatenated weight."""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import kernels
+from .base import ParamSpec, Part, register_feed_forward
+from .context import StepContext
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(Part):
+    def __init__(self, *, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 gate_name: str = "gate_proj.weight", up_name: str = "up_proj.weight",
+                 down_name: str = "down_proj.weight") -> None:
+        if activation != "silu":
+            raise ValueError(f"gated_mlp implements the 'silu' activation, not {activation!r}")
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.names = dict(gate=prefix + gate_name, up=prefix + up_name, down=prefix + down_name)
+        self.gate_up_weight: Optional[torch.Tensor] = None
+        self.down_weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> list[ParamSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return [ParamSpec(self.names["gate"], (i, h)), ParamSpec(self.names["up"], (i, h)),
+                ParamSpec(self.names["down"], (h, i))]
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        self.gate_up_weight = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]], dim=0).contiguous()
+        self.down_weight = tensors[self.names["down"]]
+
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n = x.shape[0]
+        gate_up = torch.empty((n, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.linear(x, self.gate_up_weight, gate_up)
+        hidden = torch.empty((n, self.intermediate_size), dtype=x.dtype, device=x.device)
+        kernels.silu_mul(gate_up, hidden)
+        out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.linear(hidden, self.down_weight, out)
+        return out

@@ -1,0 +1,140 @@
+"""Plain PyTorch statements of what each kernel entry point computes.
+
+Two uses: the GPU tests compare every kernel alone with the function of the same name here
+(computed in float64 from the same inputs), and the CPU tests put these functions in the
+kernels' place (``install``) so that the host-side logic of the engine (batching, cache
+manager, step function) can be exercised on a machine without a GPU.  Nothing here is used by
+the package itself.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+import plain_qwen3 as plain
+
+
+def embedding(tokens, table, out):
+    out.copy_(table[tokens.long()].to(out.dtype))
+
+
+def add_rmsnorm(residual, delta, weight, eps, out, rows=None):
+    if rows is None:
+        if delta is not None:
+            residual += delta.to(residual.dtype)
+        x = residual
+    else:
+        x = residual[rows.long()]
+        if delta is not None:
+            x = x + delta[rows.long()].to(residual.dtype)
+    x = x.double()
+    y = weight.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))
+    out.copy_(y.to(out.dtype))
+
+
+def rmsnorm(x, weight, eps, out):
+    xd = x.double()
+    y = weight.double() * (xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps))
+    out.copy_(y.to(out.dtype))
+
+
+def rope_table(positions, inv_freq, cos_sin):
+    angles = (positions.to(torch.float32)[:, None] * inv_freq[None, :]).double()
+    cos_sin[..., 0] = angles.cos().to(cos_sin.dtype)
+    cos_sin[..., 1] = angles.sin().to(cos_sin.dtype)
+
+
+def rotate(x, cos_sin, rotary_dim, interleaved):
+    """x [N, heads, d] float64; cos_sin [N, rotary_dim/2, 2]."""
+    cos, sin = cos_sin[..., 0].double()[:, None, :], cos_sin[..., 1].double()[:, None, :]
+    out = x.clone()
+    half = rotary_dim // 2
+    if interleaved:
+        a, b = x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2]
+        out[..., 0:rotary_dim:2] = a * cos - b * sin
+        out[..., 1:rotary_dim:2] = b * cos + a * sin
+    else:
+        a, b = x[..., :half], x[..., half:rotary_dim]
+        out[..., :half] = a * cos - b * sin
+        out[..., half:rotary_dim] = b * cos + a * sin
+    return out
+
+
+def qk_norm_rope_append(qkv, slots, q_weight, k_weight, eps, cos_sin, rotary_dim, interleaved, k_pool, v_pool,
+                        n_q, n_kv, head_dim, q_out):
+    n = qkv.shape[0]
+    heads = qkv.view(n, n_q + 2 * n_kv, head_dim).double()
+    q, k, v = heads[:, :n_q], heads[:, n_q:n_q + n_kv], heads[:, n_q + n_kv:]
+
+    def norm(x, w):
+        if w is None:
+            return x
+        return w.double() * (x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps))
+
+    q, k = norm(q, q_weight), norm(k, k_weight)
+    if cos_sin is not None:
+        q, k = rotate(q, cos_sin, rotary_dim, interleaved), rotate(k, cos_sin, rotary_dim, interleaved)
+    q_out.copy_(q.to(q_out.dtype))
+    page_size = k_pool.shape[2]
+    for token in range(n):
+        slot = int(slots[token])
+        if slot < 0:
+            continue
+        page, offset = divmod(slot, page_size)
+        k_pool[page, :, offset, :] = k[token].to(k_pool.dtype)
+        v_pool[page, :, offset, :] = v[token].to(v_pool.dtype)
+
+
+def silu_mul(gate_up, out):
+    inter = out.shape[1]
+    g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+    out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
+
+
+def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, scale, window, out):
+    n, n_q, d = q.shape
+    n_kv, page_size = k_pool.shape[1], k_pool.shape[2]
+    group = n_q // n_kv
+    for token in range(n):
+        pos = int(positions[token])
+        table = block_tables[int(request_of_token[token])]
+        first = max(0, pos - window + 1) if window else 0
+        keys = torch.arange(first, pos + 1)
+        pages = table[(keys // page_size).long()].long()
+        offsets = (keys % page_size).long()
+        k = k_pool[pages, :, offsets, :].double()      # [keys, n_kv, d]
+        v = v_pool[pages, :, offsets, :].double()
+        for head in range(n_q):
+            scores = (k[:, head // group, :] @ q[token, head].double()) * scale
+            p = torch.softmax(scores, dim=0)
+            out[token, head] = (p @ v[:, head // group, :]).to(out.dtype)
+
+
+def linear(x, weight, out):
+    out.copy_((x.double() @ weight.double().T).to(out.dtype))
+
+
+def sample(logits, records, slot_of_row, draw_index, out):
+    import struct
+
+    for row in range(logits.shape[0]):
+        if records is None:
+            out[row] = int(torch.argmax(logits[row]))
+            continue
+        words = records[int(slot_of_row[row])].tolist()
+        temperature, top_p, top_k, seed_lo, seed_hi, *_ = struct.unpack("<ffiIIiii", struct.pack("<8i", *words))
+        out[row] = plain.plain_sample(logits[row].cpu(), temperature, top_k, top_p, seed_lo | (seed_hi << 32),
+                                      int(draw_index[row]))
+
+
+def install(monkeypatch) -> None:
+    """Puts the functions above in place of the kernel bindings (CPU tests of host logic only)."""
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200 import kernels
+
+    for name in ("embedding", "add_rmsnorm", "rmsnorm", "rope_table", "qk_norm_rope_append", "silu_mul",
+                 "paged_attention", "linear", "sample"):
+        monkeypatch.setattr(kernels, name, globals()[name])

@@ -212,11 +212,11 @@ def plain_philox4x32(counter: tuple[int, int, int, int], key: tuple[int, int]) -
 def plain_gumbel(seed: int, step: int, index: int) -> float:
     """Standard Gumbel noise of vocabulary entry ``index`` at a request's ``step``-th draw.
 
-    The uniform comes from word ``index % 4`` of Philox(counter=(index // 4, step, 0, 0),
-    key=seed) as ``(word + 0.5) / 2^32``.
+    The uniform comes from the upper 24 bits of word ``index % 4`` of
+    Philox(counter=(index // 4, step, 0, 0), key=seed) as ``(bits + 0.5) / 2^24``.
     """
     words = plain_philox4x32((index // 4, step & 0xFFFFFFFF, 0, 0), (seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF))
-    u = (words[index % 4] + 0.5) / 4294967296.0
+    u = ((words[index % 4] >> 8) + 0.5) / 16777216.0
     return -math.log(-math.log(u))
 
 

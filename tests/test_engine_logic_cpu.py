@@ -1,0 +1,69 @@
+"""Host-side logic of the step function and the cache manager, run on the CPU with plain
+PyTorch functions standing in for the kernels: every cutting of a set of requests must give
+the logits of the plain implementation."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import helpers
+import plain_ops
+
+
+@pytest.fixture
+def cpu_runtime(monkeypatch, tmp_path):
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200.config import EngineConfig
+    from miniserve_b200.engine import runtime as runtime_module
+
+    plain_ops.install(monkeypatch)
+    monkeypatch.setattr(runtime_module, "require_device", lambda device: torch.device("cpu"))
+    monkeypatch.setattr(runtime_module.kernels, "library", lambda: None)
+    monkeypatch.setattr(torch.cuda, "set_device", lambda device: None)
+
+    def build(name, num_pages, page_size=16, dtype="float32"):
+        folder = helpers.make_folder(tmp_path, name, seed=1)
+        runtime = runtime_module.build_runtime(folder, EngineConfig(
+            dtype=dtype, kv_block_size=page_size, num_kv_blocks=num_pages, max_num_seqs=4,
+            enable_prefix_cache=False, device="cpu"))
+        return folder, runtime
+    return build
+
+
+def replay(runtime, steps):
+    from miniserve_b200.engine.step import StepEntry
+
+    outputs = {}
+    manager = runtime.manager
+    for record in steps:
+        entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in record["entries"]]
+        for entry in entries:
+            if entry.request_id not in manager.requests:
+                manager.admit(entry.request_id)
+        reservation = manager.prepare([(e.request_id, len(e.tokens)) for e in entries])
+        outputs[record["step"]] = runtime.step_function.run(entries, reservation).double()
+        manager.commit(reservation)
+        for rid in record["end"]:
+            manager.release(rid)
+        manager.check_invariants()
+    return outputs
+
+
+@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4)])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_cuttings_match_plain_on_cpu(cpu_runtime, name, page_size, cutting):
+    vocab = helpers.TINY[name]["vocab_size"]
+    requests = {f"r{i}": helpers.random_tokens(vocab, n, seed=10 + i) for i, n in enumerate((1, 7, 16, 33, 50))}
+    steps = {"whole": helpers.cut_whole, "tail": lambda r: helpers.cut_decode_tail(r, 12),
+             "portions": helpers.cut_portions, "mixed": helpers.cut_mixed}[cutting](requests)
+    pages = (helpers.max_live_tokens(steps, granule=page_size * 2) + page_size - 1) // page_size
+    folder, runtime = cpu_runtime(name, pages, page_size)
+    got = helpers.collect(steps, replay(runtime, steps))
+    for rid, tokens in requests.items():
+        expected = helpers.oracle_logits(folder, tokens)
+        assert sorted(got[rid]) == list(range(len(tokens)))
+        for position, row in got[rid].items():
+            assert torch.allclose(row, expected[position], atol=1e-4, rtol=1e-4), (rid, position)
+    assert not runtime.manager.requests
+    assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)

@@ -1,0 +1,286 @@
+"""Each kernel alone against its plain statement (tests/plain_ops.py, computed in float64),
+at sizes other than the engine's: widths and vocabularies that are no power of two, head sizes
+in steps of 16, odd head counts and groups, page sizes from 1 up."""
+
+from __future__ import annotations
+
+import struct
+
+import pytest
+import torch
+
+import plain_ops
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+@pytest.fixture(scope="module")
+def kernels():
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200 import kernels as k
+    k.library()
+    return k
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [1, 48, 72, 1000, 2048, 5120])
+def test_embedding(kernels, dtype, hidden):
+    table = rand((331, hidden), dtype, 1)
+    tokens = torch.tensor([0, 330, 17, 17, 5], dtype=torch.int32).cuda()
+    out = torch.empty((5, hidden), dtype=torch.float32).cuda()
+    kernels.embedding(tokens, table, out)
+    assert torch.equal(out, table[tokens.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("weight_dtype", DTYPES)
+@pytest.mark.parametrize("hidden,eps", [(1, 1e-6), (31, 1e-5), (72, 1e-6), (257, 1e-3), (1031, 1e-6), (4096, 1e-6)])
+def test_add_rmsnorm(kernels, dtype, weight_dtype, hidden, eps):
+    if dtype == torch.float32 and weight_dtype == torch.bfloat16:
+        pytest.skip("a float32 model keeps float32 weights")
+    n = 7
+    residual = rand((n, hidden), torch.float32, 2, 3.0)
+    delta = rand((n, hidden), dtype, 3)
+    weight = (1 + rand((hidden,), torch.float32, 4, 0.1)).to(weight_dtype)
+    expected_res = residual.double() + delta.double()
+    expected = torch.empty((n, hidden), dtype=torch.float64).cuda()
+    plain_ops.add_rmsnorm(residual.clone().double(), delta, weight, eps, expected)
+    out = torch.empty((n, hidden), dtype=dtype).cuda()
+    kernels.add_rmsnorm(residual, delta, weight, eps, out)
+    assert torch.allclose(residual.double(), expected_res, atol=1e-6, rtol=1e-6)
+    assert torch.allclose(out.double(), expected, **tol(dtype))
+    # gathered rows, residual untouched; and no delta
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32).cuda()
+    before = residual.clone()
+    out_rows = torch.empty((3, hidden), dtype=dtype).cuda()
+    kernels.add_rmsnorm(residual, delta, weight, eps, out_rows, rows)
+    assert torch.equal(residual, before)
+    expected_rows = torch.empty((3, hidden), dtype=torch.float64).cuda()
+    plain_ops.add_rmsnorm(residual.double(), delta, weight, eps, expected_rows, rows)
+    assert torch.allclose(out_rows.double(), expected_rows, **tol(dtype))
+    out_plain = torch.empty((n, hidden), dtype=dtype).cuda()
+    kernels.add_rmsnorm(residual, None, weight, eps, out_plain)
+    assert torch.equal(residual, before)
+    expected_plain = torch.empty((n, hidden), dtype=torch.float64).cuda()
+    plain_ops.add_rmsnorm(residual.double(), None, weight, eps, expected_plain)
+    assert torch.allclose(out_plain.double(), expected_plain, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("size", [16, 48, 128, 200])
+def test_rmsnorm_rows(kernels, dtype, size):
+    x = rand((5, 3, size), dtype, 5, 2.0)
+    weight = (1 + rand((size,), torch.float32, 6, 0.1)).to(dtype)
+    out = torch.empty_like(x)
+    kernels.rmsnorm(x, weight, 1e-5, out)
+    expected = torch.empty(x.shape, dtype=torch.float64).cuda()
+    plain_ops.rmsnorm(x, weight, 1e-5, expected)
+    assert torch.allclose(out.double(), expected, **tol(dtype))
+
+
+@pytest.mark.parametrize("half,theta", [(8, 1e4), (24, 5e4), (64, 1e6)])
+def test_rope_table(kernels, half, theta):
+    positions = torch.tensor([0, 1, 2, 77, 4095, 40959], dtype=torch.int32).cuda()
+    inv_freq = (1.0 / (theta ** (torch.arange(0, 2 * half, 2, dtype=torch.float32) / (2 * half)))).cuda()
+    table = torch.empty((6, half, 2), dtype=torch.float32).cuda()
+    kernels.rope_table(positions, inv_freq, table)
+    expected = torch.empty((6, half, 2), dtype=torch.float64).cuda()
+    plain_ops.rope_table(positions, inv_freq, expected)
+    assert torch.allclose(table.double(), expected, atol=3e-7, rtol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,rotary,interleaved,with_norm", [
+    (4, 2, 16, 16, 16, False, True), (6, 2, 32, 8, 32, False, True), (3, 1, 48, 4, 48, False, True),
+    (5, 5, 64, 1, 32, False, True), (8, 2, 128, 64, 128, True, False), (2, 1, 256, 3, 64, True, True),
+    (4, 4, 80, 16, 0, False, True)])
+def test_qk_norm_rope_append(kernels, dtype, n_q, n_kv, d, page_size, rotary, interleaved, with_norm):
+    n, pages = 11, 9
+    qkv = rand((n, (n_q + 2 * n_kv) * d), dtype, 7)
+    q_w = (1 + rand((d,), torch.float32, 8, 0.1)).to(dtype) if with_norm else None
+    k_w = (1 + rand((d,), torch.float32, 9, 0.1)).to(dtype) if with_norm else None
+    positions = torch.tensor([3, 4, 5, 0, 100, 101, 102, 103, 104, 9, 10], dtype=torch.int32).cuda()
+    g = torch.Generator().manual_seed(10)
+    slots = torch.randperm(pages * page_size, generator=g)[:n].to(torch.int32)
+    slots[4] = -1
+    slots = slots.cuda()
+    cos_sin = None
+    if rotary:
+        inv_freq = (1.0 / (1e4 ** (torch.arange(0, rotary, 2, dtype=torch.float32) / rotary))).cuda()
+        cos_sin = torch.empty((n, rotary // 2, 2), dtype=torch.float32).cuda()
+        kernels.rope_table(positions, inv_freq, cos_sin)
+    k_pool = torch.zeros((pages, n_kv, page_size, d), dtype=dtype).cuda()
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty((n, n_q, d), dtype=dtype).cuda()
+    kernels.qk_norm_rope_append(qkv, slots, q_w, k_w, 1e-6, cos_sin, rotary, interleaved, k_pool, v_pool, n_q, n_kv, d, q_out)
+    ek, ev = torch.zeros(k_pool.shape, dtype=torch.float64).cuda(), torch.zeros(k_pool.shape, dtype=torch.float64).cuda()
+    eq = torch.empty(q_out.shape, dtype=torch.float64).cuda()
+    plain_ops.qk_norm_rope_append(qkv, slots, q_w, k_w, 1e-6, cos_sin, rotary, interleaved, ek, ev, n_q, n_kv, d, eq)
+    assert torch.allclose(q_out.double(), eq, **tol(dtype))
+    assert torch.allclose(k_pool.double(), ek, **tol(dtype))
+    assert torch.equal(v_pool.double(), ev)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("inter", [1, 200, 224, 6144])
+def test_silu_mul(kernels, dtype, inter):
+    gate_up = rand((5, 2 * inter), dtype, 11, 3.0)
+    out = torch.empty((5, inter), dtype=dtype).cuda()
+    kernels.silu_mul(gate_up, out)
+    expected = torch.empty((5, inter), dtype=torch.float64).cuda()
+    plain_ops.silu_mul(gate_up, expected)
+    assert torch.allclose(out.double(), expected, **tol(dtype))
+
+
+def _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, seed):
+    """Requests with context ``lengths`` whose last ``query_lens`` tokens are the step's queries;
+    pages are handed out in a shuffled order so that tables are neither contiguous nor sorted."""
+    g = torch.Generator().manual_seed(seed)
+    pages_needed = [(n + page_size - 1) // page_size for n in lengths]
+    total = sum(pages_needed) + 3
+    order = torch.randperm(total, generator=g).tolist()
+    width = max(pages_needed)
+    tables, cursor = [], 0
+    for need in pages_needed:
+        tables.append(order[cursor:cursor + need] + [total - 1] * (width - need))
+        cursor += need
+    k_pool = rand((total, n_kv, page_size, d), dtype, seed + 1)
+    v_pool = rand((total, n_kv, page_size, d), dtype, seed + 2)
+    request_of_token, positions = [], []
+    for r, (length, q_len) in enumerate(zip(lengths, query_lens)):
+        request_of_token += [r] * q_len
+        positions += list(range(length - q_len, length))
+    n = len(positions)
+    q = rand((n, n_q, d), dtype, seed + 3)
+    return (q, k_pool, v_pool, torch.tensor(tables, dtype=torch.int32).cuda(),
+            torch.tensor(request_of_token, dtype=torch.int32).cuda(), torch.tensor(positions, dtype=torch.int32).cuda())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,window", [
+    (4, 2, 16, 16, None), (6, 2, 32, 8, None), (3, 1, 48, 4, None), (5, 5, 64, 1, None), (8, 1, 128, 64, None),
+    (2, 2, 256, 16, None), (4, 2, 80, 5, 7), (6, 3, 96, 16, 33), (4, 1, 112, 32, 1)])
+def test_paged_attention(kernels, dtype, n_q, n_kv, d, page_size, window):
+    lengths, query_lens = [1, 37, 130, 64, 200], [1, 5, 1, 64, 2]
+    q, k_pool, v_pool, tables, request_of_token, positions = _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 20)
+    out = torch.empty_like(q)
+    kernels.paged_attention(q, k_pool, v_pool, tables, request_of_token, positions, d ** -0.5, window, out)
+    expected = torch.empty(q.shape, dtype=torch.float64).cuda()
+    plain_ops.paged_attention(q.cpu(), k_pool.cpu(), v_pool.cpu(), tables.cpu(), request_of_token.cpu(), positions.cpu(),
+                              d ** -0.5, window, expected)
+    assert torch.allclose(out.double(), expected, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_finds_one_far_key(kernels, dtype):
+    """One key among hundreds is made to dominate; the output must be (almost) its value row."""
+    n_q, n_kv, d, page_size = 4, 2, 64, 16
+    lengths, query_lens = [700], [3]
+    q, k_pool, v_pool, tables, request_of_token, positions = _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 30)
+    for target in (0, 15, 16, 300, 696):
+        kp = k_pool.clone()
+        page, offset = int(tables[0, target // page_size]), target % page_size
+        for head in range(n_kv):
+            kp[page, head, offset] = (q[0, head * 2].float() * 40).to(dtype)
+        out = torch.empty_like(q)
+        kernels.paged_attention(q, kp, v_pool, tables, request_of_token, positions, d ** -0.5, None, out)
+        for head in (0, 2):
+            assert torch.allclose(out[0, head].float(), v_pool[page, head // 2, offset].float(), atol=2e-2), target
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (3, 331, 72), (37, 384, 96), (64, 64, 16), (65, 130, 200), (130, 257, 1031)])
+def test_linear_float32(kernels, m, n, k):
+    x, w = rand((m, k), torch.float32, 40), rand((n, k), torch.float32, 41)
+    out = torch.empty((m, n), dtype=torch.float32).cuda()
+    kernels.linear(x, w, out)
+    expected = x.double() @ w.double().T
+    assert torch.allclose(out.double(), expected, atol=1e-5 * k ** 0.5, rtol=1e-5)
+    # a row's result does not depend on the rows beside it
+    alone = torch.empty((1, n), dtype=torch.float32).cuda()
+    kernels.linear(x[m // 2:m // 2 + 1].contiguous(), w, alone)
+    assert torch.equal(alone[0], out[m // 2])
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 331, 72), (37, 384, 96), (130, 264, 1032)])
+def test_linear_bfloat16(kernels, out_dtype, m, n, k):
+    x, w = rand((m, k), torch.bfloat16, 42), rand((n, k), torch.bfloat16, 43)
+    out = torch.empty((m, n), dtype=out_dtype).cuda()
+    kernels.linear(x, w, out)
+    expected = x.double() @ w.double().T
+    assert torch.allclose(out.double(), expected, atol=2e-2 * k ** 0.5 if out_dtype == torch.bfloat16 else 1e-3, rtol=1e-2)
+
+
+def records_tensor(rows):
+    words = [struct.unpack("<8i", struct.pack("<ffiIIiii", t, p, k, seed & 0xFFFFFFFF, seed >> 32, 0, 0, 0))
+             for (t, p, k, seed) in rows]
+    return torch.tensor(words, dtype=torch.int32).cuda()
+
+
+@pytest.mark.parametrize("vocab", [1, 7, 331, 5000, 151936])
+def test_argmax_lowest_index_on_ties(kernels, vocab):
+    logits = rand((3, vocab), torch.float32, 50)
+    if vocab > 5:
+        logits[1, 4] = logits[1, vocab - 1] = 99.0
+    out = torch.empty(3, dtype=torch.int32).cuda()
+    kernels.sample(logits, None, None, None, out)
+    expected = [int(torch.argmax(row)) for row in logits.cpu()]
+    if vocab > 5:
+        expected[1] = 4
+    assert out.tolist() == expected
+
+
+@pytest.mark.parametrize("vocab", [13, 331, 4099])
+def test_sample_matches_plain_rule(kernels, vocab):
+    rows = [(0.0, 1.0, 0, 1), (0.8, 1.0, 0, 2), (1.0, 1.0, 5, 3), (0.7, 0.9, 0, 2 ** 40 + 5), (1.3, 0.5, 11, 7),
+            (2.0, 0.3, 3, 9), (1.0, 1.0, 1, 4), (0.5, 0.999, vocab, 5)]
+    records = records_tensor(rows)
+    logits = rand((len(rows), vocab), torch.float32, 60, 2.0)
+    slot_of_row = torch.arange(len(rows), dtype=torch.int32).cuda()
+    for draw in (0, 1, 17):
+        draw_index = torch.full((len(rows),), draw, dtype=torch.int32).cuda()
+        out = torch.empty(len(rows), dtype=torch.int32).cuda()
+        kernels.sample(logits, records, slot_of_row, draw_index, out)
+        for r, (t, p, k, seed) in enumerate(rows):
+            expected = plain.plain_sample(logits[r].cpu(), t, k, p, seed, draw)
+            assert int(out[r]) == expected, (r, draw)
+
+
+def test_sample_keeps_exactly_k_under_ties(kernels):
+    vocab = 50
+    logits = torch.zeros((1, vocab), dtype=torch.float32)
+    logits[0, [3, 9, 20, 31]] = 5.0          # four equal maxima, top_k = 2 keeps indices 3 and 9
+    records = records_tensor([(1.0, 1.0, 2, 11)])
+    seen = set()
+    for draw in range(64):
+        out = torch.empty(1, dtype=torch.int32).cuda()
+        kernels.sample(logits.cuda(), records, torch.zeros(1, dtype=torch.int32).cuda(),
+                       torch.tensor([draw], dtype=torch.int32).cuda(), out)
+        seen.add(int(out[0]))
+    assert seen == {3, 9}
+
+
+def test_sample_follows_the_softmax(kernels):
+    """Frequencies over many draws approach the softmax of logits / temperature."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5]], dtype=torch.float32).cuda()
+    records = records_tensor([(0.7, 1.0, 0, 123)])
+    draws = 4000
+    big = logits.expand(draws, -1).contiguous()
+    out = torch.empty(draws, dtype=torch.int32).cuda()
+    kernels.sample(big, records, torch.zeros(draws, dtype=torch.int32).cuda(),
+                   torch.arange(draws, dtype=torch.int32).cuda(), out)
+    freq = torch.bincount(out.long().cpu(), minlength=5).double() / draws
+    expected = torch.softmax(logits[0].double().cpu() / 0.7, dim=0)
+    assert float((freq - expected).abs().max()) < 0.03

@@ -1,0 +1,120 @@
+"""The engine against the plain implementation on the GPU, in float32 and in bfloat16: the
+same requests whole, with the last tokens decoded one by one, in portions of changing size,
+and mixed with other requests in a pool so small that pages are used again; through the
+engine in-process and through ``bin/trace_run`` as a user runs it."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+REPO = Path(__file__).resolve().parent.parent
+
+CUTTINGS = {
+    "whole": helpers.cut_whole,
+    "tail": lambda r: helpers.cut_decode_tail(r, 32),
+    "portions": helpers.cut_portions,
+    "mixed": helpers.cut_mixed,
+}
+LENGTHS = (1, 7, 16, 33, 65, 150)
+
+
+def build(folder, dtype, num_pages, page_size):
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200.config import EngineConfig
+    from miniserve_b200.engine.runtime import build_runtime
+
+    return build_runtime(folder, EngineConfig(dtype=dtype, kv_block_size=page_size, num_kv_blocks=num_pages,
+                                              max_num_seqs=4, enable_prefix_cache=False, decode_execution="eager"))
+
+
+def replay(runtime, steps):
+    from miniserve_b200.engine.step import StepEntry
+
+    outputs, manager = {}, runtime.manager
+    for record in steps:
+        entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in record["entries"]]
+        for entry in entries:
+            if entry.request_id not in manager.requests:
+                manager.admit(entry.request_id)
+        reservation = manager.prepare([(e.request_id, len(e.tokens)) for e in entries])
+        outputs[record["step"]] = runtime.step_function.run(entries, reservation).double().cpu()
+        manager.commit(reservation)
+        for rid in record["end"]:
+            manager.release(rid)
+    manager.check_invariants()
+    return outputs
+
+
+def error_bounds(dtype, expected):
+    scale = float(expected.abs().max())
+    if dtype == "float32":
+        return 2e-5 * max(scale, 1.0)
+    return 3e-2 * max(scale, 1.0)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4)])
+@pytest.mark.parametrize("cutting", list(CUTTINGS))
+def test_cuttings_match_plain(tmp_path, dtype, name, page_size, cutting):
+    vocab = helpers.TINY[name]["vocab_size"]
+    requests = {f"r{i}": helpers.random_tokens(vocab, n, seed=100 + i) for i, n in enumerate(LENGTHS)}
+    steps = CUTTINGS[cutting](requests)
+    folder = helpers.make_folder(tmp_path, name, seed=2)
+    pages = (helpers.max_live_tokens(steps, granule=2 * page_size) + page_size - 1) // page_size
+    runtime = build(folder, dtype, pages, page_size)
+    got = helpers.collect(steps, replay(runtime, steps))
+    worst = 0.0
+    for rid, tokens in requests.items():
+        expected = helpers.oracle_logits(folder, tokens)
+        bound = error_bounds(dtype, expected)
+        assert sorted(got[rid]) == list(range(len(tokens)))
+        for position, row in got[rid].items():
+            error = float((row - expected[position]).abs().max())
+            worst = max(worst, error / bound)
+            assert error <= bound, (rid, position, error, bound)
+    assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
+    print(f"worst error / bound = {worst:.3f}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(tmp_path, dtype):
+    """bin/trace_run as a subprocess: protocol, files, page reuse."""
+    name, vocab = "b", helpers.TINY["b"]["vocab_size"]
+    requests = {f"q{i}": helpers.random_tokens(vocab, n, seed=200 + i) for i, n in enumerate((40, 3, 70, 25, 90, 64))}
+    steps = helpers.cut_mixed(requests, seed=5)
+    folder = helpers.make_folder(tmp_path, name, seed=3)
+    out_dir = tmp_path / f"out_{dtype}"
+    max_tokens = helpers.max_live_tokens(steps, granule=64)
+    process = subprocess.Popen(
+        [sys.executable, str(REPO / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out_dir),
+         "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    for record in steps:
+        process.stdin.write(json.dumps(record) + "\n")
+        process.stdin.flush()
+        assert process.stdout.readline().strip() == f"done {record['step']}"
+    process.stdin.close()
+    assert process.wait(timeout=120) == 0
+    outputs = {}
+    for record in steps:
+        wanted = sum(len(e["want"]) for e in record["entries"])
+        path = out_dir / f"{record['step']}.f32"
+        if wanted:
+            outputs[record["step"]] = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(wanted, vocab)).double()
+        else:
+            assert not path.exists()
+    got = helpers.collect(steps, outputs)
+    for rid, tokens in requests.items():
+        expected = helpers.oracle_logits(folder, tokens)
+        bound = error_bounds(dtype, expected)
+        for position, row in got[rid].items():
+            assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
