@@ -107,7 +107,7 @@ def test_rope_table(kernels, half, theta):
     (5, 5, 64, 1, 32, False, True), (8, 2, 128, 64, 128, True, False), (2, 1, 256, 3, 64, True, True),
     (4, 4, 80, 16, 0, False, True)])
 def test_qk_norm_rope_append(kernels, dtype, n_q, n_kv, d, page_size, rotary, interleaved, with_norm):
-    n, pages = 11, 9
+    n, pages = 11, 16
     qkv = rand((n, (n_q + 2 * n_kv) * d), dtype, 7)
     q_w = (1 + rand((d,), torch.float32, 8, 0.1)).to(dtype) if with_norm else None
     k_w = (1 + rand((d,), torch.float32, 9, 0.1)).to(dtype) if with_norm else None
