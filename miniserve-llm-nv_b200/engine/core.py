@@ -75,6 +75,7 @@ class Engine:
         self.finished: dict[str, GenerationResult] = {}
         self.stats = EngineStats()
         self.last_plan: Optional[StepPlan] = None
+        self.last_step_ran = False
         self._arrivals = 0
 
     # ------------------------------------------------------------------ admission
@@ -132,6 +133,7 @@ class Engine:
             self._preempt(victim)
             plan = self.scheduler.schedule(live, self.manager.capacity())
         self.last_plan = plan
+        self.last_step_ran = False
         self.stats.steps += 1
         if plan.is_empty:
             self.stats.empty_steps += 1
@@ -139,6 +141,7 @@ class Engine:
 
         # admit newly planned requests; a reusable prefix may move the start of their portion
         items = []
+        admitted_now = set()
         for item in plan.items:
             seq = self.sequences[item.request_id]
             start, end = item.start, item.end
@@ -146,26 +149,37 @@ class Engine:
                 entry = self.manager.admit(seq.request_id)
                 self.executor.admit(entry.slot, seq.params, seq.seed)
                 seq.status = Status.RUNNING
+                admitted_now.add(seq.request_id)
                 matched = self.manager.attach_prefix(seq.request_id, seq.tokens)
                 if matched:
                     seq.computed = matched
                     self.stats.prefix_hit_tokens += matched
-                    start, end = matched, min(seq.total, matched + (item.end - item.start))
+                    start, end = matched, min(seq.total, max(item.end, matched + 1))
             items.append((seq, start, end, item.is_decode))
 
-        entries = [StepEntry(seq.request_id, seq.token_slice(start, end), [end - start - 1] if end == seq.total else [])
-                   for seq, start, end, _ in items]
-        samples = [SampleRequest(index, self.manager.requests[seq.request_id].slot, len(seq.generated))
-                   for index, (seq, start, end, _) in enumerate(items) if end == seq.total]
-        try:
-            reservation = self.manager.prepare([(seq.request_id, end - start) for seq, start, end, _ in items])
-        except OutOfPagesError:
-            # the plan was made from an estimate; nothing was reserved.  Preempt and try again next step.
-            self.stats.failed_steps += 1
+        # The plan rests on an estimate of free pages.  If the reservation does not fit after all,
+        # the last planned (youngest, lowest priority) request waits for a later step.
+        reservation = None
+        while items:
+            try:
+                reservation = self.manager.prepare([(seq.request_id, end - start) for seq, start, end, _ in items])
+                break
+            except OutOfPagesError:
+                self.stats.failed_steps += 1
+                dropped = items.pop()[0]
+                if dropped.request_id in admitted_now:
+                    # back out of the admission too: reusable pages it pinned can be evicted for older requests
+                    self.manager.release(dropped.request_id)
+                    dropped.status, dropped.computed = Status.WAITING, 0
+        if reservation is None:
             victim = self.scheduler.choose_victim(live)
             if victim is not None:
                 self._preempt(victim)
             return plan
+        entries = [StepEntry(seq.request_id, seq.token_slice(start, end), [end - start - 1] if end == seq.total else [])
+                   for seq, start, end, _ in items]
+        samples = [SampleRequest(index, self.manager.requests[seq.request_id].slot, len(seq.generated))
+                   for index, (seq, start, end, _) in enumerate(items) if end == seq.total]
         try:
             tokens = self.executor.execute(entries, reservation, samples)
         except BaseException as error:
@@ -178,6 +192,7 @@ class Engine:
             self._finalize()
             raise
         self.manager.commit(reservation)
+        self.last_step_ran = True
 
         for seq, start, end, is_decode in items:
             seq.advance(end)
@@ -204,9 +219,9 @@ class Engine:
         for _ in range(max_steps):
             if not self.has_unfinished():
                 break
-            plan = self.step()
-            stalled = stalled + 1 if plan.is_empty else 0
-            if stalled > 3:
+            self.step()
+            stalled = 0 if self.last_step_ran else stalled + 1
+            if stalled > 8:
                 raise RuntimeError("the scheduler cannot make progress: no request fits the free pages and state slots")
         self._finalize()
 

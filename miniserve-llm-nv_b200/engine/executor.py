@@ -27,7 +27,7 @@ class DeviceExecutor:
         if not samples:
             return []
         meta = torch.tensor([[s.slot for s in samples], [s.draw_index for s in samples]], dtype=torch.int32,
-                            pin_memory=True).to(self.device, non_blocking=True)
+                            pin_memory=self.device.type == "cuda").to(self.device, non_blocking=True)
         chosen = torch.empty(len(samples), dtype=torch.int32, device=self.device)
         kernels.sample(logits, self.storage.sampling_records, meta[0], meta[1], chosen)
         return chosen.cpu().tolist()

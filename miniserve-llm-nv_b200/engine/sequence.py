@@ -52,7 +52,7 @@ class Sequence:
 
     @property
     def is_decoding(self) -> bool:
-        return self.status is Status.RUNNING and self.remaining == 1 and self.computed > 0
+        return self.status is Status.RUNNING and self.remaining == 1 and self.computed > 0 and bool(self.generated)
 
     @property
     def done(self) -> bool:

@@ -1,0 +1,203 @@
+"""The cache manager on the CPU: allocator, block tables and slots, step transactions, windows,
+prefix reuse, state slots; no page lost, held twice or freed twice under random orders."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+import miniserve_b200  # noqa: F401
+from miniserve_b200.cache import (RELEASED, CacheManager, OutOfPagesError, OutOfSlotsError, PageAllocator, StateSlots)
+from miniserve_b200.parts import CacheGroup, PagedKVNeed, StateNeed
+
+FULL = CacheGroup(PagedKVNeed(2, 16, None), 3)
+
+
+def window_group(window):
+    return CacheGroup(PagedKVNeed(2, 16, window), 2)
+
+
+def test_allocator_lowest_first_refcounts_and_atomic_failure():
+    allocator = PageAllocator(4)
+    assert allocator.allocate(2) == [0, 1]
+    allocator.retain(1)
+    assert allocator.release(1) is False and allocator.release(1) is True
+    assert allocator.allocate(1) == [1]
+    with pytest.raises(OutOfPagesError, match="requested=3, free=2"):
+        allocator.allocate(3)
+    assert allocator.free_count == 2
+    with pytest.raises(RuntimeError, match="freed twice"):
+        allocator.release(3)
+    with pytest.raises(RuntimeError, match="retained"):
+        allocator.retain(3)
+    allocator.check_invariants()
+
+
+def test_state_slots_lifecycle():
+    slots = StateSlots(2)
+    a, b = slots.allocate("a"), slots.allocate("b")
+    assert (a, b) == (0, 1) and slots.owner(1) == "b"
+    with pytest.raises(OutOfSlotsError):
+        slots.allocate("c")
+    slots.release(a)
+    with pytest.raises(RuntimeError, match="freed twice"):
+        slots.release(a)
+    assert slots.allocate("c") == 0
+    slots.check_invariants()
+
+
+def test_slots_follow_non_contiguous_tables():
+    manager = CacheManager([FULL], page_size=16, num_pages=8, max_seqs=4)
+    manager.admit("a"), manager.admit("b")
+    r = manager.prepare([("a", 17), ("b", 3)])
+    assert r.items[0].tables == [[0, 1]] and r.items[1].tables == [[2]]
+    manager.commit(r)
+    r = manager.prepare([("a", 16), ("b", 30)])          # a: page 3; b: pages 4, 5
+    a, b = r.items
+    assert a.tables == [[0, 1, 3]] and b.tables == [[2, 4, 5]]
+    for position, slot in zip(range(17, 33), a.slots[0]):
+        assert slot == a.tables[0][position // 16] * 16 + position % 16
+    assert b.slots[0][12:15] == [2 * 16 + 15, 4 * 16 + 0, 4 * 16 + 1]       # positions 15, 16, 17
+    manager.commit(r)
+    assert manager.length("a") == 33 and manager.length("b") == 33
+    manager.check_invariants()
+
+
+def test_abort_returns_pages_and_keeps_lengths():
+    manager = CacheManager([FULL], page_size=4, num_pages=4, max_seqs=2)
+    manager.admit("a")
+    manager.commit(manager.prepare([("a", 5)]))
+    before = manager.capacity()
+    r = manager.prepare([("a", 6)])
+    assert manager.capacity().free_pages == (1,)
+    with pytest.raises(RuntimeError, match="neither committed nor aborted"):
+        manager.prepare([("a", 1)])
+    with pytest.raises(RuntimeError, match="open step"):
+        manager.release("a")
+    manager.abort(r)
+    assert manager.capacity() == before and manager.length("a") == 5
+    with pytest.raises(RuntimeError):
+        manager.commit(r)
+    manager.check_invariants()
+
+
+def test_prepare_is_all_or_nothing():
+    manager = CacheManager([FULL], page_size=4, num_pages=3, max_seqs=3)
+    manager.admit("a"), manager.admit("b")
+    with pytest.raises(OutOfPagesError):
+        manager.prepare([("a", 8), ("b", 5)])
+    assert manager.capacity().free_pages == (3,)
+    manager.commit(manager.prepare([("a", 8), ("b", 4)]))
+    with pytest.raises(ValueError, match="twice"):
+        manager.prepare([("a", 1), ("a", 1)])
+    manager.release("a"), manager.release("b")
+    assert manager.capacity().free_pages == (3,) and manager.capacity().free_slots == 3
+    with pytest.raises(KeyError):
+        manager.release("a")
+
+
+def test_groups_have_pages_of_their_own_and_windows_give_pages_back():
+    manager = CacheManager([FULL, window_group(6)], page_size=4, num_pages=10, max_seqs=2)
+    manager.admit("a")
+    manager.commit(manager.prepare([("a", 9)]))           # pages 0..2 in both groups
+    entry = manager.requests["a"]
+    # next query at position 9 sees keys 4..9 in the window group: page 0 (positions 0..3) is given back
+    assert entry.tables[0] == [0, 1, 2] and entry.tables[1] == [RELEASED, 1, 2]
+    assert manager.capacity().free_pages == (7, 8)
+    manager.commit(manager.prepare([("a", 8)]))           # length 17: window keys 12..17 -> pages 0,1,2 gone
+    assert entry.tables[1][:3] == [RELEASED] * 3 and entry.tables[1][3] == 0     # the freed page 0 is used again
+    assert all(p != RELEASED for p in entry.tables[0])
+    manager.check_invariants()
+    manager.release("a")
+    assert manager.capacity().free_pages == (10, 10)
+
+
+def test_state_groups_disable_prefix_reuse_and_count_slots():
+    manager = CacheManager([FULL, CacheGroup(StateNeed((4,)), 1)], page_size=4, num_pages=4, max_seqs=2,
+                           enable_prefix_cache=True)
+    assert manager.prefix is None and len(manager.allocators) == 1
+    assert manager.group_index == [("paged", 0), ("state", 0)]
+    assert CacheManager([window_group(8)], 4, 4, 2, enable_prefix_cache=True).prefix is None
+
+
+def test_prefix_pages_are_shared_and_evicted_when_needed():
+    manager = CacheManager([FULL], page_size=4, num_pages=6, max_seqs=3, enable_prefix_cache=True)
+    prompt = list(range(100, 110))                        # 2 full pages + 2 tokens
+    manager.admit("a")
+    assert manager.attach_prefix("a", prompt) == 0
+    manager.commit(manager.prepare([("a", 10)]))
+    assert manager.cache_prefix("a", prompt) == 2
+    manager.admit("b")
+    assert manager.attach_prefix("b", prompt[:8] + [7, 7, 7]) == 8
+    assert manager.requests["b"].tables == [[0, 1]] and manager.allocators[0].refcount(0) == 3
+    manager.admit("c")
+    assert manager.attach_prefix("c", prompt[:8]) == 4    # a full hit leaves the last page to compute
+    manager.check_invariants()
+    manager.release("a"), manager.release("b"), manager.release("c")
+    snapshot = manager.capacity()
+    assert snapshot.free_pages == (4,) and snapshot.reclaimable_pages == (2,)
+    manager.admit("d")
+    manager.commit(manager.prepare([("d", 21)]))          # needs all 6 pages: both cached pages are evicted
+    assert manager.capacity().free_pages == (0,) and not manager.prefix.entries
+    manager.check_invariants()
+
+
+def test_prefix_in_use_is_not_evicted():
+    manager = CacheManager([FULL], page_size=4, num_pages=4, max_seqs=3, enable_prefix_cache=True)
+    prompt = list(range(9))
+    manager.admit("a")
+    manager.commit(manager.prepare([("a", 9)]))
+    manager.cache_prefix("a", prompt)
+    manager.admit("b")
+    manager.attach_prefix("b", prompt)
+    manager.release("a")                                  # page 2 free; pages 0, 1 held by b and the cache
+    with pytest.raises(OutOfPagesError):
+        manager.prepare([("b", 9)])                       # needs 3 pages, 2 are free, nothing reclaimable
+    manager.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_lose_no_page(seed):
+    rng = random.Random(seed)
+    groups = [FULL, window_group(rng.choice((5, 9, 16)))] if seed % 2 else [FULL]
+    manager = CacheManager(groups, page_size=rng.choice((1, 4, 16)), num_pages=24, max_seqs=5,
+                           enable_prefix_cache=True)
+    live: dict[str, list[int]] = {}
+    shared = [rng.randrange(50) for _ in range(40)]
+    counter = 0
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and manager.slots.free_count:
+            rid = f"r{counter}"
+            counter += 1
+            manager.admit(rid)
+            live[rid] = shared[:rng.randrange(0, 40)] + [rng.randrange(50) for _ in range(rng.randrange(1, 30))]
+            manager.attach_prefix(rid, live[rid])
+        elif action < 0.8 and live:
+            chosen = rng.sample(sorted(live), rng.randrange(1, len(live) + 1))
+            items = [(rid, rng.randrange(1, 12)) for rid in chosen]
+            try:
+                reservation = manager.prepare(items)
+            except OutOfPagesError:
+                manager.check_invariants()
+                continue
+            manager.check_invariants()
+            if rng.random() < 0.2:
+                manager.abort(reservation)
+            else:
+                manager.commit(reservation)
+                for rid, _ in items:
+                    if manager.length(rid) >= len(live[rid]):
+                        manager.cache_prefix(rid, live[rid])
+        elif live:
+            rid = rng.choice(sorted(live))
+            manager.release(rid)
+            del live[rid]
+        manager.check_invariants()
+    for rid in list(live):
+        manager.release(rid)
+    manager.check_invariants()
+    snapshot = manager.capacity()
+    assert all(f + r == t for f, r, t in zip(snapshot.free_pages, snapshot.reclaimable_pages, snapshot.total_pages))
+    assert snapshot.free_slots == 5

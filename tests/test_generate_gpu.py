@@ -1,0 +1,118 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation: greedy and sampled tokens, long decoding, scheduling under few pages."""
+
+from __future__ import annotations
+
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen3 as plain
+
+pytestmark = pytest.mark.gpu
+REPO = Path(__file__).resolve().parent.parent
+
+
+def check_against_plain(folder, prompt, produced, params, dtype, seed=None):
+    """Follows the produced tokens and checks each against the plain rule; a different token is
+    accepted only where the plain scores of the two are within the path's rounding."""
+    config, weights = plain.load_folder(folder, torch.float64)
+    tokens = list(prompt)
+    for draw, token in enumerate(produced):
+        logits = plain.plain_logits(tokens, weights, config)[-1]
+        expected = plain.plain_sample(logits.float(), params.temperature, params.top_k, params.top_p, seed or 0, draw)
+        if token != expected:
+            limit = (1e-4 if dtype == "float32" else 4e-2) * max(1.0, float(logits.abs().max()))
+            if params.temperature == 0:
+                assert float(logits[expected] - logits[token]) <= limit, (draw, token, expected)
+            else:
+                scaled = logits / params.temperature
+                noisy = [float(scaled[t]) + plain.plain_gumbel(seed, draw, t) for t in (expected, token)]
+                assert noisy[0] - noisy[1] <= limit / params.temperature, (draw, token, expected)
+        tokens.append(token)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size,execution", [("a", 16, "eager"), ("b", 8, "cuda_graph"), ("c", 4, "cuda_graph")])
+def test_greedy_generation(tmp_path, dtype, name, page_size, execution):
+    from miniserve_b200.engine.llm import LLM
+    from miniserve_b200.sampling import SamplingParams
+
+    folder = helpers.make_folder(tmp_path, name, seed=5)
+    vocab = helpers.TINY[name]["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=400 + n) for n in (1, 7, 16, 33)]
+    llm = LLM(str(folder), dtype=dtype, kv_block_size=page_size, num_kv_blocks=40, max_num_seqs=4,
+              max_num_batched_tokens=24, prefill_chunk_size=12, decode_execution=execution)
+    params = SamplingParams(temperature=0.0, max_new_tokens=8)
+    results = llm.generate(prompts, params)
+    for prompt, result in zip(prompts, results):
+        assert len(result.token_ids) == 8 and result.finish_reason == "length"
+        check_against_plain(folder, prompt, result.token_ids, params, dtype)
+    # the same prompts one at a time give the same tokens as in the batch
+    alone = [llm.generate([p], params)[0].token_ids for p in prompts]
+    if dtype == "float32":
+        assert alone == [r.token_ids for r in results]
+    llm.runtime.manager.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sampled_generation_with_prefix_and_chunks(tmp_path, dtype):
+    """Config B of the brief: five prompts, two sharing 16 tokens, chunk 12, temperature 0.8, a seed each."""
+    from miniserve_b200.engine.llm import LLM
+    from miniserve_b200.sampling import SamplingParams
+
+    folder = helpers.make_folder(tmp_path, "b", seed=6)
+    vocab = helpers.TINY_B["vocab_size"]
+    shared = helpers.random_tokens(vocab, 16, seed=1)
+    prompts = [helpers.random_tokens(vocab, 3, 2), helpers.random_tokens(vocab, 9, 3),
+               shared + helpers.random_tokens(vocab, 8, 4), shared + helpers.random_tokens(vocab, 24, 5),
+               helpers.random_tokens(vocab, 65, 6)]
+    params = [SamplingParams(temperature=0.8, max_new_tokens=10, seed=1000 + i, top_k=(0, 20, 0, 0, 50)[i],
+                             top_p=(1.0, 1.0, 0.9, 1.0, 0.8)[i]) for i in range(5)]
+    llm = LLM(str(folder), dtype=dtype, kv_block_size=8, num_kv_blocks=48, max_num_seqs=3, max_num_batched_tokens=32,
+              prefill_chunk_size=12)
+    first = llm.generate(prompts, params)
+    for prompt, param, result in zip(prompts, params, first):
+        check_against_plain(folder, prompt, result.token_ids, param, dtype, seed=param.seed)
+    assert llm.engine.stats.prefix_hit_tokens >= 16
+    again = llm.generate(prompts, params)               # same seeds, now with every prompt's pages cached
+    assert [r.token_ids for r in again] == [r.token_ids for r in first]
+    other = llm.generate(prompts[:1], SamplingParams(temperature=0.8, max_new_tokens=10, seed=7))
+    assert other[0].token_ids != first[0].token_ids
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_under_few_pages(tmp_path, dtype):
+    """200 decoded tokens per request with so few pages that requests are preempted and recomputed."""
+    from miniserve_b200.engine.llm import LLM
+    from miniserve_b200.sampling import SamplingParams
+
+    folder = helpers.make_folder(tmp_path, "a", seed=7)
+    prompts = [helpers.random_tokens(256, n, seed=500 + n) for n in (5, 12, 30)]
+    params = SamplingParams(temperature=0.0, max_new_tokens=200)
+    llm = LLM(str(folder), dtype=dtype, kv_block_size=16, num_kv_blocks=30, max_num_seqs=3)
+    results = llm.generate(prompts, params)
+    assert llm.engine.stats.preemptions >= 1
+    for prompt, result in zip(prompts, results):
+        assert len(result.token_ids) == 200
+        if dtype == "float32":
+            check_against_plain(folder, prompt, result.token_ids, params, dtype)
+    assert llm.runtime.manager.capacity().free_slots == 3
+
+
+def test_command_line(tmp_path):
+    folder = helpers.make_folder(tmp_path, "a", seed=8)
+    command = [sys.executable, "-m", "miniserve_b200.generate", "--model", str(folder), "--dtype", "float32",
+               "--prompt-ids", "5,17,3", "--prompt-lens", "9", "--max-new-tokens", "5", "--num-kv-blocks", "16",
+               "--max-num-seqs", "2", "--json"]
+    done = subprocess.run(command, cwd=REPO, capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stderr
+    lines = [json.loads(line) for line in done.stdout.strip().splitlines()]
+    assert len(lines) == 2 and all(len(line["token_ids"]) == 5 for line in lines)
+    from miniserve_b200.sampling import SamplingParams
+    check_against_plain(folder, [5, 17, 3], lines[0]["token_ids"], SamplingParams(), "float32")

@@ -1,0 +1,208 @@
+"""The scheduler's decisions and the engine loop's transactions, on the CPU with an executor
+that returns scripted tokens."""
+
+from __future__ import annotations
+
+import pytest
+
+import miniserve_b200  # noqa: F401
+from miniserve_b200.cache import CacheManager
+from miniserve_b200.engine.core import Engine, RequestRejected
+from miniserve_b200.engine.scheduler import Scheduler
+from miniserve_b200.engine.sequence import Sequence, Status
+from miniserve_b200.parts import CacheGroup, PagedKVNeed
+from miniserve_b200.sampling import SamplingParams
+
+GROUP = CacheGroup(PagedKVNeed(2, 16, None), 2)
+
+
+class ScriptedExecutor:
+    """Next token = (sum of the request's tokens so far + draw index) % vocab: depends on the whole
+    sequence, so any lost or repeated token changes everything after it."""
+
+    def __init__(self, vocab=97):
+        self.vocab, self.admitted, self.calls, self.fail_next = vocab, [], [], None
+        self.history: dict[str, list[int]] = {}
+
+    def admit(self, slot, params, seed):
+        self.admitted.append((slot, params.temperature, seed))
+
+    def execute(self, entries, reservation, samples):
+        if self.fail_next is not None:
+            error, self.fail_next = self.fail_next, None
+            raise error
+        self.calls.append([(e.request_id, len(e.tokens), tuple(e.want)) for e in entries])
+        for entry, item in zip(entries, reservation.items):
+            seen = self.history.setdefault(entry.request_id, [])
+            assert item.start <= len(seen), "a gap in the positions that reached the executor"
+            del seen[item.start:]
+            seen.extend(entry.tokens)
+        return [(sum(self.history[entries[s.entry].request_id]) + s.draw_index) % self.vocab for s in samples]
+
+
+def expected_tokens(prompt, n, vocab=97, stop=()):
+    tokens, out = list(prompt), []
+    for draw in range(n):
+        token = (sum(tokens) + draw) % vocab
+        out.append(token)
+        tokens.append(token)
+        if token in stop:
+            break
+    return out
+
+
+def make_engine(num_pages=16, page_size=4, max_seqs=4, budget=24, chunked=True, chunk=None, prefix=False, max_len=256):
+    manager = CacheManager([GROUP], page_size, num_pages, max_seqs, enable_prefix_cache=prefix)
+    scheduler = Scheduler(max_num_seqs=max_seqs, max_num_batched_tokens=budget, enable_chunked_prefill=chunked,
+                          prefill_chunk_size=chunk)
+    executor = ScriptedExecutor()
+    return Engine(manager, scheduler, executor, vocab_size=97, max_model_len=max_len), executor
+
+
+def run(engine):
+    engine.run_until_done()
+    results = dict(engine.finished)
+    engine.manager.check_invariants()
+    return results
+
+
+def test_sampling_params_bounds():
+    for bad in (dict(temperature=-0.1), dict(temperature=2.5), dict(temperature=float("nan")), dict(top_p=0.0),
+                dict(top_p=1.5), dict(top_k=-1), dict(max_new_tokens=0), dict(stop_token_ids=[1]),
+                dict(stop_token_ids=(1, 1)), dict(seed=-1), dict(seed=2 ** 63), dict(temperature=True)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
+    assert SamplingParams().temperature == 0.0 and SamplingParams().max_new_tokens == 4
+
+
+def test_sequence_invariant_and_finish_rules():
+    seq = Sequence("r", (1, 2, 3), SamplingParams(max_new_tokens=3, stop_token_ids=(9,)), 0, 0)
+    seq.status = Status.RUNNING
+    with pytest.raises(RuntimeError):
+        seq.append_sampled(5)                       # nothing computed yet
+    seq.advance(2)
+    assert not seq.is_decoding and seq.remaining == 1
+    seq.advance(3)
+    seq.append_sampled(5)
+    assert seq.is_decoding and seq.total == seq.computed + 1 and seq.token_slice(2, 4) == [3, 5]
+    with pytest.raises(RuntimeError):
+        seq.advance(5)
+    seq.advance(4)
+    seq.append_sampled(9)
+    assert seq.done and seq.finish_reason == "stop" and seq.generated == [5, 9]
+
+
+def test_plan_decodes_first_then_portions_within_the_budget():
+    engine, executor = make_engine(num_pages=32, budget=24, chunk=12)
+    prompts = {"r0": [1], "r1": list(range(7)), "r2": list(range(16)), "r3": list(range(33))}
+    for rid, prompt in prompts.items():
+        engine.submit(rid, prompt, SamplingParams(max_new_tokens=3))
+    plan = engine.step()
+    assert [(i.request_id, i.start, i.end) for i in plan.items] == [("r0", 0, 1), ("r1", 0, 7), ("r2", 0, 12), ("r3", 0, 4)]
+    assert executor.calls[0] == [("r0", 1, (0,)), ("r1", 7, (6,)), ("r2", 12, ()), ("r3", 4, ())]
+    plan = engine.step()
+    assert [(i.request_id, i.start, i.end, i.is_decode) for i in plan.items] == [
+        ("r0", 1, 2, True), ("r1", 7, 8, True), ("r2", 12, 16, False), ("r3", 4, 16, False)]
+    results = run(engine)
+    for rid, prompt in prompts.items():
+        assert results[rid].token_ids == expected_tokens(prompt, 3) and results[rid].finish_reason == "length"
+    assert engine.manager.capacity().free_pages == (32,) and engine.manager.capacity().free_slots == 4
+
+
+def test_stop_token_ends_and_is_not_forwarded():
+    engine, executor = make_engine()
+    prompt = [3, 4]
+    first = expected_tokens(prompt, 1)[0]
+    engine.submit("r", prompt, SamplingParams(max_new_tokens=8, stop_token_ids=(first,)))
+    results = run(engine)
+    assert results["r"].token_ids == [first] and results["r"].finish_reason == "stop"
+    assert sum(n for call in executor.calls for _, n, _ in call) == 2          # the stop token never ran
+
+
+def test_unchunked_prompts_wait_for_budget_and_rejections():
+    engine, _ = make_engine(budget=10, chunked=False)
+    with pytest.raises(RequestRejected, match="CHUNKED_PREFILL_DISABLED"):
+        engine.submit("big", list(range(11)), SamplingParams())
+    engine.submit("a", list(range(8)), SamplingParams(max_new_tokens=2))
+    engine.submit("b", list(range(8)), SamplingParams(max_new_tokens=2))
+    plan = engine.step()
+    assert [(i.request_id, i.end) for i in plan.items] == [("a", 8)]            # b does not fit the budget whole
+    with pytest.raises(RequestRejected, match="duplicate"):
+        engine.submit("a", [1], SamplingParams())
+    with pytest.raises(RequestRejected, match="vocabulary"):
+        engine.submit("c", [97], SamplingParams())
+    with pytest.raises(RequestRejected, match="max_model_len"):
+        engine.submit("c", [1] * 250, SamplingParams(max_new_tokens=10))
+    small, _ = make_engine(num_pages=2)
+    with pytest.raises(RequestRejected, match="CONTEXT_CAPACITY_EXCEEDED"):
+        small.submit("c", [1] * 8, SamplingParams(max_new_tokens=1))
+    results = run(engine)
+    assert results["b"].token_ids == expected_tokens(list(range(8)), 2)
+
+
+def test_more_requests_than_state_slots():
+    engine, executor = make_engine(max_seqs=2, num_pages=64)
+    prompts = {f"r{i}": [i + 1, i + 2, i + 3] for i in range(5)}
+    for rid, prompt in prompts.items():
+        engine.submit(rid, prompt, SamplingParams(max_new_tokens=4))
+    plan = engine.step()
+    assert len(plan.items) == 2
+    results = run(engine)
+    assert all(results[rid].token_ids == expected_tokens(p, 4) for rid, p in prompts.items())
+    assert len({slot for slot, _, _ in executor.admitted}) == 2
+
+
+def test_pages_run_out_youngest_is_preempted_and_recomputed():
+    # 6 pages of 4 tokens; two requests of 9 + 12 tokens each need 6 pages: they cannot both finish at once.
+    engine, executor = make_engine(num_pages=6, page_size=4, budget=64)
+    prompts = {"old": list(range(1, 10)), "young": list(range(11, 20))}
+    engine.submit("old", prompts["old"], SamplingParams(max_new_tokens=12), arrival=0)
+    engine.submit("young", prompts["young"], SamplingParams(max_new_tokens=12), arrival=1)
+    results = run(engine)
+    assert engine.stats.preemptions >= 1 and results["young"].preemptions >= 1 and results["old"].preemptions == 0
+    for rid, prompt in prompts.items():
+        assert results[rid].token_ids == expected_tokens(prompt, 12), rid
+    assert engine.manager.capacity().free_pages == (6,)
+
+
+def test_executor_failure_aborts_the_step():
+    engine, executor = make_engine()
+    engine.submit("a", [1, 2, 3], SamplingParams(max_new_tokens=2))
+    engine.step()
+    engine.submit("b", [4, 5], SamplingParams(max_new_tokens=2))
+    free_before = engine.manager.capacity().free_pages
+    executor.fail_next = RuntimeError("device fault")
+    with pytest.raises(RuntimeError, match="device fault"):
+        engine.step()
+    assert engine.finished["a"].finish_reason.startswith("error") and engine.finished["b"].finish_reason.startswith("error")
+    engine.manager.check_invariants()
+    assert engine.manager.capacity().free_pages == (16,) and engine.manager.capacity().free_slots == 4
+    assert free_before != (16,)
+    engine.submit("c", [7, 8], SamplingParams(max_new_tokens=2))
+    assert run(engine)["c"].token_ids == expected_tokens([7, 8], 2)
+
+
+def test_prefix_hit_skips_shared_pages():
+    engine, executor = make_engine(num_pages=32, page_size=4, budget=64, prefix=True)
+    shared = list(range(20, 36))                                  # 4 full pages
+    engine.submit("a", shared + [1, 2], SamplingParams(max_new_tokens=2))
+    run(engine)
+    engine.submit("b", shared + [3], SamplingParams(max_new_tokens=2))
+    executor.history["b"] = list(shared)                          # what is in the shared pages already
+    results = run(engine)
+    assert engine.stats.prefix_hit_tokens == 16
+    assert ("b", 1, (0,)) in executor.calls[-2]                   # only the token after the shared pages ran
+    assert results["b"].token_ids == expected_tokens(shared + [3], 2)
+
+
+def test_preemption_with_reusable_prefix_makes_progress():
+    """A preempted request finds its own prompt pages cached on re-admission; the pages the
+    scheduler counted as reclaimable are then held again.  The step must shrink, not repeat."""
+    engine, executor = make_engine(num_pages=9, page_size=4, budget=64, prefix=True, max_seqs=3)
+    prompts = {"r0": list(range(1, 6)), "r1": list(range(11, 20)), "r2": list(range(21, 34))}
+    for index, (rid, prompt) in enumerate(prompts.items()):
+        engine.submit(rid, prompt, SamplingParams(max_new_tokens=18), arrival=index)
+    results = run(engine)
+    assert engine.stats.preemptions >= 1
+    for rid, prompt in prompts.items():
+        assert results[rid].token_ids == expected_tokens(prompt, 18), rid
