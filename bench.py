@@ -1,0 +1,282 @@
+"""Decode and prefill throughput of the engine at Qwen3-1.7B size with random weights.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line.  ``value`` is decoded tokens per second at batch 8 and the context
+length below, timed on the device over exactly K decode steps through the step function;
+``e2e`` is the same through the engine loop a user drives (host token ids in, sampled token
+ids out, every step).  ``prefill`` times one 2,048-token prompt, ``roofline`` relates the
+decode step to the memory bandwidth, ``points`` adds batch 1 and 64.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+
+# Qwen3-1.7B layer sizes.
+MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=2048, intermediate_size=6144,
+             num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128, vocab_size=151936,
+             max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_dropout=0.0,
+             hidden_act="silu", attention_bias=False, tie_word_embeddings=True)
+CONTEXT = 4096           # tokens each request holds at the end of the timed decode steps
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            data = json.loads(path.read_text())
+            flat = {}
+
+            def walk(node):
+                if isinstance(node, dict):
+                    for key, value in node.items():
+                        if isinstance(value, (int, float)):
+                            flat.setdefault(key, float(value))
+                        else:
+                            walk(value)
+            walk(data)
+            if "hbm_gbs" in flat and "bf16_tflops" in flat:
+                return flat, "measured"
+        except (ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs (reads only)."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.samples: list[list[str]] = []
+        self.process = None
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self) -> None:
+        for line in self.process.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc) -> None:
+        if self.process is not None:
+            self.process.terminate()
+
+    def summary(self) -> dict:
+        clocks = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        maxima = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({name for s in self.samples for name, flag in zip(names, s[2:]) if flag.lower().startswith("active")})
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max(maxima) if maxima else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def reference_arm(args) -> int:
+    """MiniServe itself: its native extension builds only for sm_75 / sm_120 (its CMakeLists.txt requires one
+    of them) and its engine refuses to start without that extension, so there is nothing to run on sm_100."""
+    marker = REPO / "baseline" / "_ref" / "miniserve"
+    why = ("MiniServe's CUDA extension is built for sm_75 or sm_120 only and its engine core requires it; "
+           "no sm_100 build exists" if marker.exists() else
+           "the reference is not installed under baseline/_ref (its wheel needs a CUDA build for sm_75/sm_120 only)")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
+                        help="fewer layers than the model has (named in the output); for quick checks only")
+    parser.add_argument("--skip-points", action="store_true")
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200 import kernels
+    from miniserve_b200.config import EngineConfig
+    from miniserve_b200.engine.llm import build_engine
+    from miniserve_b200.engine.runtime import build_runtime
+    from miniserve_b200.engine.step import StepEntry
+    from miniserve_b200.sampling import SamplingParams
+
+    config = dict(MODEL, num_hidden_layers=args.layers)
+    max_batch = args.batch if args.skip_points else max(args.batch, 64)
+    pages = max_batch * ((CONTEXT + PAGE_SIZE - 1) // PAGE_SIZE) + 64
+    runtime = build_runtime(None, EngineConfig(
+        dtype="bfloat16", max_model_len=CONTEXT, max_num_seqs=max_batch, kv_block_size=PAGE_SIZE, num_kv_blocks=pages,
+        max_num_batched_tokens=8192, enable_prefix_cache=False, decode_execution="cuda_graph"),
+        config_dict=config, weights_seed=0)
+    manager, step_function = runtime.manager, runtime.step_function
+    vocab = config["vocab_size"]
+    generator = torch.Generator().manual_seed(1)
+
+    def prompt(n: int) -> list[int]:
+        return torch.randint(0, vocab, (n,), generator=generator).tolist()
+
+    def event_time(fn, repeats: int = 1) -> float:
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(repeats):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / 1e3
+
+    def fill(batch: int, length: int) -> list[str]:
+        """Admits ``batch`` requests and prefills ``length`` tokens each through the step function."""
+        ids = [f"b{batch}-{i}" for i in range(batch)]
+        for rid in ids:
+            manager.admit(rid)
+            runtime.storage.reset_slot(manager.requests[rid].slot, 0.0, 1.0, 0, 0)
+            done = 0
+            while done < length:
+                take = min(2048, length - done)
+                entries = [StepEntry(rid, prompt(take), [])]
+                reservation = manager.prepare([(rid, take)])
+                step_function.run(entries, reservation)
+                manager.commit(reservation)
+                done += take
+        torch.cuda.synchronize()
+        return ids
+
+    def decode_steps(ids: list[str], count: int) -> None:
+        tokens = [1] * len(ids)
+        for _ in range(count):
+            entries = [StepEntry(rid, [tokens[i]], [0]) for i, rid in enumerate(ids)]
+            reservation = manager.prepare([(rid, 1) for rid in ids])
+            step_function.run(entries, reservation, [0] * len(ids))
+            manager.commit(reservation)
+
+    def measure_decode(batch: int, steps: int) -> tuple[float, float, int]:
+        """(seconds per step, mean live context over the timed steps, kernel launches per step)."""
+        ids = fill(batch, CONTEXT - steps - warmup)
+        decode_steps(ids, warmup)
+        before = manager.length(ids[0])
+        seconds = event_time(lambda: decode_steps(ids, steps)) / steps
+        mean_context = (before + manager.length(ids[0]) + 1) / 2
+        launches = step_function.graphs[next(b for b in sorted(step_function.graphs) if b >= batch)].kernel_launches
+        for rid in ids:
+            manager.release(rid)
+        return seconds, mean_context, launches
+
+    # ---------------------------------------------------------------- prefill of 2,048 tokens
+    def prefill_once() -> None:
+        manager.admit("p")
+        entries = [StepEntry("p", prefill_prompt, [PREFILL_TOKENS - 1])]
+        reservation = manager.prepare([("p", PREFILL_TOKENS)])
+        step_function.run(entries, reservation)
+        manager.commit(reservation)
+        manager.release("p")
+
+    prefill_prompt = prompt(PREFILL_TOKENS)
+    for _ in range(warmup):
+        prefill_once()
+    prefill_seconds = min(event_time(prefill_once) for _ in range(3))
+    h, i_, nq, nkv, d, layers = (config[k] for k in ("hidden_size", "intermediate_size", "num_attention_heads",
+                                                      "num_key_value_heads", "head_dim", "num_hidden_layers"))
+    matrix_params = layers * (h * (nq + 2 * nkv) * d + nq * d * h + 3 * h * i_)
+    prefill_flops = 2 * matrix_params * PREFILL_TOKENS + 2 * vocab * h \
+        + layers * 4 * nq * d * PREFILL_TOKENS * (PREFILL_TOKENS + 1) / 2
+    peak, peak_source = peaks()
+
+    # ---------------------------------------------------------------- decode, device-timed
+    with ClockSampler() as clocks:
+        step_seconds, mean_context, launches = measure_decode(args.batch, args.steps)
+    clock_summary = clocks.summary()
+    weight_bytes = 2 * (matrix_params + vocab * h) + 2 * h * (2 * layers + 1) + 2 * 2 * d * layers
+    kv_bytes_per_token = 2 * layers * nkv * d * 2
+    step_bytes = weight_bytes + kv_bytes_per_token * mean_context * args.batch
+    achieved_gbs = step_bytes / step_seconds / 1e9
+
+    points = {}
+    if not args.skip_points:
+        for batch in (1, 64):
+            seconds, _, _ = measure_decode(batch, min(args.steps, 32))
+            points[f"decode_b{batch}"] = round(batch / seconds, 1)
+
+    # ---------------------------------------------------------------- end to end through the engine loop
+    engine = build_engine(runtime)
+    for index in range(args.batch):
+        engine.submit(f"e{index}", prompt(CONTEXT - args.steps - warmup - 1),
+                      SamplingParams(temperature=0.0, max_new_tokens=args.steps + warmup + 1))
+    while any(not s.is_decoding for s in engine.sequences.values()):
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    started = time.perf_counter()
+    for _ in range(args.steps):
+        engine.step()
+    torch.cuda.synchronize()
+    e2e_seconds = (time.perf_counter() - started) / args.steps
+    graph = step_function.graphs[next(b for b in sorted(step_function.graphs) if b >= args.batch)]
+    h2d_bytes = graph.host.numel() * 4
+    d2h_bytes = args.batch * 4
+
+    value = args.batch / step_seconds
+    line = {
+        "metric": "Qwen3-1.7B bf16 decode tok/s @ batch 8 (context 4096); prefill tok/s @ 2,048 tokens",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(step_seconds * 1e3, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random weights)",
+        "impl": "ours",
+        "config": {"model": "Qwen3-1.7B shape", "layers": layers, "layers_of_model": MODEL["num_hidden_layers"],
+                   "hidden": h, "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": i_, "vocab": vocab,
+                   "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT,
+                   "context_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "single GPU",
+                   "decode_execution": "cuda_graph", "l2": "inputs larger than L2 (weights + cache read every step)"},
+        "e2e": {"value": round(args.batch / e2e_seconds, 1), "unit": "tokens/s", "ms_per_step": round(e2e_seconds * 1e3, 4),
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+        "gpu_launches": launches * args.steps,
+        "prefill": {"value": round(PREFILL_TOKENS / prefill_seconds, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_seconds * 1e3, 3),
+                    "frac": round(prefill_flops / prefill_seconds / (peak["bf16_tflops"] * 1e12), 4),
+                    "peak": f"{peak['bf16_tflops']} TFLOP/s bf16 of {peak_source}"},
+        "roofline": {"bound": "hbm", "achieved": round(achieved_gbs, 1), "peak": peak["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved_gbs / peak["hbm_gbs"], 4), "peak_source": peak_source,
+                     "bytes_per_step": int(step_bytes)},
+        "points": points,
+        "clocks": clock_summary,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -23,9 +23,14 @@ class DeviceExecutor:
         self.storage.reset_slot(slot, params.temperature, params.top_p, params.top_k, seed)
 
     def execute(self, entries: Seq[StepEntry], reservation: StepReservation, samples) -> list[int]:
-        logits = self.step_function.run(entries, reservation)
+        draws = None
+        if len(samples) == len(entries):
+            draws = [s.draw_index for s in samples]
+        logits = self.step_function.run(entries, reservation, draws)
         if not samples:
             return []
+        if self.step_function.last_tokens is not None:      # a replayed graph sampled already
+            return self.step_function.last_tokens.cpu().tolist()
         meta = torch.tensor([[s.slot for s in samples], [s.draw_index for s in samples]], dtype=torch.int32,
                             pin_memory=self.device.type == "cuda").to(self.device, non_blocking=True)
         chosen = torch.empty(len(samples), dtype=torch.int32, device=self.device)

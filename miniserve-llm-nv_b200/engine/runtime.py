@@ -17,9 +17,10 @@ from .. import kernels
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.engine_config import EngineConfig
-from ..config.registry import load_model_config
+from ..config.registry import load_model_config, resolve_architecture
 from ..parts.model import DecoderModel
 from ..weights.loader import load_tensors
+from ..weights.random_init import random_tensors_on_device
 from .step import StepFunction
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -47,7 +48,11 @@ def require_device(device: str) -> torch.device:
     return dev
 
 
-def build_runtime(model_dir: Union[str, Path], engine_config: Optional[EngineConfig] = None) -> Runtime:
+def build_runtime(model_dir: Union[str, Path, None], engine_config: Optional[EngineConfig] = None, *,
+                  config_dict: Optional[dict] = None, weights_seed: Optional[int] = None) -> Runtime:
+    """Builds a runtime from a model folder, or (``model_dir=None``) from a ``config.json`` mapping with
+    random weights drawn on the device from ``weights_seed`` (for benchmarks of real sizes, where writing
+    and reading gigabytes of random numbers would only cost time)."""
     engine_config = engine_config or EngineConfig()
     engine_config.validate()
     device = require_device(engine_config.device)
@@ -55,11 +60,18 @@ def build_runtime(model_dir: Union[str, Path], engine_config: Optional[EngineCon
     kernels.library()          # build or load the CUDA library now; fail here if that is impossible
     dtype = _DTYPES[engine_config.dtype]
 
-    architecture, config = load_model_config(model_dir)
+    if model_dir is not None:
+        architecture, config = load_model_config(model_dir)
+    else:
+        architecture = resolve_architecture(config_dict)
+        config = architecture.config_class.from_dict(config_dict)
     spec = architecture.build_spec(config)
     model = DecoderModel(spec, dtype, device)
-    tied = [(name, spec.embedding_name) for name in spec.optional_names] if spec.output_name is None else []
-    tensors, report = load_tensors(model_dir, model.param_specs(), dtype, device, spec.optional_names, tied)
+    if model_dir is not None:
+        tied = [(name, spec.embedding_name) for name in spec.optional_names] if spec.output_name is None else []
+        tensors, report = load_tensors(model_dir, model.param_specs(), dtype, device, spec.optional_names, tied)
+    else:
+        tensors, report = random_tensors_on_device(model.param_specs(), weights_seed or 0, dtype, device), None
     model.load(tensors)
     del tensors
 
@@ -75,9 +87,11 @@ def build_runtime(model_dir: Union[str, Path], engine_config: Optional[EngineCon
         by_need = engine_config.max_num_seqs * ((max_model_len + page_size - 1) // page_size)
         num_pages = max(1, min(by_memory, by_need))
     storage = CacheStorage(model.cache_groups, page_size, num_pages, engine_config.max_num_seqs, dtype, device)
-    namespace = f"{Path(model_dir).resolve()};{engine_config.dtype};page={page_size}"
+    origin = Path(model_dir).resolve() if model_dir is not None else f"random:{weights_seed}"
+    namespace = f"{origin};{engine_config.dtype};page={page_size}"
     manager = CacheManager(model.cache_groups, page_size, num_pages, engine_config.max_num_seqs,
                            engine_config.enable_prefix_cache, engine_config.prefix_cache_max_entries, namespace)
-    step_function = StepFunction(model, storage, manager, max_model_len)
+    step_function = StepFunction(model, storage, manager, max_model_len,
+                                 use_graphs=engine_config.decode_execution == "cuda_graph")
     resolved = replace(engine_config, max_model_len=max_model_len, num_kv_blocks=num_pages)
     return Runtime(config, resolved, model, storage, manager, step_function, max_model_len, report)

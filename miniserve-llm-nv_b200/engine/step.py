@@ -16,6 +16,7 @@ from typing import Optional, Sequence
 
 import torch
 
+from .. import kernels
 from ..cache.manager import RELEASED, CacheManager, StepReservation
 from ..parts.context import StepContext
 
@@ -29,13 +30,98 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)
 
 
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+class DecodeGraph:
+    """One captured decode step for exactly ``rows`` rows, with fixed device buffers.
+
+    Mechanics of miniserve/engine/graph.py:645-823: the index arrays live in one static buffer
+    that a replay overwrites with a single copy; rows beyond the live ones are padding that reads
+    and writes only the pool's scratch page; positions feed the rotation inside the graph, so
+    nothing about a position is baked in; the pools never move.  Unlike there, every batch size
+    up to the largest bucket replays a graph (the next bucket up, padded).
+    """
+
+    def __init__(self, step_function: "StepFunction", rows: int) -> None:
+        sf = step_function
+        self.rows = rows
+        manager, storage = sf.manager, sf.storage
+        ps = self.page_size = manager.page_size
+        self.width = (sf.max_model_len + ps - 1) // ps
+        n_groups = len(manager.paged_needs)
+        # layout: tokens, positions, request_of_token, query_start, context_lens, state_slots, logit_rows,
+        #         draw_index, then per group (block_tables, slots)
+        sizes = [rows, rows, rows, rows + 1, rows, rows, rows, rows] + [rows * self.width, rows] * n_groups
+        self.offsets = [0]
+        for size in sizes:
+            self.offsets.append(self.offsets[-1] + size)
+        self.host = torch.empty(self.offsets[-1], dtype=torch.int32, pin_memory=True)
+        self.meta = torch.zeros(self.offsets[-1], dtype=torch.int32, device=sf.device)
+        self.n_groups = n_groups
+        self.scratch = storage.scratch_page
+        self._fill_padding(0)
+        self.meta.copy_(self.host)
+        views = [self.meta[self.offsets[i]:self.offsets[i + 1]] for i in range(len(sizes))]
+        group_views = [(views[8 + 2 * g].view(rows, self.width), views[9 + 2 * g]) for g in range(n_groups)]
+        self.ctx_args = dict(
+            n_tokens=rows, n_requests=rows, token_ids=views[0], positions=views[1], request_of_token=views[2],
+            query_start=views[3], context_lens=views[4], state_slots=views[5], logit_rows=views[6],
+            max_query_len=1, max_context_len=sf.max_model_len, dtype=sf.model.dtype, device=sf.device,
+            group_views=group_views)
+        self.draw_index = views[7]
+        self.tokens_out = torch.zeros(rows, dtype=torch.int32, device=sf.device)
+        self.logits: Optional[torch.Tensor] = None
+        self.graph = torch.cuda.CUDAGraph()
+        self.kernel_launches = 0
+
+        def body() -> torch.Tensor:
+            ctx = StepContext(**self.ctx_args)
+            logits = sf.model.forward(ctx, storage)
+            kernels.sample(logits, storage.sampling_records, ctx.state_slots, self.draw_index, self.tokens_out)
+            return logits
+
+        side = torch.cuda.Stream(device=sf.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            body()                       # warm-up outside the capture (lazy library set-up happens here)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        before = kernels.launch_count
+        with torch.cuda.graph(self.graph, pool=sf.graph_pool):
+            self.logits = body()
+        self.kernel_launches = kernels.launch_count - before
+
+    def _fill_padding(self, first_row: int) -> None:
+        """Rows from ``first_row`` on become padding: token 0 at position 0 on the scratch page."""
+        o, rows, host = self.offsets, self.rows, self.host
+        ps = self.page_size
+        host[o[0] + first_row:o[1]] = 0
+        host[o[1] + first_row:o[2]] = 0
+        host[o[2]:o[3]] = torch.arange(rows, dtype=torch.int32)
+        host[o[3]:o[4]] = torch.arange(rows + 1, dtype=torch.int32)
+        host[o[4] + first_row:o[5]] = 1
+        host[o[5] + first_row:o[6]] = 0
+        host[o[6]:o[7]] = torch.arange(rows, dtype=torch.int32)
+        host[o[7] + first_row:o[8]] = 0
+        for g in range(self.n_groups):
+            tables = host[o[8 + 2 * g]:o[9 + 2 * g]].view(rows, self.width)
+            tables[first_row:] = self.scratch
+            host[o[9 + 2 * g] + first_row:o[10 + 2 * g]] = self.scratch * ps
+
+
 class StepFunction:
-    def __init__(self, model, storage, manager: CacheManager, max_model_len: int) -> None:
+    def __init__(self, model, storage, manager: CacheManager, max_model_len: int, use_graphs: bool = False) -> None:
         self.model, self.storage, self.manager = model, storage, manager
         self.max_model_len = max_model_len
         self.device = model.device
         self.vocab_size = model.spec.vocab_size
-        self.launches = 0            # steps run (for the bench's bookkeeping)
+        self.use_graphs = use_graphs
+        self.graphs: dict[int, DecodeGraph] = {}
+        self.graph_pool = None
+        self.graph_replays = 0
+        self.eager_steps = 0
+        self.last_tokens: Optional[torch.Tensor] = None   # tokens sampled inside the last replayed graph
 
     # ------------------------------------------------------------------ batch building
     def build_context(self, entries: Sequence[StepEntry], reservation: StepReservation) -> StepContext:
@@ -119,8 +205,67 @@ class StepFunction:
             group_views=group_views)
 
     # ------------------------------------------------------------------ running
-    def run(self, entries: Sequence[StepEntry], reservation: StepReservation) -> torch.Tensor:
-        """float32 logits ``[number of wanted positions, vocab]`` on the device, in entry order."""
+    def run(self, entries: Sequence[StepEntry], reservation: StepReservation,
+            draw_index: Optional[Sequence[int]] = None) -> torch.Tensor:
+        """float32 logits ``[number of wanted positions, vocab]`` on the device, in entry order.
+
+        A step of single tokens whose logits are all wanted replays a captured graph when graphs
+        are on; the graph also samples, and ``last_tokens`` then holds one token per entry
+        (``draw_index``: each request's draw count, for its random stream).
+        """
+        self.last_tokens = None
+        if (self.use_graphs and entries and len(entries) <= DECODE_BUCKETS[-1]
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)):
+            return self._replay(entries, reservation, draw_index)
         ctx = self.build_context(entries, reservation)
-        self.launches += 1
+        self.eager_steps += 1
         return self.model.forward(ctx, self.storage)
+
+    def _replay(self, entries, reservation, draw_index) -> torch.Tensor:
+        n = len(entries)
+        rows = next(b for b in DECODE_BUCKETS if b >= n)
+        graph = self.graphs.get(rows)
+        if graph is None:
+            if self.graph_pool is None:
+                self.graph_pool = torch.cuda.graph_pool_handle()
+            graph = self.graphs[rows] = DecodeGraph(self, rows)
+        manager, ps = self.manager, self.manager.page_size
+        limit, scratch = self.storage.num_pages, self.storage.scratch_page
+        o, host = graph.offsets, graph.host
+        graph._fill_padding(n)
+        tokens, positions, lens, slots_state, draws = [], [], [], [], []
+        for row, (entry, item) in enumerate(zip(entries, reservation.items)):
+            token = int(entry.tokens[0])
+            if entry.request_id != item.request_id or item.end - item.start != 1:
+                raise ValueError(f"entry {row} does not match its reservation")
+            if not 0 <= token < self.vocab_size:
+                raise ValueError(f"token id {token} outside the vocabulary of {self.vocab_size}")
+            if item.end > self.max_model_len:
+                raise ValueError(f"request {entry.request_id!r} would reach {item.end} tokens; the limit is {self.max_model_len}")
+            tokens.append(token)
+            positions.append(item.start)
+            lens.append(item.end)
+            slots_state.append(manager.requests[entry.request_id].slot)
+            draws.append(0 if draw_index is None else int(draw_index[row]))
+            for g in range(graph.n_groups):
+                table = item.tables[g]
+                if len(table) > graph.width or any(p != RELEASED and not 0 <= p < limit for p in table):
+                    raise ValueError("a block table does not fit the pool")
+                slot = item.slots[g][0]
+                if not 0 <= slot < limit * ps:
+                    raise ValueError(f"slot {slot} outside the pool")
+                base = o[8 + 2 * g] + row * graph.width
+                host[base:base + len(table)] = torch.tensor([scratch if p == RELEASED else p for p in table],
+                                                            dtype=torch.int32)
+                host[base + len(table):base + graph.width] = scratch
+                host[o[9 + 2 * g] + row] = slot
+        host[o[0]:o[0] + n] = torch.tensor(tokens, dtype=torch.int32)
+        host[o[1]:o[1] + n] = torch.tensor(positions, dtype=torch.int32)
+        host[o[4]:o[4] + n] = torch.tensor(lens, dtype=torch.int32)
+        host[o[5]:o[5] + n] = torch.tensor(slots_state, dtype=torch.int32)
+        host[o[7]:o[7] + n] = torch.tensor(draws, dtype=torch.int32)
+        graph.meta.copy_(host, non_blocking=True)
+        graph.graph.replay()
+        self.graph_replays += 1
+        self.last_tokens = graph.tokens_out[:n]
+        return graph.logits[:n]

@@ -39,9 +39,14 @@ def library() -> ctypes.CDLL:
     return _library
 
 
+launch_count = 0   # entry points of this library called so far (each launches one kernel, or a fixed few)
+
+
 def _check(code: int) -> None:
+    global launch_count
     if code != 0:
         raise KernelError(library().ms_last_error().decode())
+    launch_count += 1
 
 
 def _stream() -> ctypes.c_void_p:

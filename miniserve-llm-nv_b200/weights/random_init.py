@@ -39,6 +39,21 @@ def random_tensors(config_dict: Mapping[str, Any], seed: int, stored_dtype: str 
     return tensors
 
 
+def random_tensors_on_device(specs, seed: int, dtype: torch.dtype, device, matrix_std: float = 0.02,
+                             vector_std: float = 0.1) -> dict[str, torch.Tensor]:
+    """The same distributions drawn with the device's generator (another stream than the CPU's)."""
+    generator = torch.Generator(device=device).manual_seed(int(seed))
+    tensors: dict[str, torch.Tensor] = {}
+    for spec in specs:
+        if spec.kind == "table":
+            tensors[spec.name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
+            continue
+        value = torch.randn(spec.shape, generator=generator, device=device, dtype=torch.float32)
+        value = 1.0 + value * vector_std if spec.kind == "vector" else value * matrix_std
+        tensors[spec.name] = value.to(dtype)
+    return tensors
+
+
 def write_random_model(folder: Union[str, Path], config_dict: Mapping[str, Any], seed: int,
                        stored_dtype: str = "bfloat16", matrix_std: float = 0.02) -> Path:
     """Creates ``folder`` with ``config.json`` and ``model.safetensors`` for the configuration."""

@@ -26,7 +26,7 @@ def cpu_runtime(monkeypatch, tmp_path):
         folder = helpers.make_folder(tmp_path, name, seed=1)
         runtime = runtime_module.build_runtime(folder, EngineConfig(
             dtype=dtype, kv_block_size=page_size, num_kv_blocks=num_pages, max_num_seqs=4,
-            enable_prefix_cache=False, device="cpu"))
+            enable_prefix_cache=False, device="cpu", decode_execution="eager"))
         return folder, runtime
     return build
 
