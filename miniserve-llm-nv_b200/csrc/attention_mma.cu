@@ -1,0 +1,384 @@
+// Paged grouped-query attention on the tensor cores (bfloat16 operands, float32 scores,
+// softmax and accumulation), for prompt portions and decoded tokens alike.
+//
+// Work unit: one (request, key/value head, tile of query rows, split of the keys).  The
+// query rows of a request and kv head are the pairs (token, query head of that kv head's
+// group), token-major, so the G query heads that share a kv head sit in the same tile and
+// every key/value tile read from the pool serves all of them.  A thread block has W warps
+// of 16 rows each; key/value tiles of BN keys are gathered from the pages with 16-byte
+// asynchronous copies into shared memory (double-buffered), then
+//   S = Q K^T      mma.m16n8k16, K fragments by ldmatrix
+//   online softmax (running maximum and sum per row, exp2 with the scale folded in)
+//   O += P V       P re-used from the S accumulators as bf16, V fragments by ldmatrix.trans
+// A key is visible to a row iff  pos - window < key <= pos  (pos: the row's token position).
+// With one split the normalised result is written as bfloat16; with more, each split writes
+// its normalised float32 partial result and log-sum-exp to scratch and a second kernel
+// merges them.
+#include "common.cuh"
+
+namespace ms {
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // zero-fills the 16 bytes when not valid
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Shared-memory tiles are [rows][D] bfloat16 with the 16-byte chunks of a row XOR-swizzled by
+// the row index, so that ldmatrix reads eight rows without bank conflicts.
+// A row of D elements has D / 8 chunks; the XOR mask never leaves the row: rows of 128 bytes or
+// more use the low three row bits, 64-byte rows (D = 32) the row bits 1..2, so that in both cases
+// eight consecutive rows land in eight different 16-byte bank groups.
+template <int D> __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row, int chunk) {
+  static_assert(D % 32 == 0, "head size must be a multiple of 32 for this kernel");
+  constexpr int CHUNKS = D / 8;
+  const int mask = CHUNKS >= 8 ? (row & 7) : ((row >> 1) & (CHUNKS - 1));
+  return base + row * D + ((chunk ^ mask) << 3);
+}
+
+template <int D, int W, int BN>
+__global__ void __launch_bounds__(W * 32)
+attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
+                     const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_tables, int table_stride,
+                     const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
+                     int n_kv, float scale_log2, int window, __nv_bfloat16* __restrict__ out,
+                     float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits) {
+  constexpr int BM = 16 * W, THREADS = 32 * W, CHUNKS = D / 8;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][D]
+  __nv_bfloat16* k_s = q_s + BM * D;                                        // [2][BN][D]
+  __nv_bfloat16* v_s = k_s + 2 * BN * D;                                    // [2][BN][D]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kv_head = blockIdx.y;
+  const int request = blockIdx.z / num_splits, split = blockIdx.z % num_splits;
+  const int group = n_q / n_kv;
+  const int q0 = query_start[request];
+  const int q_len = query_start[request + 1] - q0;
+  const int ctx = context_lens[request];
+  const int rows_total = q_len * group;
+  const int row0 = blockIdx.x * BM;
+  if (row0 >= rows_total) return;
+  const int first_pos = ctx - q_len;                     // position of the request's first query token
+  const int t_lo = row0 / group;
+  const int last_row = min(rows_total, row0 + BM) - 1;
+  const int t_hi = last_row / group;
+  int key_begin = 0;
+  if (window > 0) key_begin = max(0, first_pos + t_lo - window + 1);
+  const int key_end = first_pos + t_hi + 1;
+  const int tile_begin = (key_begin / BN) * BN;
+  const int n_tiles = (key_end - tile_begin + BN - 1) / BN;
+  const int tiles_per_split = (n_tiles + num_splits - 1) / num_splits;
+  const int tile_lo = split * tiles_per_split;
+  const int tile_hi = min(n_tiles, tile_lo + tiles_per_split);
+  const int* table = block_tables + (size_t)request * table_stride;
+
+  // rows of this thread in the mma layout: r_a (lane / 4) and r_a + 8 of the warp's 16 rows
+  const int quad_row = lane >> 2, quad_col = lane & 3;
+  const int row_a = row0 + warp * 16 + quad_row, row_b = row_a + 8;
+
+  if (tile_lo >= tile_hi) {                               // nothing to do for this split
+    if (num_splits > 1 && quad_col == 0) {
+      for (int which = 0; which < 2; ++which) {
+        const int row = which ? row_b : row_a;
+        if (row < rows_total) {
+          const size_t index = ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group);
+          part_lse[index * num_splits + split] = -INFINITY;
+        }
+      }
+    }
+    return;
+  }
+
+  // ---- Q tile to shared memory, then to registers as A fragments
+  for (int i = tid; i < BM * CHUNKS; i += THREADS) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int row = row0 + r;
+    const bool valid = row < rows_total;
+    const __nv_bfloat16* src = q;
+    if (valid) src = q + ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group) * D + c * 8;
+    cp_async_16(tile_ptr<D>(q_s, r, c), src, valid);
+  }
+  cp_async_commit();
+
+  auto load_tile = [&](int tile, int stage) {
+    const int key0 = tile_begin + tile * BN;
+    __nv_bfloat16* ks = k_s + stage * BN * D;
+    __nv_bfloat16* vs = v_s + stage * BN * D;
+    for (int i = tid; i < BN * CHUNKS; i += THREADS) {
+      const int r = i / CHUNKS, c = i % CHUNKS;
+      const int key = key0 + r;
+      const bool valid = key < key_end;
+      size_t offset = 0;
+      if (valid) {
+        const int page = table[key / page_size];
+        offset = (((size_t)page * n_kv + kv_head) * page_size + key % page_size) * D + c * 8;
+      }
+      cp_async_16(tile_ptr<D>(ks, r, c), k_pool + offset, valid);
+      cp_async_16(tile_ptr<D>(vs, r, c), v_pool + offset, valid);
+    }
+  };
+
+  load_tile(tile_lo, 0);
+  cp_async_commit();
+  cp_async_wait<1>();            // Q has landed
+  __syncthreads();
+
+  unsigned q_frag[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int c = kk * 2 + (lane >> 4);
+    ldmatrix_x4(q_frag[kk], tile_ptr<D>(q_s, r, c));
+  }
+
+  float acc_o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc_o[n][e] = 0.f;
+  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+  const int pos_a = first_pos + row_a / group, pos_b = first_pos + row_b / group;
+
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int stage = (tile - tile_lo) & 1;
+    if (tile + 1 < tile_hi) load_tile(tile + 1, stage ^ 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const __nv_bfloat16* ks = k_s + stage * BN * D;
+    const __nv_bfloat16* vs = v_s + stage * BN * D;
+    const int key0 = tile_begin + tile * BN;
+
+    // ---- S = Q K^T
+    float acc_s[BN / 8][4];
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc_s[n][e] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int np = 0; np < BN / 16; ++np) {
+        unsigned b[4];
+        const int r = np * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int c = kk * 2 + ((lane >> 3) & 1);
+        ldmatrix_x4(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(ks), r, c));
+        mma_bf16(acc_s[2 * np], q_frag[kk], b[0], b[1]);
+        mma_bf16(acc_s[2 * np + 1], q_frag[kk], b[2], b[3]);
+      }
+    }
+
+    // ---- mask and online softmax (scores are scaled inside the exponent)
+    const bool full = (key0 + BN - 1 <= first_pos + t_lo) && (window <= 0 || key0 >= first_pos + t_hi - window + 1);
+    float max_a = -INFINITY, max_b = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (!full) {
+          const int key = key0 + n * 8 + quad_col * 2 + (e & 1);
+          const int pos = (e < 2) ? pos_a : pos_b;
+          const bool visible = key <= pos && (window <= 0 || key > pos - window);
+          if (!visible) acc_s[n][e] = -INFINITY;
+        }
+        if (e < 2) max_a = fmaxf(max_a, acc_s[n][e]); else max_b = fmaxf(max_b, acc_s[n][e]);
+      }
+    }
+    max_a = fmaxf(max_a, __shfl_xor_sync(0xffffffffu, max_a, 1));
+    max_a = fmaxf(max_a, __shfl_xor_sync(0xffffffffu, max_a, 2));
+    max_b = fmaxf(max_b, __shfl_xor_sync(0xffffffffu, max_b, 1));
+    max_b = fmaxf(max_b, __shfl_xor_sync(0xffffffffu, max_b, 2));
+    const float new_a = fmaxf(m_a, max_a), new_b = fmaxf(m_b, max_b);
+    const float base_a = new_a == -INFINITY ? 0.f : new_a * scale_log2;
+    const float base_b = new_b == -INFINITY ? 0.f : new_b * scale_log2;
+    const float corr_a = exp2f(m_a * scale_log2 - base_a);      // m == -inf gives 0
+    const float corr_b = exp2f(m_b * scale_log2 - base_b);
+    m_a = new_a;
+    m_b = new_b;
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int n = 0; n < BN / 8; ++n) {
+      acc_s[n][0] = exp2f(acc_s[n][0] * scale_log2 - base_a);
+      acc_s[n][1] = exp2f(acc_s[n][1] * scale_log2 - base_a);
+      acc_s[n][2] = exp2f(acc_s[n][2] * scale_log2 - base_b);
+      acc_s[n][3] = exp2f(acc_s[n][3] * scale_log2 - base_b);
+      sum_a += acc_s[n][0] + acc_s[n][1];
+      sum_b += acc_s[n][2] + acc_s[n][3];
+    }
+    l_a = l_a * corr_a + sum_a;
+    l_b = l_b * corr_b + sum_b;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      acc_o[n][0] *= corr_a;
+      acc_o[n][1] *= corr_a;
+      acc_o[n][2] *= corr_b;
+      acc_o[n][3] *= corr_b;
+    }
+
+    // ---- O += P V
+#pragma unroll
+    for (int kp = 0; kp < BN / 16; ++kp) {
+      unsigned p[4];
+      p[0] = pack_bf16(acc_s[2 * kp][0], acc_s[2 * kp][1]);
+      p[1] = pack_bf16(acc_s[2 * kp][2], acc_s[2 * kp][3]);
+      p[2] = pack_bf16(acc_s[2 * kp + 1][0], acc_s[2 * kp + 1][1]);
+      p[3] = pack_bf16(acc_s[2 * kp + 1][2], acc_s[2 * kp + 1][3]);
+#pragma unroll
+      for (int np = 0; np < D / 16; ++np) {
+        unsigned b[4];
+        const int r = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = np * 2 + (lane >> 4);
+        ldmatrix_x4_trans(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(vs), r, c));
+        mma_bf16(acc_o[2 * np], p, b[0], b[1]);
+        mma_bf16(acc_o[2 * np + 1], p, b[2], b[3]);
+      }
+    }
+    __syncthreads();       // all warps are done with this stage before it is refilled
+  }
+  cp_async_wait<0>();
+
+  // ---- finish: row sums across the quad, normalise, store
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    const int row = which ? row_b : row_a;
+    if (row >= rows_total) continue;
+    const float l = which ? l_b : l_a;
+    const float m = which ? m_b : m_a;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    const size_t index = (size_t)(q0 + row / group) * n_q + kv_head * group + row % group;
+    if (num_splits == 1) {
+      __nv_bfloat16* dst = out + index * D;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        const unsigned packed = pack_bf16(acc_o[n][2 * which] * inv, acc_o[n][2 * which + 1] * inv);
+        *reinterpret_cast<unsigned*>(dst + n * 8 + quad_col * 2) = packed;
+      }
+    } else {
+      float* dst = part_o + (index * num_splits + split) * D;
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n)
+        *reinterpret_cast<float2*>(dst + n * 8 + quad_col * 2) =
+            make_float2(acc_o[n][2 * which] * inv, acc_o[n][2 * which + 1] * inv);
+      if (quad_col == 0) part_lse[index * num_splits + split] = l > 0.f ? m * scale_log2 + log2f(l) : -INFINITY;
+    }
+  }
+}
+
+// Merges the splits of one (token, head): out = sum_s w_s O_s / sum_s w_s with w_s = 2^(lse_s - max lse).
+template <int D>
+__global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                         __nv_bfloat16* __restrict__ out, int num_splits, int n_items) {
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= n_items) return;
+  const float* lse = part_lse + (size_t)item * num_splits;
+  float m = -INFINITY;
+  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, lse[s]);
+  float acc[D / 32] = {};
+  float total = 0.f;
+  for (int s = 0; s < num_splits; ++s) {
+    const float v = lse[s];
+    if (v == -INFINITY) continue;
+    const float w = exp2f(v - m);
+    total += w;
+    const float* src = part_o + ((size_t)item * num_splits + s) * D;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] += w * src[lane + 32 * i];
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) out[(size_t)item * D + lane + 32 * i] = __float2bfloat16_rn(acc[i] * inv);
+}
+
+template <int D, int W, int BN>
+int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
+                         int table_stride, const int* query_start, const int* context_lens, int page_size, int n_q,
+                         int n_kv, float scale, int window, void* out, float* part_o, float* part_lse, int num_splits,
+                         int n_requests, int max_query_len, int n_tokens, cudaStream_t stream) {
+  constexpr int BM = 16 * W;
+  const size_t smem = (size_t)(BM + 4 * BN) * D * sizeof(__nv_bfloat16);
+  auto kernel = attention_mma_kernel<D, W, BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) MS_FAIL("attention: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  const int group = n_q / n_kv;
+  const long long tiles = ((long long)max_query_len * group + BM - 1) / BM;
+  MS_REQUIRE(tiles <= 2147483647LL && (long long)n_requests * num_splits <= 65535 && n_kv <= 65535,
+             "attention: grid %lld x %d x %lld exceeds the launch limits", tiles, n_kv, (long long)n_requests * num_splits);
+  dim3 grid((unsigned)tiles, n_kv, n_requests * num_splits);
+  const float scale_log2 = scale * 1.4426950408889634f;
+  kernel<<<grid, W * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+                                         (const __nv_bfloat16*)v_pool, block_tables, table_stride, query_start,
+                                         context_lens, page_size, n_q, n_kv, scale_log2, window, (__nv_bfloat16*)out,
+                                         part_o, part_lse, num_splits);
+  MS_CHECK_LAUNCH("attention_mma");
+  if (num_splits > 1) {
+    const int items = n_tokens * n_q;
+    attention_combine_kernel<D><<<(items + 3) / 4, 128, 0, stream>>>(part_o, part_lse, (__nv_bfloat16*)out,
+                                                                     num_splits, items);
+    MS_CHECK_LAUNCH("attention_combine");
+  }
+  return 0;
+}
+
+}  // namespace ms
+
+using namespace ms;
+
+// Head sizes this kernel is built for; other sizes use the general kernel.
+MS_EXPORT int ms_attention_mma_supports(int head_dim) { return head_dim == 32 || head_dim == 64 || head_dim == 128; }
+
+// q, out [n_tokens, n_q, d] bfloat16; pools of one layer [pages, n_kv, page_size, d]; block_tables
+// [n_requests, table_stride]; query_start [n_requests + 1]; context_lens [n_requests] (lengths after
+// this step's tokens).  Request r's tokens query_start[r] .. query_start[r+1] are the last ones of its
+// context.  num_splits > 1 needs part_o [n_tokens * n_q * num_splits * d] and part_lse
+// [n_tokens * n_q * num_splits] float32 scratch and is meant for steps of single tokens.
+MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
+                                     int table_stride, const int* query_start, const int* context_lens,
+                                     int page_size, int n_q, int n_kv, int d, float scale, int window, void* out,
+                                     float* part_o, float* part_lse, int num_splits, int n_requests,
+                                     int max_query_len, int n_tokens, cudaStream_t stream) {
+  if (n_tokens == 0 || n_requests == 0) return 0;
+  MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d query heads are not a multiple of %d key/value heads", n_q, n_kv);
+  MS_REQUIRE(page_size > 0 && max_query_len > 0, "attention: page size %d, longest portion %d", page_size, max_query_len);
+  MS_REQUIRE(num_splits >= 1 && (num_splits == 1 || (part_o && part_lse)), "attention: %d splits need scratch", num_splits);
+  const bool small = (long long)max_query_len * (n_q / n_kv) <= 16;
+#define MS_ATTENTION_CASE(D, W, BN)                                                                                   \
+  return launch_attention_mma<D, W, BN>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens,    \
+                                        page_size, n_q, n_kv, scale, window, out, part_o, part_lse, num_splits,      \
+                                        n_requests, max_query_len, n_tokens, stream)
+  if (d == 128) { if (small) { MS_ATTENTION_CASE(128, 1, 32); } else { MS_ATTENTION_CASE(128, 4, 64); } }
+  if (d == 64) { if (small) { MS_ATTENTION_CASE(64, 1, 64); } else { MS_ATTENTION_CASE(64, 4, 64); } }
+  if (d == 32) { if (small) { MS_ATTENTION_CASE(32, 1, 64); } else { MS_ATTENTION_CASE(32, 4, 64); } }
+#undef MS_ATTENTION_CASE
+  MS_FAIL("attention: the tensor-core kernel is not built for head size %d", d);
+}

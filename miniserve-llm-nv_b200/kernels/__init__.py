@@ -182,14 +182,28 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 # --------------------------------------------------------------------------- attention
 
 
+def attention_splits(n_requests: int, n_kv: int, max_query_len: int, max_context_len: int) -> int:
+    """In how many parts a decode step's keys are split so that the work fills the GPU's 148 SMs."""
+    if max_query_len != 1:
+        return 1
+    by_occupancy = -(-4 * 148 // max(n_requests * n_kv, 1))
+    by_length = max(max_context_len // 128, 1)
+    return max(1, min(by_occupancy, by_length, 32))
+
+
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
-                    request_of_token: torch.Tensor, positions: torch.Tensor, scale: float, window: Optional[int],
-                    out: torch.Tensor) -> None:
+                    request_of_token: torch.Tensor, positions: torch.Tensor, query_start: torch.Tensor,
+                    context_lens: torch.Tensor, max_query_len: int, max_context_len: int, scale: float,
+                    window: Optional[int], out: torch.Tensor) -> None:
     """Causal grouped-query attention of every token over its request's paged keys and values.
 
     q, out ``[N, n_q, d]``; pools of one layer ``[pages, n_kv, page_size, d]``; block_tables
-    int32 ``[R, width]``; request_of_token, positions int32 ``[N]``.  A token at position p sees
-    keys ``max(0, p - window + 1) .. p`` of its own request, which must be in the pool already.
+    int32 ``[R, width]``; request_of_token, positions int32 ``[N]``; query_start ``[R + 1]`` and
+    context_lens ``[R]`` describe the same batch per request (a request's tokens are the last
+    ones of its context).  A token at position p sees keys ``max(0, p - window + 1) .. p`` of
+    its own request, which must be in the pool already.  bfloat16 with a head size the
+    tensor-core kernel is built for runs there (``max_query_len``/``max_context_len`` are upper
+    bounds used to shape its grid); everything else runs the general float32-arithmetic kernel.
     """
     n, n_q, head_dim = q.shape
     _want(q, "q")
@@ -201,7 +215,24 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     _want(block_tables, "block_tables", torch.int32)
     _want(request_of_token, "request_of_token", torch.int32, (n,))
     _want(positions, "positions", torch.int32, (n,))
-    _check(library().ms_paged_attention_generic(
+    n_requests = context_lens.numel()
+    _want(query_start, "query_start", torch.int32, (n_requests + 1,))
+    _want(context_lens, "context_lens", torch.int32, (n_requests,))
+    lib = library()
+    if q.dtype == torch.bfloat16 and lib.ms_attention_mma_supports(_i(head_dim)):
+        n_kv = k_pool.shape[1]
+        splits = attention_splits(n_requests, n_kv, max_query_len, max_context_len)
+        part_o = part_lse = None
+        if splits > 1:
+            part_o = torch.empty((n * n_q * splits, head_dim), dtype=torch.float32, device=q.device)
+            part_lse = torch.empty((n * n_q * splits,), dtype=torch.float32, device=q.device)
+        _check(lib.ms_paged_attention_mma(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]), _ptr(query_start),
+            _ptr(context_lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
+            _i(window if window else 0), _ptr(out), _ptr(part_o), _ptr(part_lse), _i(splits), _i(n_requests),
+            _i(max_query_len), _i(n), _stream()))
+        return
+    _check(lib.ms_paged_attention_generic(
         _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
         _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(k_pool.shape[1]), _i(head_dim),
         _f(scale), _i(window if window else 0), _ptr(out), _i(n), _stream()))

@@ -23,7 +23,12 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
               num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1, head_dim=48, vocab_size=331,
               max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=50000.0, attention_dropout=0.0,
               hidden_act="silu", attention_bias=False, tie_word_embeddings=True)
-TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C}
+# A fourth with the head size of real checkpoints' smaller siblings (64), four query heads per kv head.
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=128, intermediate_size=192,
+              num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=500,
+              max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_dropout=0.0,
+              hidden_act="silu", attention_bias=False, tie_word_embeddings=False)
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D}
 
 
 def make_folder(tmp_path: Path, name: str, seed: int = 0, stored_dtype: str = "bfloat16", matrix_std: float = 0.05) -> Path:

@@ -158,44 +158,68 @@ def _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, seed):
         cursor += need
     k_pool = rand((total, n_kv, page_size, d), dtype, seed + 1)
     v_pool = rand((total, n_kv, page_size, d), dtype, seed + 2)
-    request_of_token, positions = [], []
+    request_of_token, positions, query_start = [], [], [0]
     for r, (length, q_len) in enumerate(zip(lengths, query_lens)):
         request_of_token += [r] * q_len
         positions += list(range(length - q_len, length))
+        query_start.append(len(positions))
     n = len(positions)
     q = rand((n, n_q, d), dtype, seed + 3)
-    return (q, k_pool, v_pool, torch.tensor(tables, dtype=torch.int32).cuda(),
-            torch.tensor(request_of_token, dtype=torch.int32).cuda(), torch.tensor(positions, dtype=torch.int32).cuda())
+    as_int = lambda values: torch.tensor(values, dtype=torch.int32).cuda()
+    return (q, k_pool, v_pool, as_int(tables), as_int(request_of_token), as_int(positions), as_int(query_start),
+            as_int(lengths), max(query_lens), max(lengths))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def _check_attention(kernels, dtype, case, d, window):
+    q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = case
+    out = torch.empty_like(q)
+    kernels.paged_attention(q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                            max_ctx, d ** -0.5, window, out)
+    expected = torch.empty(q.shape, dtype=torch.float64).cuda()
+    plain_ops.paged_attention(q.cpu(), k_pool.cpu(), v_pool.cpu(), tables.cpu(), request_of_token.cpu(), positions.cpu(),
+                              query_start.cpu(), context_lens.cpu(), max_q, max_ctx, d ** -0.5, window, expected)
+    assert torch.allclose(out.double(), expected, **tol(dtype)), float((out.double() - expected).abs().max())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_q,n_kv,d,page_size,window", [
     (4, 2, 16, 16, None), (6, 2, 32, 8, None), (3, 1, 48, 4, None), (5, 5, 64, 1, None), (8, 1, 128, 64, None),
-    (2, 2, 256, 16, None), (4, 2, 80, 5, 7), (6, 3, 96, 16, 33), (4, 1, 112, 32, 1)])
+    (2, 2, 256, 16, None), (4, 2, 80, 5, 7), (6, 3, 96, 16, 33), (4, 1, 112, 32, 1), (16, 8, 128, 16, None),
+    (6, 1, 64, 16, 50), (4, 2, 128, 3, 20), (40, 2, 32, 16, None)])
 def test_paged_attention(kernels, dtype, n_q, n_kv, d, page_size, window):
-    lengths, query_lens = [1, 37, 130, 64, 200], [1, 5, 1, 64, 2]
-    q, k_pool, v_pool, tables, request_of_token, positions = _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 20)
-    out = torch.empty_like(q)
-    kernels.paged_attention(q, k_pool, v_pool, tables, request_of_token, positions, d ** -0.5, window, out)
-    expected = torch.empty(q.shape, dtype=torch.float64).cuda()
-    plain_ops.paged_attention(q.cpu(), k_pool.cpu(), v_pool.cpu(), tables.cpu(), request_of_token.cpu(), positions.cpu(),
-                              d ** -0.5, window, expected)
-    assert torch.allclose(out.double(), expected, **tol(dtype))
+    """Portions of prompts (down to one token) beside each other: every kernel variant, shuffled pages."""
+    lengths, query_lens = [1, 37, 130, 64, 200, 333], [1, 5, 1, 64, 2, 333]
+    _check_attention(kernels, dtype, _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 20), d, window)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_paged_attention_finds_one_far_key(kernels, dtype):
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,window", [
+    (16, 8, 128, 16, None), (6, 2, 32, 8, None), (8, 1, 64, 5, None), (4, 4, 128, 64, 100), (48, 2, 64, 16, None)])
+def test_paged_attention_decode_steps(kernels, dtype, n_q, n_kv, d, page_size, window):
+    """Single tokens only, so that the keys are split over several thread blocks and merged."""
+    lengths = [1, 2, 31, 32, 33, 700, 1500]
+    _check_attention(kernels, dtype, _attention_case(dtype, n_q, n_kv, d, page_size, lengths, [1] * len(lengths), 21), d, window)
+    lengths = [2500]
+    _check_attention(kernels, dtype, _attention_case(dtype, n_q, n_kv, d, page_size, lengths, [1], 22), d, window)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("query_len", [3, 1])
+def test_paged_attention_finds_one_far_key(kernels, dtype, query_len):
     """One key among hundreds is made to dominate; the output must be (almost) its value row."""
     n_q, n_kv, d, page_size = 4, 2, 64, 16
-    lengths, query_lens = [700], [3]
-    q, k_pool, v_pool, tables, request_of_token, positions = _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 30)
+    lengths, query_lens = [700], [query_len]
+    q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = \
+        _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 30)
     for target in (0, 15, 16, 300, 696):
         kp = k_pool.clone()
         page, offset = int(tables[0, target // page_size]), target % page_size
         for head in range(n_kv):
             kp[page, head, offset] = (q[0, head * 2].float() * 40).to(dtype)
         out = torch.empty_like(q)
-        kernels.paged_attention(q, kp, v_pool, tables, request_of_token, positions, d ** -0.5, None, out)
+        kernels.paged_attention(q, kp, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                                max_ctx, d ** -0.5, None, out)
         for head in (0, 2):
             assert torch.allclose(out[0, head].float(), v_pool[page, head // 2, offset].float(), atol=2e-2), target
 

@@ -63,7 +63,7 @@ def error_bounds(dtype, expected):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4)])
+@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4), ("d", 16)])
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
 def test_cuttings_match_plain(tmp_path, dtype, name, page_size, cutting):
     vocab = helpers.TINY[name]["vocab_size"]
