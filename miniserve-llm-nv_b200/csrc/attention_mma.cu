@@ -382,3 +382,55 @@ MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const vo
 #undef MS_ATTENTION_CASE
   MS_FAIL("attention: the tensor-core kernel is not built for head size %d", d);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Split-key attention for callers that must not allocate (declared in attention_static.h).
+//
+// The split-key path above needs float32 scratch for the partial results of every split, which
+// its caller allocates.  This entry point keeps that scratch in a fixed array inside the library
+// instead, so a caller that cannot call cudaMalloc (a plug-in running inside another program's
+// memory pool, a real-time loop that may not block in the allocator, a process whose device memory
+// was handed out completely at start-up) can still run attention with its keys split.
+namespace ms {
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;   // 8 MiB per GPU that loads the library
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_ptr[kMaxDevices] = {};
+}  // namespace ms
+
+MS_EXPORT int ms_paged_attention_decode_static(const void* q, const void* k_pool, const void* v_pool,
+                                               const int* block_tables, int table_stride, const int* query_start,
+                                               const int* context_lens, int page_size, int n_q, int n_kv, int d,
+                                               float scale, int window, void* out, int num_splits, int n_requests,
+                                               int n_tokens, cudaStream_t stream) {
+  MS_REQUIRE(num_splits >= 1 && num_splits <= 64, "attention (static scratch): %d splits outside 1..64", num_splits);
+  MS_REQUIRE(ms_attention_mma_supports(d), "attention (static scratch): head size %d is not built (32, 64, 128 are)", d);
+  MS_REQUIRE(n_tokens == n_requests, "attention (static scratch): one token per request is expected (%d tokens, %d requests)",
+             n_tokens, n_requests);
+  const size_t rows = (size_t)n_tokens * (size_t)n_q * (size_t)num_splits;
+  const size_t needed = rows * (size_t)(d + 1);
+  MS_REQUIRE(needed <= kStaticScratchFloats,
+             "attention (static scratch): tokens %d x heads %d x splits %d x (head size %d + 1) = %zu floats exceed the "
+             "built-in scratch of %zu floats; use fewer splits or the entry point that takes scratch from its caller",
+             n_tokens, n_q, num_splits, d, needed, (size_t)kStaticScratchFloats);
+  int device = -1;
+  cudaError_t e = cudaGetDevice(&device);
+  MS_REQUIRE(e == cudaSuccess && device >= 0 && device < kMaxDevices, "attention (static scratch): no usable current device (%s)",
+             cudaGetErrorString(e));
+  if (g_static_scratch_ptr[device] == nullptr) {
+    // First call on this device: ask the runtime where this device keeps its copy of the array.  In host
+    // code the array's name is only a handle; passing it to a kernel would hand over a host address.
+    float* address = nullptr;
+    e = cudaGetSymbolAddress((void**)&address, g_static_scratch);
+    MS_REQUIRE(e == cudaSuccess && address != nullptr, "attention (static scratch): cudaGetSymbolAddress failed: %s",
+               cudaGetErrorString(e));
+    g_static_scratch_ptr[device] = address;
+  }
+  float* part_o = g_static_scratch_ptr[device];
+  float* part_lse = part_o + rows * (size_t)d;
+  // Nothing in the scratch has to start at zero: every split of every row writes its log-sum-exp (minus
+  // infinity when it had no keys), and a partial result is read only where that value is finite.
+  return ms_paged_attention_mma(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens, page_size,
+                                n_q, n_kv, d, scale, window, out, part_o, part_lse, num_splits, n_requests, 1, n_tokens,
+                                stream);
+}
