@@ -2,6 +2,7 @@
 // with RMSNorm, rotation tables, per-head norm + rotation + paged cache append, and
 // the gated activation.  All arithmetic is float32; storage is float32 or bfloat16.
 #include "common.cuh"
+#include "elementwise_vec.cuh"
 
 namespace ms {
 
@@ -203,6 +204,18 @@ MS_EXPORT int ms_add_rmsnorm(float* residual, const void* delta, int dtype, cons
                              const int* rows, void* out, int n_out, int hidden, float eps, cudaStream_t stream) {
   if (n_out == 0) return 0;
   MS_REQUIRE(hidden > 0, "add_rmsnorm: hidden size must be positive, got %d", hidden);
+  if (hidden % 8 == 0 && hidden <= 8192) {
+    const int groups = hidden / 8;
+    const int threads = groups >= 256 ? 256 : ((groups + 31) / 32) * 32;
+    const int chunks = (groups + threads - 1) / threads;
+#define MS_ADD_RMSNORM_VEC(C)                                                                                     \
+  MS_DISPATCH(dtype, (add_rmsnorm_vec_kernel<T, C><<<n_out, threads, 0, stream>>>(residual, (const T*)delta, weight, \
+                                                                               weight_dtype, rows, (T*)out, hidden, eps)))
+    if (chunks == 1) { MS_ADD_RMSNORM_VEC(1); } else if (chunks == 2) { MS_ADD_RMSNORM_VEC(2); } else { MS_ADD_RMSNORM_VEC(4); }
+#undef MS_ADD_RMSNORM_VEC
+    MS_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+  }
   const int threads = hidden >= 1024 ? 256 : 128;
   MS_DISPATCH(dtype, (add_rmsnorm_kernel<T><<<n_out, threads, 0, stream>>>(residual, (const T*)delta, weight,
                                                                          weight_dtype, rows, (T*)out, hidden, eps)));
@@ -243,6 +256,14 @@ MS_EXPORT int ms_qk_norm_rope_append(const void* qkv, int dtype, const int* slot
   const long long items = (long long)n_tokens * (n_q + 2 * n_kv);
   const long long blocks = (items + warps - 1) / warps;
   MS_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_append: %lld heads in one launch is too many", items);
+  const bool vector_ok = d % 8 == 0 && d <= 256 && (cos_sin == nullptr || interleaved || rotary_dim % 16 == 0);
+  if (vector_ok) {
+    MS_DISPATCH(dtype, (qk_norm_rope_append_vec_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+                           (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, cos_sin, rotary_dim,
+                           interleaved, (T*)k_pool, (T*)v_pool, page_size, n_q, n_kv, d, (T*)q_out, n_tokens)));
+    MS_CHECK_LAUNCH("qk_norm_rope_append");
+    return 0;
+  }
   const size_t smem = (size_t)warps * d * sizeof(float);
   MS_DISPATCH(dtype, (qk_norm_rope_append_kernel<T><<<(unsigned)blocks, warps * 32, smem, stream>>>(
                          (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, (const float2*)cos_sin,
@@ -255,6 +276,15 @@ MS_EXPORT int ms_qk_norm_rope_append(const void* qkv, int dtype, const int* slot
 MS_EXPORT int ms_silu_mul(const void* gate_up, int dtype, void* out, int n_tokens, int inter, cudaStream_t stream) {
   const size_t total = (size_t)n_tokens * inter;
   if (total == 0) return 0;
+  if (inter % 8 == 0) {
+    const size_t total8 = total / 8;
+    const size_t blocks8 = (total8 + 255) / 256;
+    MS_REQUIRE(blocks8 < 2147483647ULL, "silu_mul: %zu elements in one launch is too many", total);
+    MS_DISPATCH(dtype, (silu_mul_vec_kernel<T><<<(unsigned)blocks8, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter,
+                                                                                    total8)));
+    MS_CHECK_LAUNCH("silu_mul");
+    return 0;
+  }
   const size_t blocks = (total + 255) / 256;
   MS_REQUIRE(blocks < 2147483647ULL, "silu_mul: %zu elements in one launch is too many", total);
   MS_DISPATCH(dtype, (silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter,

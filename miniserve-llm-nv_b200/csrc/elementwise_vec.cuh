@@ -1,0 +1,219 @@
+// 16-byte-vectorised forms of the memory-bound kernels, used when the row sizes are
+// multiples of eight elements (rows then start on 16-byte boundaries).  Same arithmetic as
+// the scalar forms in elementwise.cu: float32 inside, one rounding at the store.
+#pragma once
+
+#include "common.cuh"
+
+namespace ms {
+
+// Eight consecutive elements as floats, whatever the stored type.
+struct Vec8 {
+  float v[8];
+};
+
+__device__ __forceinline__ Vec8 load8(const float* p) {
+  Vec8 r;
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w;
+  r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+  return r;
+}
+
+__device__ __forceinline__ Vec8 load8(const __nv_bfloat16* p) {
+  Vec8 r;
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(pairs[i]);
+    r.v[2 * i] = f.x;
+    r.v[2 * i + 1] = f.y;
+  }
+  return r;
+}
+
+__device__ __forceinline__ Vec8 load8_any(const void* p, int dtype, size_t index) {
+  return dtype == MS_F32 ? load8(reinterpret_cast<const float*>(p) + index)
+                         : load8(reinterpret_cast<const __nv_bfloat16*>(p) + index);
+}
+
+__device__ __forceinline__ void store8(float* p, const Vec8& x) {
+  *reinterpret_cast<float4*>(p) = make_float4(x.v[0], x.v[1], x.v[2], x.v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(x.v[4], x.v[5], x.v[6], x.v[7]);
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const Vec8& x) {
+  uint4 raw;
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) pairs[i] = __floats2bfloat162_rn(x.v[2 * i], x.v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// ---------------------------------------------------------------- residual add + RMSNorm
+// One block per output row; each thread keeps up to CHUNKS groups of eight elements in registers,
+// so the row is read once.  Requires hidden % 8 == 0 and hidden <= 8 * blockDim.x * CHUNKS.
+template <typename T, int CHUNKS>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const void* __restrict__ weight, int weight_dtype,
+                                       const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
+  __shared__ float scratch[32];
+  const size_t k = blockIdx.x;
+  const size_t r = rows ? (size_t)rows[k] : k;
+  float* res = residual + r * hidden;
+  const T* del = delta ? delta + r * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (delta != nullptr);
+  Vec8 x[CHUNKS];
+  float sum_sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      x[i] = load8(res + c);
+      if (del) {
+        const Vec8 d = load8(del + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) x[i].v[e] += d.v[e];
+        if (write_back) store8(res + c, x[i]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum_sq += x[i].v[e] * x[i].v[e];
+    }
+  }
+  const float total = block_sum(sum_sq, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+  T* dst = out + k * hidden;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < hidden) {
+      const Vec8 w = load8_any(weight, weight_dtype, c);
+      Vec8 y;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) y.v[e] = w.v[e] * (x[i].v[e] * inv);
+      store8(dst + c, y);
+    }
+  }
+}
+
+// ---------------------------------------------------------------- q/k norm + rotation + cache append
+// One warp per (token, head); lane l holds elements 8l .. 8l+7 of the head (d <= 256, d % 8 == 0).
+// Half-split rotation needs rotary_dim % 16 == 0 so that an element's partner sits at the same place
+// in another lane; interleaved pairs sit within a lane.
+template <typename T>
+__global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const int* __restrict__ slots,
+                                               const void* __restrict__ q_weight, const void* __restrict__ k_weight,
+                                               int weight_dtype, float eps, const float* __restrict__ cos_sin,
+                                               int rotary_dim, int interleaved, T* __restrict__ k_pool,
+                                               T* __restrict__ v_pool, int page_size, int n_q, int n_kv, int d,
+                                               T* __restrict__ q_out, int n_tokens) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = n_q + 2 * n_kv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int n = (int)(item / heads), head = (int)(item % heads);
+  const T* src = qkv + ((size_t)n * heads + head) * d;
+  const int c0 = lane * 8;
+  const bool active = c0 < d;
+
+  T* dst;
+  const void* weight = nullptr;
+  bool rotate = false;
+  if (head < n_q) {
+    dst = q_out + ((size_t)n * n_q + head) * d;
+    weight = q_weight;
+    rotate = cos_sin != nullptr;
+  } else {
+    const int slot = slots[n];
+    if (slot < 0) return;
+    const int page = slot / page_size, offset = slot % page_size;
+    const bool is_key = head < n_q + n_kv;
+    const int kv_head = is_key ? head - n_q : head - n_q - n_kv;
+    dst = (is_key ? k_pool : v_pool) + (((size_t)page * n_kv + kv_head) * page_size + offset) * d;
+    if (!is_key) {
+      if (active) *reinterpret_cast<uint4*>(dst + c0) = *reinterpret_cast<const uint4*>(src + c0);
+      if (active && sizeof(T) == 4)
+        *reinterpret_cast<uint4*>(dst + c0 + 4) = *reinterpret_cast<const uint4*>(src + c0 + 4);
+      return;
+    }
+    weight = k_weight;
+    rotate = cos_sin != nullptr;
+  }
+
+  Vec8 x;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) x.v[e] = 0.f;
+  if (active) x = load8(src + c0);
+  if (weight) {
+    float sum_sq = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sum_sq += x.v[e] * x.v[e];
+    sum_sq = warp_sum(sum_sq);
+    const float inv = 1.0f / sqrtf(sum_sq / (float)d + eps);
+    if (active) {
+      const Vec8 w = load8_any(weight, weight_dtype, c0);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x.v[e] = x.v[e] * inv * w.v[e];
+    }
+  }
+  if (rotate) {
+    const int half = rotary_dim >> 1;
+    const float* table = cos_sin + (size_t)n * rotary_dim;       // [half][2] floats
+    if (interleaved) {
+      if (active && c0 < rotary_dim) {
+        const Vec8 cs = load8(table + c0);                       // (cos, sin) of pairs c0/2 .. c0/2+3
+        Vec8 y;
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {
+          const float c = cs.v[2 * p], s = cs.v[2 * p + 1];
+          y.v[2 * p] = x.v[2 * p] * c - x.v[2 * p + 1] * s;
+          y.v[2 * p + 1] = x.v[2 * p + 1] * c + x.v[2 * p] * s;
+        }
+        x = y;
+      }
+    } else {
+      const int lanes_half = half >> 3;                          // lanes that hold one half of the rotary part
+      const bool in_rotary = active && c0 < rotary_dim;
+      const bool first = c0 < half;
+      const int partner_lane = first ? lane + lanes_half : lane - lanes_half;
+      Vec8 partner;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) partner.v[e] = __shfl_sync(0xffffffffu, x.v[e], partner_lane & 31);
+      if (in_rotary) {
+        const int j0 = first ? c0 : c0 - half;
+        const Vec8 cs_a = load8(table + 2 * j0);
+        const Vec8 cs_b = load8(table + 2 * j0 + 8);
+        const float sign = first ? -1.f : 1.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float c = e < 4 ? cs_a.v[2 * e] : cs_b.v[2 * (e - 4)];
+          const float s = e < 4 ? cs_a.v[2 * e + 1] : cs_b.v[2 * (e - 4) + 1];
+          x.v[e] = x.v[e] * c + sign * partner.v[e] * s;
+        }
+      }
+    }
+  }
+  if (active) store8(dst + c0, x);
+}
+
+// ---------------------------------------------------------------- gated activation
+// Eight outputs per thread; requires inter % 8 == 0.
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total8) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  const int per_row = inter >> 3;
+  const size_t n = i / per_row;
+  const int c = (int)(i % per_row) * 8;
+  const Vec8 g = load8(gate_up + n * 2 * inter + c);
+  const Vec8 u = load8(gate_up + n * 2 * inter + inter + c);
+  Vec8 y;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y.v[e] = g.v[e] / (1.0f + expf(-g.v[e])) * u.v[e];
+  store8(out + n * inter + c, y);
+}
+
+}  // namespace ms

@@ -46,7 +46,8 @@ def test_embedding(kernels, dtype, hidden):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("weight_dtype", DTYPES)
-@pytest.mark.parametrize("hidden,eps", [(1, 1e-6), (31, 1e-5), (72, 1e-6), (257, 1e-3), (1031, 1e-6), (4096, 1e-6)])
+@pytest.mark.parametrize("hidden,eps", [(1, 1e-6), (31, 1e-5), (72, 1e-6), (257, 1e-3), (1031, 1e-6), (2048, 1e-6), (4096, 1e-6),
+                                        (6144, 1e-5), (8192, 1e-6), (8200, 1e-6)])
 def test_add_rmsnorm(kernels, dtype, weight_dtype, hidden, eps):
     if dtype == torch.float32 and weight_dtype == torch.bfloat16:
         pytest.skip("a float32 model keeps float32 weights")
