@@ -69,6 +69,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][D]
   __nv_bfloat16* k_s = q_s + BM * D;                                        // [2][BN][D]
   __nv_bfloat16* v_s = k_s + 2 * BN * D;                                    // [2][BN][D]
+  long long* row_offset = reinterpret_cast<long long*>(v_s + 2 * BN * D);   // [2][BN] pool offset of a key row, -1: none
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.y;
@@ -78,8 +79,10 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   const int q_len = query_start[request + 1] - q0;
   const int ctx = context_lens[request];
   const int rows_total = q_len * group;
-  const int row0 = blockIdx.x * BM;
-  if (row0 >= rows_total) return;
+  // Query tiles are taken from the end of the request: under the causal mask the last tiles have the
+  // most keys, and starting them first keeps the tail of the launch short.
+  const int row0 = ((rows_total + BM - 1) / BM - 1 - (int)blockIdx.x) * BM;
+  if (row0 < 0) return;
   const int first_pos = ctx - q_len;                     // position of the request's first query token
   const int t_lo = row0 / group;
   const int last_row = min(rows_total, row0 + BM) - 1;
@@ -122,24 +125,39 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   }
   cp_async_commit();
 
-  auto load_tile = [&](int tile, int stage) {
+  // Where each key row of a tile lies in the pool is looked up once per row (block table, page
+  // arithmetic) and kept in shared memory; the copies then only add the chunk offset.  The offsets of
+  // tile t+2 are computed while tile t is being worked on, into the buffer that tile t used.
+  auto find_rows = [&](int tile, int buffer) {
     const int key0 = tile_begin + tile * BN;
+    for (int r = tid; r < BN; r += THREADS) {
+      const int key = key0 + r;
+      long long offset = -1;
+      if (tile < tile_hi && key < key_end) {
+        const int page = table[key / page_size];
+        offset = (((long long)page * n_kv + kv_head) * page_size + key % page_size) * D;
+      }
+      row_offset[buffer * BN + r] = offset;
+    }
+  };
+  auto load_tile = [&](int tile, int stage) {
     __nv_bfloat16* ks = k_s + stage * BN * D;
     __nv_bfloat16* vs = v_s + stage * BN * D;
+    const long long* offsets = row_offset + stage * BN;
+#pragma unroll 4
     for (int i = tid; i < BN * CHUNKS; i += THREADS) {
       const int r = i / CHUNKS, c = i % CHUNKS;
-      const int key = key0 + r;
-      const bool valid = key < key_end;
-      size_t offset = 0;
-      if (valid) {
-        const int page = table[key / page_size];
-        offset = (((size_t)page * n_kv + kv_head) * page_size + key % page_size) * D + c * 8;
-      }
-      cp_async_16(tile_ptr<D>(ks, r, c), k_pool + offset, valid);
-      cp_async_16(tile_ptr<D>(vs, r, c), v_pool + offset, valid);
+      const long long offset = offsets[r];
+      const bool valid = offset >= 0;
+      const long long at = valid ? offset + c * 8 : 0;
+      cp_async_16(tile_ptr<D>(ks, r, c), k_pool + at, valid);
+      cp_async_16(tile_ptr<D>(vs, r, c), v_pool + at, valid);
     }
   };
 
+  find_rows(tile_lo, 0);
+  find_rows(tile_lo + 1, 1);
+  __syncthreads();
   load_tile(tile_lo, 0);
   cp_async_commit();
   cp_async_wait<1>();            // Q has landed
@@ -167,6 +185,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
+    find_rows(tile + 2, stage);      // this tile's copies have landed; its offsets are no longer needed
     const __nv_bfloat16* ks = k_s + stage * BN * D;
     const __nv_bfloat16* vs = v_s + stage * BN * D;
     const int key0 = tile_begin + tile * BN;
@@ -322,7 +341,7 @@ int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, 
                          int n_kv, float scale, int window, void* out, float* part_o, float* part_lse, int num_splits,
                          int n_requests, int max_query_len, int n_tokens, cudaStream_t stream) {
   constexpr int BM = 16 * W;
-  const size_t smem = (size_t)(BM + 4 * BN) * D * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(BM + 4 * BN) * D * sizeof(__nv_bfloat16) + 2 * BN * sizeof(long long);
   auto kernel = attention_mma_kernel<D, W, BN>;
   static bool configured = false;
   if (!configured) {

@@ -261,12 +261,45 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         return
     _want(x, "x", torch.bfloat16)
     _want(weight, "weight", torch.bfloat16)
-    if not x.is_cuda:
-        raise KernelError("linear: CUDA tensors only")
+    _want(out, "out")
+    if m <= SKINNY_MAX_ROWS and k % 8 == 0:
+        # few rows (decode steps): the library's weight-streaming kernel
+        _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m), _i(n),
+                                        _i(k), _stream()))
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(x, weight.t(), out=out)
     else:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+
+
+SKINNY_MAX_ROWS = 8     # above this the weight-streaming kernel re-reads the activations too often
+
+
+FUSE_GATED_INPUT = False    # applying the activation while streaming recomputes it in every block: slower
+
+
+def gated_linear(gate_up: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = (silu(gate_up[:, :I]) * gate_up[:, I:]) @ weight[N, I]^T``.
+
+    With few rows in bfloat16 the activation is applied while the product streams the weights;
+    otherwise it is one kernel (:func:`silu_mul`) followed by :func:`linear`.
+    """
+    m, two_i = gate_up.shape
+    inter = two_i // 2
+    n = weight.shape[0]
+    if two_i != 2 * inter or weight.shape[1] != inter or tuple(out.shape) != (m, n):
+        raise KernelError(f"gated_linear: gate_up {tuple(gate_up.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if FUSE_GATED_INPUT and gate_up.dtype == torch.bfloat16 and m <= SKINNY_MAX_ROWS and inter % 8 == 0:
+        _want(gate_up, "gate_up", torch.bfloat16)
+        _want(weight, "weight", torch.bfloat16)
+        _want(out, "out")
+        _check(library().ms_gemm_skinny(_ptr(gate_up), _i(1), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m),
+                                        _i(n), _i(inter), _stream()))
+        return
+    hidden = torch.empty((m, inter), dtype=gate_up.dtype, device=gate_up.device)
+    silu_mul(gate_up, hidden)
+    linear(hidden, weight, out)
 
 
 # --------------------------------------------------------------------------- sampling

@@ -38,8 +38,6 @@ class GatedMLP(Part):
         n = x.shape[0]
         gate_up = torch.empty((n, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
         kernels.linear(x, self.gate_up_weight, gate_up)
-        hidden = torch.empty((n, self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.silu_mul(gate_up, hidden)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
-        kernels.linear(hidden, self.down_weight, out)
+        kernels.gated_linear(gate_up, self.down_weight, out)
         return out

@@ -118,6 +118,13 @@ def linear(x, weight, out):
     out.copy_((x.double() @ weight.double().T).to(out.dtype))
 
 
+def gated_linear(gate_up, weight, out):
+    inter = gate_up.shape[1] // 2
+    g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+    hidden = (g * torch.sigmoid(g) * u).to(gate_up.dtype)
+    out.copy_((hidden.double() @ weight.double().T).to(out.dtype))
+
+
 def sample(logits, records, slot_of_row, draw_index, out):
     import struct
 
@@ -137,5 +144,5 @@ def install(monkeypatch) -> None:
     from miniserve_b200 import kernels
 
     for name in ("embedding", "add_rmsnorm", "rmsnorm", "rope_table", "qk_norm_rope_append", "silu_mul",
-                 "paged_attention", "linear", "sample"):
+                 "paged_attention", "linear", "gated_linear", "sample"):
         monkeypatch.setattr(kernels, name, globals()[name])

@@ -248,6 +248,37 @@ def test_linear_bfloat16(kernels, out_dtype, m, n, k):
     assert torch.allclose(out.double(), expected, atol=2e-2 * k ** 0.5 if out_dtype == torch.bfloat16 else 1e-3, rtol=1e-2)
 
 
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 16, 8), (1, 331, 72), (3, 2048, 2048), (8, 500, 1032), (9, 100, 256), (16, 37, 96),
+                                   (17, 384, 200), (33, 64, 6144), (64, 331, 264)])
+def test_linear_few_rows(kernels, out_dtype, m, n, k):
+    """The weight-streaming kernel of decode steps: every row-count class, ragged N and K."""
+    x, w = rand((m, k), torch.bfloat16, 44), rand((n, k), torch.bfloat16, 45, 0.1)
+    out = torch.empty((m, n), dtype=out_dtype).cuda()
+    kernels.linear(x, w, out)
+    expected = x.double() @ w.double().T
+    bound = 1e-3 if out_dtype == torch.float32 else 2e-2
+    assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
+    alone = torch.empty((1, n), dtype=out_dtype).cuda()
+    kernels.linear(x[m // 2:m // 2 + 1].contiguous(), w, alone)
+    if m <= kernels.SKINNY_MAX_ROWS:
+        assert torch.equal(alone[0], out[m // 2])      # a row does not depend on the rows beside it
+    else:
+        assert torch.allclose(alone[0].double(), out[m // 2].double(), atol=bound * max(1.0, float(expected.abs().max())))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,inter", [(1, 72, 200), (8, 2048, 6144), (20, 96, 224), (64, 331, 128), (100, 96, 224), (5, 64, 100)])
+def test_gated_linear(kernels, dtype, m, n, inter):
+    gate_up, w = rand((m, 2 * inter), dtype, 46, 2.0), rand((n, inter), dtype, 47, 0.1)
+    out = torch.empty((m, n), dtype=dtype).cuda()
+    kernels.gated_linear(gate_up, w, out)
+    expected = torch.empty((m, n), dtype=torch.float64).cuda()
+    plain_ops.gated_linear(gate_up, w, expected)
+    bound = 1e-4 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
+
+
 def records_tensor(rows):
     words = [struct.unpack("<8i", struct.pack("<ffiIIiii", t, p, k, seed & 0xFFFFFFFF, seed >> 32, 0, 0, 0))
              for (t, p, k, seed) in rows]
