@@ -57,6 +57,10 @@ class DecodeGraph:
         for size in sizes:
             self.offsets.append(self.offsets[-1] + size)
         self.host = torch.empty(self.offsets[-1], dtype=torch.int32, pin_memory=True)
+        self.host_np = self.host.numpy()             # same memory, cheaper to fill from Python lists
+        self.live_rows = -1
+        self.row_owner: list = [None] * rows         # per row: (request id, pages already written per group)
+        self.has_windows = any(need.window is not None for need in manager.paged_needs)
         self.meta = torch.zeros(self.offsets[-1], dtype=torch.int32, device=sf.device)
         self.n_groups = n_groups
         self.scratch = storage.scratch_page
@@ -94,18 +98,20 @@ class DecodeGraph:
 
     def _fill_padding(self, first_row: int) -> None:
         """Rows from ``first_row`` on become padding: token 0 at position 0 on the scratch page."""
-        o, rows, host = self.offsets, self.rows, self.host
+        import numpy
+
+        o, rows, host = self.offsets, self.rows, self.host_np
         ps = self.page_size
         host[o[0] + first_row:o[1]] = 0
         host[o[1] + first_row:o[2]] = 0
-        host[o[2]:o[3]] = torch.arange(rows, dtype=torch.int32)
-        host[o[3]:o[4]] = torch.arange(rows + 1, dtype=torch.int32)
+        host[o[2]:o[3]] = numpy.arange(rows, dtype=numpy.int32)
+        host[o[3]:o[4]] = numpy.arange(rows + 1, dtype=numpy.int32)
         host[o[4] + first_row:o[5]] = 1
         host[o[5] + first_row:o[6]] = 0
-        host[o[6]:o[7]] = torch.arange(rows, dtype=torch.int32)
+        host[o[6]:o[7]] = numpy.arange(rows, dtype=numpy.int32)
         host[o[7] + first_row:o[8]] = 0
         for g in range(self.n_groups):
-            tables = host[o[8 + 2 * g]:o[9 + 2 * g]].view(rows, self.width)
+            tables = host[o[8 + 2 * g]:o[9 + 2 * g]].reshape(rows, self.width)
             tables[first_row:] = self.scratch
             host[o[9 + 2 * g] + first_row:o[10 + 2 * g]] = self.scratch * ps
 
@@ -231,9 +237,13 @@ class StepFunction:
             graph = self.graphs[rows] = DecodeGraph(self, rows)
         manager, ps = self.manager, self.manager.page_size
         limit, scratch = self.storage.num_pages, self.storage.scratch_page
-        o, host = graph.offsets, graph.host
-        graph._fill_padding(n)
-        tokens, positions, lens, slots_state, draws = [], [], [], [], []
+        o, host = graph.offsets, graph.host_np
+        if graph.live_rows != n:
+            graph._fill_padding(n)
+            for row in range(n, graph.rows):
+                graph.row_owner[row] = None
+            graph.live_rows = n
+        tokens, positions, lens, slots_state = [], [], [], []
         for row, (entry, item) in enumerate(zip(entries, reservation.items)):
             token = int(entry.tokens[0])
             if entry.request_id != item.request_id or item.end - item.start != 1:
@@ -246,25 +256,33 @@ class StepFunction:
             positions.append(item.start)
             lens.append(item.end)
             slots_state.append(manager.requests[entry.request_id].slot)
-            draws.append(0 if draw_index is None else int(draw_index[row]))
+            owner = graph.row_owner[row]
+            same = owner is not None and owner[0] == entry.request_id and not graph.has_windows
             for g in range(graph.n_groups):
                 table = item.tables[g]
-                if len(table) > graph.width or any(p != RELEASED and not 0 <= p < limit for p in table):
-                    raise ValueError("a block table does not fit the pool")
+                if len(table) > graph.width:
+                    raise ValueError("a block table is wider than the model's longest context")
+                # pages that this row already shows (same request as in the last replay) stay; new ones are checked
+                first = owner[1][g] if same and owner[1][g] <= len(table) else 0
+                fresh = table[first:]
+                if any(p != RELEASED and not 0 <= p < limit for p in fresh):
+                    raise ValueError("a page lies outside the pool")
+                base = o[8 + 2 * g] + row * graph.width
+                if fresh:
+                    host[base + first:base + len(table)] = [scratch if p == RELEASED else p for p in fresh]
+                if first == 0:
+                    host[base + len(table):base + graph.width] = scratch
                 slot = item.slots[g][0]
                 if not 0 <= slot < limit * ps:
                     raise ValueError(f"slot {slot} outside the pool")
-                base = o[8 + 2 * g] + row * graph.width
-                host[base:base + len(table)] = torch.tensor([scratch if p == RELEASED else p for p in table],
-                                                            dtype=torch.int32)
-                host[base + len(table):base + graph.width] = scratch
                 host[o[9 + 2 * g] + row] = slot
-        host[o[0]:o[0] + n] = torch.tensor(tokens, dtype=torch.int32)
-        host[o[1]:o[1] + n] = torch.tensor(positions, dtype=torch.int32)
-        host[o[4]:o[4] + n] = torch.tensor(lens, dtype=torch.int32)
-        host[o[5]:o[5] + n] = torch.tensor(slots_state, dtype=torch.int32)
-        host[o[7]:o[7] + n] = torch.tensor(draws, dtype=torch.int32)
-        graph.meta.copy_(host, non_blocking=True)
+            graph.row_owner[row] = (entry.request_id, [len(item.tables[g]) for g in range(graph.n_groups)])
+        host[o[0]:o[0] + n] = tokens
+        host[o[1]:o[1] + n] = positions
+        host[o[4]:o[4] + n] = lens
+        host[o[5]:o[5] + n] = slots_state
+        host[o[7]:o[7] + n] = 0 if draw_index is None else list(draw_index)
+        graph.meta.copy_(graph.host, non_blocking=True)
         graph.graph.replay()
         self.graph_replays += 1
         self.last_tokens = graph.tokens_out[:n]
