@@ -61,6 +61,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                int table_stride, const int* __restrict__ request_of_token,
                                                const int* __restrict__ positions, int page_size, int n_q, int n_kv,
                                                int d, float scale, int window, T* __restrict__ out) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   extern __shared__ float smem[];
   float* q_s = smem;                                  // [d]
   float* part_acc = smem + d;                         // [warps][d]
@@ -161,11 +163,11 @@ MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k
   const size_t smem = (size_t)(d + kAttnWarps * d + 2 * kAttnWarps) * sizeof(float);
   dim3 grid(n_tokens, n_q);
   if (dtype == MS_F32) {
-    paged_attention_generic_kernel<float><<<grid, kAttnWarps * 32, smem, stream>>>(
+    ms::launch(paged_attention_generic_kernel<float>, grid, kAttnWarps * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, table_stride, request_of_token,
         positions, page_size, n_q, n_kv, d, scale, window, (float*)out);
   } else if (dtype == MS_BF16) {
-    paged_attention_generic_kernel<__nv_bfloat16><<<grid, kAttnWarps * 32, smem, stream>>>(
+    ms::launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, kAttnWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_tables,
         table_stride, request_of_token, positions, page_size, n_q, n_kv, d, scale, window, (__nv_bfloat16*)out);
   } else {

@@ -64,6 +64,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
                      int n_kv, float scale_log2, int window, __nv_bfloat16* __restrict__ out,
                      float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   constexpr int BM = 16 * W, THREADS = 32 * W, CHUNKS = D / 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][D]
@@ -313,6 +315,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                          __nv_bfloat16* __restrict__ out, int num_splits, int n_items) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (item >= n_items) return;
@@ -355,14 +359,14 @@ int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, 
              "attention: grid %lld x %d x %lld exceeds the launch limits", tiles, n_kv, (long long)n_requests * num_splits);
   dim3 grid((unsigned)tiles, n_kv, n_requests * num_splits);
   const float scale_log2 = scale * 1.4426950408889634f;
-  kernel<<<grid, W * 32, smem, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
+  ms::launch(kernel, grid, W * 32, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool,
                                          (const __nv_bfloat16*)v_pool, block_tables, table_stride, query_start,
                                          context_lens, page_size, n_q, n_kv, scale_log2, window, (__nv_bfloat16*)out,
                                          part_o, part_lse, num_splits);
   MS_CHECK_LAUNCH("attention_mma");
   if (num_splits > 1) {
     const int items = n_tokens * n_q;
-    attention_combine_kernel<D><<<(items + 3) / 4, 128, 0, stream>>>(part_o, part_lse, (__nv_bfloat16*)out,
+    ms::launch(attention_combine_kernel<D>, (items + 3) / 4, 128, 0, stream, part_o, part_lse, (__nv_bfloat16*)out,
                                                                      num_splits, items);
     MS_CHECK_LAUNCH("attention_combine");
   }

@@ -36,6 +36,32 @@ char* error_buffer();  // defined in runtime.cu
     if (e_ != cudaSuccess) MS_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
   } while (0)
 
+// Programmatic dependent launch.  Every kernel of this library is launched so that it may start
+// while the kernel before it on the stream is still running; it must call `grid_dependency_wait()`
+// before it reads anything an earlier kernel wrote and before it writes anything at all (the call
+// returns once the earlier kernel has finished and its writes are visible).  What a kernel does before
+// that call (fetching weights, which no kernel writes) overlaps with the tail of its predecessor.
+// Every thread block calls it on every path, so that a kernel never finishes before its predecessor.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+
+bool dependent_launch_enabled();  // defined in runtime.cu
+
+template <typename... Params, typename... Args>
+cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -11,6 +11,8 @@ namespace ms {
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   const size_t row = blockIdx.x;
   const T* src = table + (size_t)tokens[row] * hidden;
   float* dst = out + row * hidden;
@@ -27,6 +29,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const void* __restrict__ weight, int weight_dtype,
                                    const int* __restrict__ rows, T* __restrict__ out,
                                    int hidden, float eps) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   __shared__ float scratch[32];
   const size_t k = blockIdx.x;
   const size_t r = rows ? (size_t)rows[k] : k;
@@ -54,6 +58,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__ weight, int weight_dtype,
                                T* __restrict__ out, int hidden, float eps) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   __shared__ float scratch[32];
   const T* src = x + (size_t)blockIdx.x * hidden;
   float sum_sq = 0.f;
@@ -72,6 +78,8 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const void* __restrict__
 // cos_sin[n, j] = (cos, sin)(float(position[n]) * inv_freq[j]) for j < half, in float32.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float2* __restrict__ cos_sin, int n_tokens, int half) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_tokens * half) return;
   const int n = i / half, j = i % half;
@@ -97,6 +105,8 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, const int*
                                            int rotary_dim, int interleaved, T* __restrict__ k_pool,
                                            T* __restrict__ v_pool, int page_size, int n_q, int n_kv, int d,
                                            T* __restrict__ q_out, int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -173,6 +183,8 @@ __global__ void qk_norm_rope_append_kernel(const T* __restrict__ qkv, const int*
 // out[n, c] = silu(gate_up[n, c]) * gate_up[n, inter + c]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const size_t n = i / inter;
@@ -195,7 +207,7 @@ MS_EXPORT int ms_embedding(const int* tokens, const void* table, int dtype, floa
                            cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(hidden > 0, "embedding: hidden size must be positive, got %d", hidden);
-  MS_DISPATCH(dtype, (embedding_kernel<T><<<n_tokens, 256, 0, stream>>>(tokens, (const T*)table, out, hidden)));
+  MS_DISPATCH(dtype, (ms::launch(embedding_kernel<T>, n_tokens, 256, 0, stream, tokens, (const T*)table, out, hidden)));
   MS_CHECK_LAUNCH("embedding");
   return 0;
 }
@@ -209,7 +221,7 @@ MS_EXPORT int ms_add_rmsnorm(float* residual, const void* delta, int dtype, cons
     const int threads = groups >= 256 ? 256 : ((groups + 31) / 32) * 32;
     const int chunks = (groups + threads - 1) / threads;
 #define MS_ADD_RMSNORM_VEC(C)                                                                                     \
-  MS_DISPATCH(dtype, (add_rmsnorm_vec_kernel<T, C><<<n_out, threads, 0, stream>>>(residual, (const T*)delta, weight, \
+  MS_DISPATCH(dtype, (ms::launch(add_rmsnorm_vec_kernel<T, C>, n_out, threads, 0, stream, residual, (const T*)delta, weight, \
                                                                                weight_dtype, rows, (T*)out, hidden, eps)))
     if (chunks == 1) { MS_ADD_RMSNORM_VEC(1); } else if (chunks == 2) { MS_ADD_RMSNORM_VEC(2); } else { MS_ADD_RMSNORM_VEC(4); }
 #undef MS_ADD_RMSNORM_VEC
@@ -217,7 +229,7 @@ MS_EXPORT int ms_add_rmsnorm(float* residual, const void* delta, int dtype, cons
     return 0;
   }
   const int threads = hidden >= 1024 ? 256 : 128;
-  MS_DISPATCH(dtype, (add_rmsnorm_kernel<T><<<n_out, threads, 0, stream>>>(residual, (const T*)delta, weight,
+  MS_DISPATCH(dtype, (ms::launch(add_rmsnorm_kernel<T>, n_out, threads, 0, stream, residual, (const T*)delta, weight,
                                                                          weight_dtype, rows, (T*)out, hidden, eps)));
   MS_CHECK_LAUNCH("add_rmsnorm");
   return 0;
@@ -228,7 +240,7 @@ MS_EXPORT int ms_rmsnorm(const void* x, int dtype, const void* weight, int weigh
   if (n_rows == 0) return 0;
   MS_REQUIRE(hidden > 0, "rmsnorm: size must be positive, got %d", hidden);
   const int threads = hidden >= 1024 ? 256 : (hidden >= 128 ? 128 : 32);
-  MS_DISPATCH(dtype, (rmsnorm_kernel<T><<<n_rows, threads, 0, stream>>>((const T*)x, weight, weight_dtype, (T*)out,
+  MS_DISPATCH(dtype, (ms::launch(rmsnorm_kernel<T>, n_rows, threads, 0, stream, (const T*)x, weight, weight_dtype, (T*)out,
                                                                       hidden, eps)));
   MS_CHECK_LAUNCH("rmsnorm");
   return 0;
@@ -238,7 +250,7 @@ MS_EXPORT int ms_rope_table(const int* positions, const float* inv_freq, float* 
                             cudaStream_t stream) {
   if (n_tokens == 0 || half == 0) return 0;
   const int total = n_tokens * half;
-  rope_table_kernel<<<(total + 255) / 256, 256, 0, stream>>>(positions, inv_freq, (float2*)cos_sin, n_tokens, half);
+  ms::launch(rope_table_kernel, (total + 255) / 256, 256, 0, stream, positions, inv_freq, (float2*)cos_sin, n_tokens, half);
   MS_CHECK_LAUNCH("rope_table");
   return 0;
 }
@@ -258,14 +270,14 @@ MS_EXPORT int ms_qk_norm_rope_append(const void* qkv, int dtype, const int* slot
   MS_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_append: %lld heads in one launch is too many", items);
   const bool vector_ok = d % 8 == 0 && d <= 256 && (cos_sin == nullptr || interleaved || rotary_dim % 16 == 0);
   if (vector_ok) {
-    MS_DISPATCH(dtype, (qk_norm_rope_append_vec_kernel<T><<<(unsigned)blocks, warps * 32, 0, stream>>>(
+    MS_DISPATCH(dtype, (ms::launch(qk_norm_rope_append_vec_kernel<T>, (unsigned)blocks, warps * 32, 0, stream, 
                            (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, cos_sin, rotary_dim,
                            interleaved, (T*)k_pool, (T*)v_pool, page_size, n_q, n_kv, d, (T*)q_out, n_tokens)));
     MS_CHECK_LAUNCH("qk_norm_rope_append");
     return 0;
   }
   const size_t smem = (size_t)warps * d * sizeof(float);
-  MS_DISPATCH(dtype, (qk_norm_rope_append_kernel<T><<<(unsigned)blocks, warps * 32, smem, stream>>>(
+  MS_DISPATCH(dtype, (ms::launch(qk_norm_rope_append_kernel<T>, (unsigned)blocks, warps * 32, smem, stream, 
                          (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, (const float2*)cos_sin,
                          rotary_dim, interleaved, (T*)k_pool, (T*)v_pool, page_size, n_q, n_kv, d, (T*)q_out,
                          n_tokens)));
@@ -280,14 +292,14 @@ MS_EXPORT int ms_silu_mul(const void* gate_up, int dtype, void* out, int n_token
     const size_t total8 = total / 8;
     const size_t blocks8 = (total8 + 255) / 256;
     MS_REQUIRE(blocks8 < 2147483647ULL, "silu_mul: %zu elements in one launch is too many", total);
-    MS_DISPATCH(dtype, (silu_mul_vec_kernel<T><<<(unsigned)blocks8, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter,
+    MS_DISPATCH(dtype, (ms::launch(silu_mul_vec_kernel<T>, (unsigned)blocks8, 256, 0, stream, (const T*)gate_up, (T*)out, inter,
                                                                                     total8)));
     MS_CHECK_LAUNCH("silu_mul");
     return 0;
   }
   const size_t blocks = (total + 255) / 256;
   MS_REQUIRE(blocks < 2147483647ULL, "silu_mul: %zu elements in one launch is too many", total);
-  MS_DISPATCH(dtype, (silu_mul_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter,
+  MS_DISPATCH(dtype, (ms::launch(silu_mul_kernel<T>, (unsigned)blocks, 256, 0, stream, (const T*)gate_up, (T*)out, inter,
                                                                              total)));
   MS_CHECK_LAUNCH("silu_mul");
   return 0;

@@ -59,6 +59,8 @@ template <typename T, int CHUNKS>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const void* __restrict__ weight, int weight_dtype,
                                        const int* __restrict__ rows, T* __restrict__ out, int hidden, float eps) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   __shared__ float scratch[32];
   const size_t k = blockIdx.x;
   const size_t r = rows ? (size_t)rows[k] : k;
@@ -109,6 +111,8 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
                                                int rotary_dim, int interleaved, T* __restrict__ k_pool,
                                                T* __restrict__ v_pool, int page_size, int n_q, int n_kv, int d,
                                                T* __restrict__ q_out, int n_tokens) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = n_q + 2 * n_kv;
@@ -203,6 +207,8 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
 // Eight outputs per thread; requires inter % 8 == 0.
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total8) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total8) return;
   const int per_row = inter >> 3;

@@ -12,6 +12,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C, int M, int N, int K,
                 int lda, int ldw, int ldc) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -68,7 +70,7 @@ MS_EXPORT int ms_gemm_f32(const float* A, const float* W, float* C, int M, int N
   const int grid_m = (M + BM - 1) / BM, grid_n = (N + BN - 1) / BN;
   MS_REQUIRE(grid_m <= 65535, "gemm_f32: %d rows in one launch is too many", M);
   dim3 grid(grid_n, grid_m);
-  gemm_f32_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
+  ms::launch(gemm_f32_kernel, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   MS_CHECK_LAUNCH("gemm_f32");
   return 0;
 }

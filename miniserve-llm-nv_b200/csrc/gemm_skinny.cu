@@ -92,16 +92,24 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
 #pragma unroll
     for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
 
-  constexpr int UNROLL = 8;
-  for (int k0 = k_begin; k0 < k_end; k0 += 32 * UNROLL) {
-    uint4 wa[UNROLL], wb[UNROLL];
+  // Two batches of weight fragments are in flight: while one is consumed the next is on its way.  The
+  // first batch is requested before the kernel waits for its predecessor: weights depend on no kernel.
+  constexpr int UNROLL = 4;
+  uint4 wa[UNROLL], wb[UNROLL], next_a[UNROLL], next_b[UNROLL];
+  auto fetch = [&](int k0, uint4 (&fa)[UNROLL], uint4 (&fb)[UNROLL]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = k0 + 32 * u + 8 * quad_col;
       const bool ok = k + 8 <= k_end;
-      wa[u] = (ok && row_a_ok) ? load_stream_16(w_a + k) : make_uint4(0u, 0u, 0u, 0u);
-      wb[u] = (ok && row_b_ok) ? load_stream_16(w_b + k) : make_uint4(0u, 0u, 0u, 0u);
+      fa[u] = (ok && row_a_ok) ? load_stream_16(w_a + k) : make_uint4(0u, 0u, 0u, 0u);
+      fb[u] = (ok && row_b_ok) ? load_stream_16(w_b + k) : make_uint4(0u, 0u, 0u, 0u);
     }
+  };
+  fetch(k_begin, wa, wb);
+  grid_dependency_wait();
+  grid_dependency_launch();
+  for (int k0 = k_begin; k0 < k_end; k0 += 32 * UNROLL) {
+    fetch(k0 + 32 * UNROLL, next_a, next_b);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = k0 + 32 * u + 8 * quad_col;
@@ -112,6 +120,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ X, int ldx, const __nv_bflo
         mma_bf16_16816(acc[j], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb[j].x, xb[j].y);
         mma_bf16_16816(acc[j], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb[j].z, xb[j].w);
       }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      wa[u] = next_a[u];
+      wb[u] = next_b[u];
     }
   }
 
@@ -166,7 +179,7 @@ int launch_skinny_nt(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, Ou
   int k_blocks = 1;
   while (k_blocks < 4 && blocks * k_blocks < 2 * 148 && K / (SK_WARPS * k_blocks * 2) >= 128) k_blocks *= 2;
   if (k_blocks == 1) {
-    gemm_skinny_kernel<NT, MODE, OutT, false><<<blocks, SK_WARPS * 32, 0, stream>>>(x, ldx, w, o, M, N, K);
+    ms::launch(gemm_skinny_kernel<NT, MODE, OutT, false>, blocks, SK_WARPS * 32, 0, stream, x, ldx, w, o, M, N, K);
     MS_CHECK_LAUNCH("gemm_skinny");
     return 0;
   }

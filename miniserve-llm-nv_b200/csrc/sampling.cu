@@ -113,6 +113,8 @@ __device__ int index_bound(const float* row, float temperature, int vocab, unsig
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int row_stride, int vocab, const SamplingRecord* __restrict__ records,
               const int* __restrict__ slot_of_row, const int* __restrict__ draw_index, int* __restrict__ out) {
+  grid_dependency_wait();
+  grid_dependency_launch();
   __shared__ float fscratch[32];
   __shared__ int iscratch[32];
   __shared__ ArgBest ascratch[32];
@@ -257,7 +259,7 @@ MS_EXPORT int ms_sample(const float* logits, int row_stride, int vocab, const vo
   MS_REQUIRE(vocab > 0 && row_stride >= vocab, "sample: vocabulary %d, row stride %d", vocab, row_stride);
   MS_REQUIRE(records == nullptr || (slot_of_row != nullptr && draw_index != nullptr),
              "sample: sampling records need slot and draw index arrays");
-  sample_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, row_stride, vocab, (const SamplingRecord*)records,
+  ms::launch(sample_kernel, n_rows, kSampleThreads, 0, stream, logits, row_stride, vocab, (const SamplingRecord*)records,
                                                        slot_of_row, draw_index, out);
   MS_CHECK_LAUNCH("sample");
   return 0;
