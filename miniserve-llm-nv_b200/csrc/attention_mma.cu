@@ -312,6 +312,8 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 }
 
 // Merges the splits of one (token, head): out = sum_s w_s O_s / sum_s w_s with w_s = 2^(lse_s - max lse).
+// One warp per (token, head); lane s holds the weight of split s (at most 64 splits), so the partial
+// results can be fetched without waiting for one another.
 template <int D>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                          __nv_bfloat16* __restrict__ out, int num_splits, int n_items) {
@@ -321,18 +323,20 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   const int lane = threadIdx.x & 31;
   if (item >= n_items) return;
   const float* lse = part_lse + (size_t)item * num_splits;
-  float m = -INFINITY;
-  for (int s = 0; s < num_splits; ++s) m = fmaxf(m, lse[s]);
+  const float lse_a = lane < num_splits ? lse[lane] : -INFINITY;
+  const float lse_b = lane + 32 < num_splits ? lse[lane + 32] : -INFINITY;
+  const float m = warp_max(fmaxf(lse_a, lse_b));
+  const float w_a = lse_a == -INFINITY ? 0.f : exp2f(lse_a - m);
+  const float w_b = lse_b == -INFINITY ? 0.f : exp2f(lse_b - m);
+  const float total = warp_sum(w_a + w_b);
   float acc[D / 32] = {};
-  float total = 0.f;
+  const float* base = part_o + (size_t)item * num_splits * D;
+#pragma unroll 8
   for (int s = 0; s < num_splits; ++s) {
-    const float v = lse[s];
-    if (v == -INFINITY) continue;
-    const float w = exp2f(v - m);
-    total += w;
-    const float* src = part_o + ((size_t)item * num_splits + s) * D;
+    const float w = __shfl_sync(0xffffffffu, s < 32 ? w_a : w_b, s & 31);
+    if (w == 0.f) continue;                 // uniform across the warp
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) acc[i] += w * src[lane + 32 * i];
+    for (int i = 0; i < D / 32; ++i) acc[i] += w * base[(size_t)s * D + lane + 32 * i];
   }
   const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll
@@ -393,7 +397,8 @@ MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const vo
   if (n_tokens == 0 || n_requests == 0) return 0;
   MS_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "attention: %d query heads are not a multiple of %d key/value heads", n_q, n_kv);
   MS_REQUIRE(page_size > 0 && max_query_len > 0, "attention: page size %d, longest portion %d", page_size, max_query_len);
-  MS_REQUIRE(num_splits >= 1 && (num_splits == 1 || (part_o && part_lse)), "attention: %d splits need scratch", num_splits);
+  MS_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || (part_o && part_lse)),
+             "attention: %d splits (1..64) need scratch", num_splits);
   const bool small = (long long)max_query_len * (n_q / n_kv) <= 16;
 #define MS_ATTENTION_CASE(D, W, BN)                                                                                   \
   return launch_attention_mma<D, W, BN>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens,    \
