@@ -225,6 +225,26 @@ def test_paged_attention_finds_one_far_key(kernels, dtype, query_len):
             assert torch.allclose(out[0, head].float(), v_pool[page, head // 2, offset].float(), atol=2e-2), target
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("query_len", [1, 4])
+@pytest.mark.parametrize("d", [64, 48])
+def test_paged_attention_window_edge(kernels, dtype, query_len, d):
+    """A dominant key just outside the window must be invisible, just inside it must win."""
+    n_q, n_kv, page_size, window, length = 2, 1, 16, 37, 200
+    q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = \
+        _attention_case(dtype, n_q, n_kv, d, page_size, [length], [query_len], 31)
+    last = length - 1                                   # position of the last query token
+    for key, visible in ((last - window, False), (last - window + 1, True), (last, True)):
+        kp = k_pool.clone()
+        page, offset = int(tables[0, key // page_size]), key % page_size
+        kp[page, 0, offset] = (q[query_len - 1, 0].float() * 40).to(dtype)
+        out = torch.empty_like(q)
+        kernels.paged_attention(q, kp, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                                max_ctx, d ** -0.5, window, out)
+        close = torch.allclose(out[query_len - 1, 0].float(), v_pool[page, 0, offset].float(), atol=3e-2)
+        assert close == visible, (key, visible)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 1, 1), (3, 331, 72), (37, 384, 96), (64, 64, 16), (65, 130, 200), (130, 257, 1031)])
 def test_linear_float32(kernels, m, n, k):
     x, w = rand((m, k), torch.float32, 40), rand((n, k), torch.float32, 41)

@@ -45,7 +45,7 @@ def replay(runtime, steps):
         entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in record["entries"]]
         for entry in entries:
             if entry.request_id not in manager.requests:
-                manager.admit(entry.request_id)
+                runtime.storage.reset_slot(manager.admit(entry.request_id).slot, 0.0, 1.0, 0, 0)
         reservation = manager.prepare([(e.request_id, len(e.tokens)) for e in entries])
         outputs[record["step"]] = runtime.step_function.run(entries, reservation).double().cpu()
         manager.commit(reservation)
@@ -84,6 +84,24 @@ def test_cuttings_match_plain(tmp_path, dtype, name, page_size, cutting):
             assert error <= bound, (rid, position, error, bound)
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
     print(f"worst error / bound = {worst:.3f}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page_size", [("b", 8), ("d", 16)])
+def test_long_decoding_and_first_tokens(tmp_path, dtype, name, page_size):
+    """A sequence decoded one token at a time from its very first token, across many page edges."""
+    vocab = helpers.TINY[name]["vocab_size"]
+    tokens = helpers.random_tokens(vocab, 300, seed=77)
+    steps = [{"step": i, "entries": [{"id": "r", "tokens": [t], "want": [0]}], "end": ["r"] if i == 299 else []}
+             for i, t in enumerate(tokens)]
+    folder = helpers.make_folder(tmp_path, name, seed=2)
+    runtime = build(folder, dtype, (300 + page_size - 1) // page_size, page_size)
+    got = helpers.collect(steps, replay(runtime, steps))["r"]
+    expected = helpers.oracle_logits(folder, tokens)
+    bound = error_bounds(dtype, expected)
+    errors = [float((got[p] - expected[p]).abs().max()) for p in range(300)]
+    assert max(errors) <= bound, (errors.index(max(errors)), max(errors), bound)
+    assert max(errors[:3]) <= bound                       # the first tokens of a sequence
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
