@@ -96,13 +96,35 @@ class ClockSampler:
 
 
 def reference_arm(args) -> int:
-    """MiniServe itself: its native extension builds only for sm_75 / sm_120 (its CMakeLists.txt requires one
-    of them) and its engine refuses to start without that extension, so there is nothing to run on sm_100."""
-    marker = REPO / "baseline" / "_ref" / "miniserve"
-    why = ("MiniServe's CUDA extension is built for sm_75 or sm_120 only and its engine core requires it; "
-           "no sm_100 build exists" if marker.exists() else
-           "the reference is not installed under baseline/_ref (its wheel needs a CUDA build for sm_75/sm_120 only)")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    """MiniServe itself, unmodified, from ``baseline/_ref`` (see ``baseline/reference_arm.py``): the same
+    metric (decoded tokens per second at the same batch, context and model sizes), timed over the same
+    number of steps around its own ``EngineCore.step_multi``.  Its steps return token ids to the host,
+    so its device-timed and end-to-end numbers are one and the same."""
+    sys.path.insert(0, str(REPO / "baseline"))
+    import reference_arm as arm
+
+    if args.gpus != 1:
+        print(json.dumps({"impl": "reference", "unavailable": "MiniServe runs on one GPU only"}))
+        return 0
+    warmup = max(args.warmup, 3)
+    steps = min(args.steps, 64)
+    result = arm.main(dict(MODEL), args.batch, CONTEXT, steps, warmup, PAGE_SIZE)
+    if "unavailable" in result:
+        print(json.dumps(result))
+        return 0
+    line = {
+        "metric": "Qwen3-1.7B bf16 decode tok/s @ batch 8 (context 4096); prefill tok/s @ 2,048 tokens",
+        "impl": "reference", "value": result["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random weights)",
+        "config": {"model": "Qwen3-1.7B shape", "layers": MODEL["num_hidden_layers"], "hidden": MODEL["hidden_size"],
+                   "global_batch": args.batch, "seq_len": CONTEXT, "context_len": CONTEXT, "page_size": PAGE_SIZE,
+                   "parallelism": "single GPU", "decode_execution": "cuda_graph (batched)",
+                   "attention_backend": "cuda_paged", "rmsnorm_backend": "cuda"},
+        "e2e": {"value": result["value"], "unit": "tokens/s", "ms_per_step": result["ms_per_step"]},
+        "prefill_seconds_total": result["prefill_seconds_total"],
+    }
+    print(json.dumps(line))
     return 0
 
 
