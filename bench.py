@@ -138,6 +138,8 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
+                        help="run only a few eager steps of one phase and exit (a small case for ncu; times nothing)")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -161,7 +163,8 @@ def main() -> int:
     pages = max_batch * ((CONTEXT + PAGE_SIZE - 1) // PAGE_SIZE) + 64
     runtime = build_runtime(None, EngineConfig(
         dtype="bfloat16", max_model_len=CONTEXT, max_num_seqs=max_batch, kv_block_size=PAGE_SIZE, num_kv_blocks=pages,
-        max_num_batched_tokens=8192, enable_prefix_cache=False, decode_execution="cuda_graph"),
+        max_num_batched_tokens=8192, enable_prefix_cache=False,
+        decode_execution="eager" if args.profile else "cuda_graph"),
         config_dict=config, weights_seed=0)
     manager, step_function = runtime.manager, runtime.step_function
     vocab = config["vocab_size"]
@@ -216,6 +219,26 @@ def main() -> int:
         for rid in ids:
             manager.release(rid)
         return seconds, mean_context, launches
+
+    if args.profile:
+        # A small, self-ending case for a profiler: the cache is reserved but not computed (its content
+        # does not change what the kernels do), then a few eager steps of the chosen phase run.
+        if args.profile == "decode":
+            ids = [f"p{i}" for i in range(args.batch)]
+            for rid in ids:
+                manager.admit(rid)
+                manager.commit(manager.prepare([(rid, CONTEXT - args.steps - warmup - 1)]))
+            decode_steps(ids, warmup + args.steps)
+        else:
+            for _ in range(warmup + args.steps):
+                manager.admit("p")
+                reservation = manager.prepare([("p", PREFILL_TOKENS)])
+                step_function.run([StepEntry("p", prompt(PREFILL_TOKENS), [PREFILL_TOKENS - 1])], reservation)
+                manager.commit(reservation)
+                manager.release("p")
+        torch.cuda.synchronize()
+        print(json.dumps({"profile": args.profile, "layers": args.layers, "batch": args.batch, "steps": args.steps}))
+        return 0
 
     # ---------------------------------------------------------------- prefill of 2,048 tokens
     def prefill_once() -> None:
