@@ -57,7 +57,10 @@ template <int D> __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat1
   return base + row * D + ((chunk ^ mask) << 3);
 }
 
-template <int D, int W, int BN>
+// D head size, W warps, BN keys per tile, MT 16-row tiles per warp (a K/V fragment fetched from shared
+// memory feeds MT MMAs), STAGES key/value tiles in shared memory (STAGES - 1 of them in flight while one
+// is worked on).
+template <int D, int W, int BN, int MT, int STAGES>
 __global__ void __launch_bounds__(W * 32)
 attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                      const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ block_tables, int table_stride,
@@ -66,12 +69,13 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits) {
   grid_dependency_wait();
   grid_dependency_launch();
-  constexpr int BM = 16 * W, THREADS = 32 * W, CHUNKS = D / 8;
+  constexpr int BM = 16 * MT * W, THREADS = 32 * W, CHUNKS = D / 8;
+  constexpr bool Q_IN_REGISTERS = MT == 1;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [BM][D]
-  __nv_bfloat16* k_s = q_s + BM * D;                                        // [2][BN][D]
-  __nv_bfloat16* v_s = k_s + 2 * BN * D;                                    // [2][BN][D]
-  long long* row_offset = reinterpret_cast<long long*>(v_s + 2 * BN * D);   // [2][BN] pool offset of a key row, -1: none
+  __nv_bfloat16* k_s = q_s + BM * D;                                        // [STAGES][BN][D]
+  __nv_bfloat16* v_s = k_s + STAGES * BN * D;                               // [STAGES][BN][D]
+  long long* row_offset = reinterpret_cast<long long*>(v_s + STAGES * BN * D);   // [STAGES][BN] pool offset of a key row, -1: none
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kv_head = blockIdx.y;
@@ -99,24 +103,28 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   const int tile_hi = min(n_tiles, tile_lo + tiles_per_split);
   const int* table = block_tables + (size_t)request * table_stride;
 
-  // rows of this thread in the mma layout: r_a (lane / 4) and r_a + 8 of the warp's 16 rows
+  // rows of this thread in the mma layout: for each of the warp's MT tiles, rows (lane / 4) and (lane / 4) + 8
   const int quad_row = lane >> 2, quad_col = lane & 3;
-  const int row_a = row0 + warp * 16 + quad_row, row_b = row_a + 8;
+  const int warp_row0 = row0 + warp * 16 * MT;
+  auto thread_row = [&](int mt, int half) { return warp_row0 + mt * 16 + quad_row + half * 8; };
 
   if (tile_lo >= tile_hi) {                               // nothing to do for this split
     if (num_splits > 1 && quad_col == 0) {
-      for (int which = 0; which < 2; ++which) {
-        const int row = which ? row_b : row_a;
-        if (row < rows_total) {
-          const size_t index = ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group);
-          part_lse[index * num_splits + split] = -INFINITY;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int row = thread_row(mt, half);
+          if (row < rows_total) {
+            const size_t index = ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group);
+            part_lse[index * num_splits + split] = -INFINITY;
+          }
         }
-      }
     }
     return;
   }
 
-  // ---- Q tile to shared memory, then to registers as A fragments
+  // ---- Q tile to shared memory
   for (int i = tid; i < BM * CHUNKS; i += THREADS) {
     const int r = i / CHUNKS, c = i % CHUNKS;
     const int row = row0 + r;
@@ -129,7 +137,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 
   // Where each key row of a tile lies in the pool is looked up once per row (block table, page
   // arithmetic) and kept in shared memory; the copies then only add the chunk offset.  The offsets of
-  // tile t+2 are computed while tile t is being worked on, into the buffer that tile t used.
+  // tile t + STAGES are computed while tile t is being worked on, into the buffer that tile t used.
   auto find_rows = [&](int tile, int buffer) {
     const int key0 = tile_begin + tile * BN;
     for (int r = tid; r < BN; r += THREADS) {
@@ -142,7 +150,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
       row_offset[buffer * BN + r] = offset;
     }
   };
-  auto load_tile = [&](int tile, int stage) {
+  auto load_tile = [&](int stage) {
     __nv_bfloat16* ks = k_s + stage * BN * D;
     __nv_bfloat16* vs = v_s + stage * BN * D;
     const long long* offsets = row_offset + stage * BN;
@@ -157,123 +165,160 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     }
   };
 
-  find_rows(tile_lo, 0);
-  find_rows(tile_lo + 1, 1);
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) find_rows(tile_lo + s, s);
   __syncthreads();
-  load_tile(tile_lo, 0);
-  cp_async_commit();
-  cp_async_wait<1>();            // Q has landed
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (tile_lo + s < tile_hi) load_tile(s);
+    cp_async_commit();
+  }
+  cp_async_wait<STAGES - 1>();   // Q has landed
   __syncthreads();
 
-  unsigned q_frag[D / 16][4];
-#pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) {
-    const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+  unsigned q_frag[Q_IN_REGISTERS ? D / 16 : 1][4];
+  auto q_fragment_address = [&](int mt, int kk) {
+    const int r = (warp * MT + mt) * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
     const int c = kk * 2 + (lane >> 4);
-    ldmatrix_x4(q_frag[kk], tile_ptr<D>(q_s, r, c));
+    return tile_ptr<D>(q_s, r, c);
+  };
+  if (Q_IN_REGISTERS) {
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) ldmatrix_x4(q_frag[kk], q_fragment_address(0, kk));
   }
 
-  float acc_o[D / 8][4];
+  float acc_o[MT][D / 8][4];
+  float m_run[MT][2], l_run[MT][2];
+  int pos[MT][2];
 #pragma unroll
-  for (int n = 0; n < D / 8; ++n)
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc_o[n][e] = 0.f;
-  float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-  const int pos_a = first_pos + row_a / group, pos_b = first_pos + row_b / group;
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc_o[mt][n][e] = 0.f;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      m_run[mt][half] = -INFINITY;
+      l_run[mt][half] = 0.f;
+      pos[mt][half] = first_pos + thread_row(mt, half) / group;
+    }
+  }
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
-    const int stage = (tile - tile_lo) & 1;
-    if (tile + 1 < tile_hi) load_tile(tile + 1, stage ^ 1);
+    const int stage = (tile - tile_lo) % STAGES;
+    if (tile + STAGES - 1 < tile_hi) load_tile((stage + STAGES - 1) % STAGES);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<STAGES - 1>();
     __syncthreads();
-    find_rows(tile + 2, stage);      // this tile's copies have landed; its offsets are no longer needed
+    find_rows(tile + STAGES, stage);     // this tile's copies have landed; its offsets are no longer needed
     const __nv_bfloat16* ks = k_s + stage * BN * D;
     const __nv_bfloat16* vs = v_s + stage * BN * D;
     const int key0 = tile_begin + tile * BN;
 
     // ---- S = Q K^T
-    float acc_s[BN / 8][4];
+    float acc_s[MT][BN / 8][4];
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n)
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc_s[n][e] = 0.f;
+      for (int n = 0; n < BN / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc_s[mt][n][e] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk) {
+      unsigned a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if (Q_IN_REGISTERS) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) a[mt][e] = q_frag[kk][e];
+        } else {
+          ldmatrix_x4(a[mt], q_fragment_address(mt, kk));
+        }
+      }
 #pragma unroll
       for (int np = 0; np < BN / 16; ++np) {
         unsigned b[4];
         const int r = np * 16 + (lane & 7) + (lane >> 4) * 8;
         const int c = kk * 2 + ((lane >> 3) & 1);
         ldmatrix_x4(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(ks), r, c));
-        mma_bf16(acc_s[2 * np], q_frag[kk], b[0], b[1]);
-        mma_bf16(acc_s[2 * np + 1], q_frag[kk], b[2], b[3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(acc_s[mt][2 * np], a[mt], b[0], b[1]);
+          mma_bf16(acc_s[mt][2 * np + 1], a[mt], b[2], b[3]);
+        }
       }
     }
 
     // ---- mask and online softmax (scores are scaled inside the exponent)
     const bool full = (key0 + BN - 1 <= first_pos + t_lo) && (window <= 0 || key0 >= first_pos + t_hi - window + 1);
-    float max_a = -INFINITY, max_b = -INFINITY;
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
+    for (int mt = 0; mt < MT; ++mt) {
+      float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (!full) {
-          const int key = key0 + n * 8 + quad_col * 2 + (e & 1);
-          const int pos = (e < 2) ? pos_a : pos_b;
-          const bool visible = key <= pos && (window <= 0 || key > pos - window);
-          if (!visible) acc_s[n][e] = -INFINITY;
+      for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (!full) {
+            const int key = key0 + n * 8 + quad_col * 2 + (e & 1);
+            const int p = pos[mt][e >> 1];
+            const bool visible = key <= p && (window <= 0 || key > p - window);
+            if (!visible) acc_s[mt][n][e] = -INFINITY;
+          }
+          tile_max[e >> 1] = fmaxf(tile_max[e >> 1], acc_s[mt][n][e]);
         }
-        if (e < 2) max_a = fmaxf(max_a, acc_s[n][e]); else max_b = fmaxf(max_b, acc_s[n][e]);
       }
-    }
-    max_a = fmaxf(max_a, __shfl_xor_sync(0xffffffffu, max_a, 1));
-    max_a = fmaxf(max_a, __shfl_xor_sync(0xffffffffu, max_a, 2));
-    max_b = fmaxf(max_b, __shfl_xor_sync(0xffffffffu, max_b, 1));
-    max_b = fmaxf(max_b, __shfl_xor_sync(0xffffffffu, max_b, 2));
-    const float new_a = fmaxf(m_a, max_a), new_b = fmaxf(m_b, max_b);
-    const float base_a = new_a == -INFINITY ? 0.f : new_a * scale_log2;
-    const float base_b = new_b == -INFINITY ? 0.f : new_b * scale_log2;
-    const float corr_a = exp2f(m_a * scale_log2 - base_a);      // m == -inf gives 0
-    const float corr_b = exp2f(m_b * scale_log2 - base_b);
-    m_a = new_a;
-    m_b = new_b;
-    float sum_a = 0.f, sum_b = 0.f;
+      float base[2], corr[2], sum[2] = {0.f, 0.f};
 #pragma unroll
-    for (int n = 0; n < BN / 8; ++n) {
-      acc_s[n][0] = exp2f(acc_s[n][0] * scale_log2 - base_a);
-      acc_s[n][1] = exp2f(acc_s[n][1] * scale_log2 - base_a);
-      acc_s[n][2] = exp2f(acc_s[n][2] * scale_log2 - base_b);
-      acc_s[n][3] = exp2f(acc_s[n][3] * scale_log2 - base_b);
-      sum_a += acc_s[n][0] + acc_s[n][1];
-      sum_b += acc_s[n][2] + acc_s[n][3];
-    }
-    l_a = l_a * corr_a + sum_a;
-    l_b = l_b * corr_b + sum_b;
+      for (int half = 0; half < 2; ++half) {
+        float v = tile_max[half];
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        const float updated = fmaxf(m_run[mt][half], v);
+        base[half] = updated == -INFINITY ? 0.f : updated * scale_log2;
+        corr[half] = exp2f(m_run[mt][half] * scale_log2 - base[half]);      // m == -inf gives 0
+        m_run[mt][half] = updated;
+      }
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
-      acc_o[n][0] *= corr_a;
-      acc_o[n][1] *= corr_a;
-      acc_o[n][2] *= corr_b;
-      acc_o[n][3] *= corr_b;
+      for (int n = 0; n < BN / 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc_s[mt][n][e] = exp2f(acc_s[mt][n][e] * scale_log2 - base[e >> 1]);
+          sum[e >> 1] += acc_s[mt][n][e];
+        }
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) l_run[mt][half] = l_run[mt][half] * corr[half] + sum[half];
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) {
+        acc_o[mt][n][0] *= corr[0];
+        acc_o[mt][n][1] *= corr[0];
+        acc_o[mt][n][2] *= corr[1];
+        acc_o[mt][n][3] *= corr[1];
+      }
     }
 
     // ---- O += P V
 #pragma unroll
     for (int kp = 0; kp < BN / 16; ++kp) {
-      unsigned p[4];
-      p[0] = pack_bf16(acc_s[2 * kp][0], acc_s[2 * kp][1]);
-      p[1] = pack_bf16(acc_s[2 * kp][2], acc_s[2 * kp][3]);
-      p[2] = pack_bf16(acc_s[2 * kp + 1][0], acc_s[2 * kp + 1][1]);
-      p[3] = pack_bf16(acc_s[2 * kp + 1][2], acc_s[2 * kp + 1][3]);
+      unsigned p[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        p[mt][0] = pack_bf16(acc_s[mt][2 * kp][0], acc_s[mt][2 * kp][1]);
+        p[mt][1] = pack_bf16(acc_s[mt][2 * kp][2], acc_s[mt][2 * kp][3]);
+        p[mt][2] = pack_bf16(acc_s[mt][2 * kp + 1][0], acc_s[mt][2 * kp + 1][1]);
+        p[mt][3] = pack_bf16(acc_s[mt][2 * kp + 1][2], acc_s[mt][2 * kp + 1][3]);
+      }
 #pragma unroll
       for (int np = 0; np < D / 16; ++np) {
         unsigned b[4];
         const int r = kp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int c = np * 2 + (lane >> 4);
         ldmatrix_x4_trans(b, tile_ptr<D>(const_cast<__nv_bfloat16*>(vs), r, c));
-        mma_bf16(acc_o[2 * np], p, b[0], b[1]);
-        mma_bf16(acc_o[2 * np + 1], p, b[2], b[3]);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          mma_bf16(acc_o[mt][2 * np], p[mt], b[0], b[1]);
+          mma_bf16(acc_o[mt][2 * np + 1], p[mt], b[2], b[3]);
+        }
       }
     }
     __syncthreads();       // all warps are done with this stage before it is refilled
@@ -281,32 +326,33 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   cp_async_wait<0>();
 
   // ---- finish: row sums across the quad, normalise, store
-  l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
-  l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
-  l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
-  l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    const int row = which ? row_b : row_a;
-    if (row >= rows_total) continue;
-    const float l = which ? l_b : l_a;
-    const float m = which ? m_b : m_a;
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    const size_t index = (size_t)(q0 + row / group) * n_q + kv_head * group + row % group;
-    if (num_splits == 1) {
-      __nv_bfloat16* dst = out + index * D;
+  for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n) {
-        const unsigned packed = pack_bf16(acc_o[n][2 * which] * inv, acc_o[n][2 * which + 1] * inv);
-        *reinterpret_cast<unsigned*>(dst + n * 8 + quad_col * 2) = packed;
+    for (int half = 0; half < 2; ++half) {
+      float l = l_run[mt][half];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int row = thread_row(mt, half);
+      if (row >= rows_total) continue;
+      const float m = m_run[mt][half];
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const size_t index = (size_t)(q0 + row / group) * n_q + kv_head * group + row % group;
+      if (num_splits == 1) {
+        __nv_bfloat16* dst = out + index * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n) {
+          const unsigned packed = pack_bf16(acc_o[mt][n][2 * half] * inv, acc_o[mt][n][2 * half + 1] * inv);
+          *reinterpret_cast<unsigned*>(dst + n * 8 + quad_col * 2) = packed;
+        }
+      } else {
+        float* dst = part_o + (index * num_splits + split) * D;
+#pragma unroll
+        for (int n = 0; n < D / 8; ++n)
+          *reinterpret_cast<float2*>(dst + n * 8 + quad_col * 2) =
+              make_float2(acc_o[mt][n][2 * half] * inv, acc_o[mt][n][2 * half + 1] * inv);
+        if (quad_col == 0) part_lse[index * num_splits + split] = l > 0.f ? m * scale_log2 + log2f(l) : -INFINITY;
       }
-    } else {
-      float* dst = part_o + (index * num_splits + split) * D;
-#pragma unroll
-      for (int n = 0; n < D / 8; ++n)
-        *reinterpret_cast<float2*>(dst + n * 8 + quad_col * 2) =
-            make_float2(acc_o[n][2 * which] * inv, acc_o[n][2 * which + 1] * inv);
-      if (quad_col == 0) part_lse[index * num_splits + split] = l > 0.f ? m * scale_log2 + log2f(l) : -INFINITY;
     }
   }
 }
@@ -343,14 +389,35 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   for (int i = 0; i < D / 32; ++i) out[(size_t)item * D + lane + 32 * i] = __float2bfloat16_rn(acc[i] * inv);
 }
 
-template <int D, int W, int BN>
+// Thread blocks of the single-token variant that fit on the whole GPU at once (0 if it cannot be asked).
+template <int D, int W, int BN, int MT, int STAGES>
+int attention_block_slots() {
+  static int slots = -1;
+  if (slots < 0) {
+    constexpr int BM = 16 * MT * W;
+    const size_t smem = (size_t)(BM + 2 * STAGES * BN) * D * sizeof(__nv_bfloat16) + STAGES * BN * sizeof(long long);
+    auto kernel = attention_mma_kernel<D, W, BN, MT, STAGES>;
+    int device = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, W * 32, smem) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    slots = sms * per_sm;
+  }
+  return slots;
+}
+
+template <int D, int W, int BN, int MT, int STAGES>
 int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, const int* block_tables,
                          int table_stride, const int* query_start, const int* context_lens, int page_size, int n_q,
                          int n_kv, float scale, int window, void* out, float* part_o, float* part_lse, int num_splits,
                          int n_requests, int max_query_len, int n_tokens, cudaStream_t stream) {
-  constexpr int BM = 16 * W;
-  const size_t smem = (size_t)(BM + 4 * BN) * D * sizeof(__nv_bfloat16) + 2 * BN * sizeof(long long);
-  auto kernel = attention_mma_kernel<D, W, BN>;
+  constexpr int BM = 16 * MT * W;
+  const size_t smem = (size_t)(BM + 2 * STAGES * BN) * D * sizeof(__nv_bfloat16) + STAGES * BN * sizeof(long long);
+  auto kernel = attention_mma_kernel<D, W, BN, MT, STAGES>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -384,6 +451,24 @@ using namespace ms;
 // Head sizes this kernel is built for; other sizes use the general kernel.
 MS_EXPORT int ms_attention_mma_supports(int head_dim) { return head_dim == 32 || head_dim == 64 || head_dim == 128; }
 
+// In how many parts the keys of a step of single tokens should be split: as many as fill the GPU
+// with one wave of thread blocks (a second, partly filled wave would double the time), each part
+// keeping at least 128 keys; 1 for anything else.
+MS_EXPORT int ms_attention_mma_splits(int d, int n_requests, int n_kv, int n_q, int max_query_len, int max_context_len) {
+  if (n_kv <= 0 || (long long)max_query_len * (n_q / n_kv) > 16) return 1;
+  int slots = 0;
+  if (d == 128) slots = attention_block_slots<128, 1, 32, 1, 3>();
+  else if (d == 64) slots = attention_block_slots<64, 1, 64, 1, 3>();
+  else if (d == 32) slots = attention_block_slots<32, 1, 64, 1, 3>();
+  const int base = n_requests * n_kv;
+  if (slots <= 0 || base <= 0) return 1;
+  int splits = slots / base;
+  const int by_length = max_context_len / 128;
+  if (splits > by_length) splits = by_length;
+  if (splits > 64) splits = 64;
+  return splits < 1 ? 1 : splits;
+}
+
 // q, out [n_tokens, n_q, d] bfloat16; pools of one layer [pages, n_kv, page_size, d]; block_tables
 // [n_requests, table_stride]; query_start [n_requests + 1]; context_lens [n_requests] (lengths after
 // this step's tokens).  Request r's tokens query_start[r] .. query_start[r+1] are the last ones of its
@@ -399,14 +484,16 @@ MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const vo
   MS_REQUIRE(page_size > 0 && max_query_len > 0, "attention: page size %d, longest portion %d", page_size, max_query_len);
   MS_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || (part_o && part_lse)),
              "attention: %d splits (1..64) need scratch", num_splits);
+  // Steps of single tokens: one warp per block (its 16 rows hold the group's query heads), three tiles in
+  // shared memory.  Prompt portions: four warps of 32 rows each, two tiles.
   const bool small = (long long)max_query_len * (n_q / n_kv) <= 16;
-#define MS_ATTENTION_CASE(D, W, BN)                                                                                   \
-  return launch_attention_mma<D, W, BN>(q, k_pool, v_pool, block_tables, table_stride, query_start, context_lens,    \
-                                        page_size, n_q, n_kv, scale, window, out, part_o, part_lse, num_splits,      \
-                                        n_requests, max_query_len, n_tokens, stream)
-  if (d == 128) { if (small) { MS_ATTENTION_CASE(128, 1, 32); } else { MS_ATTENTION_CASE(128, 4, 64); } }
-  if (d == 64) { if (small) { MS_ATTENTION_CASE(64, 1, 64); } else { MS_ATTENTION_CASE(64, 4, 64); } }
-  if (d == 32) { if (small) { MS_ATTENTION_CASE(32, 1, 64); } else { MS_ATTENTION_CASE(32, 4, 64); } }
+#define MS_ATTENTION_CASE(D, W, BN, MT, STAGES)                                                                       \
+  return launch_attention_mma<D, W, BN, MT, STAGES>(q, k_pool, v_pool, block_tables, table_stride, query_start,       \
+                                                    context_lens, page_size, n_q, n_kv, scale, window, out, part_o,  \
+                                                    part_lse, num_splits, n_requests, max_query_len, n_tokens, stream)
+  if (d == 128) { if (small) { MS_ATTENTION_CASE(128, 1, 32, 1, 3); } else { MS_ATTENTION_CASE(128, 4, 64, 2, 2); } }
+  if (d == 64) { if (small) { MS_ATTENTION_CASE(64, 1, 64, 1, 3); } else { MS_ATTENTION_CASE(64, 4, 64, 2, 2); } }
+  if (d == 32) { if (small) { MS_ATTENTION_CASE(32, 1, 64, 1, 3); } else { MS_ATTENTION_CASE(32, 4, 64, 2, 2); } }
 #undef MS_ATTENTION_CASE
   MS_FAIL("attention: the tensor-core kernel is not built for head size %d", d);
 }

@@ -182,15 +182,6 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 # --------------------------------------------------------------------------- attention
 
 
-def attention_splits(n_requests: int, n_kv: int, max_query_len: int, max_context_len: int) -> int:
-    """In how many parts a decode step's keys are split so that the work fills the GPU's 148 SMs."""
-    if max_query_len != 1:
-        return 1
-    by_occupancy = -(-4 * 148 // max(n_requests * n_kv, 1))
-    by_length = max(max_context_len // 128, 1)
-    return max(1, min(by_occupancy, by_length, 32))
-
-
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                     request_of_token: torch.Tensor, positions: torch.Tensor, query_start: torch.Tensor,
                     context_lens: torch.Tensor, max_query_len: int, max_context_len: int, scale: float,
@@ -221,7 +212,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     lib = library()
     if q.dtype == torch.bfloat16 and lib.ms_attention_mma_supports(_i(head_dim)):
         n_kv = k_pool.shape[1]
-        splits = attention_splits(n_requests, n_kv, max_query_len, max_context_len)
+        splits = lib.ms_attention_mma_splits(_i(head_dim), _i(n_requests), _i(n_kv), _i(n_q), _i(max_query_len),
+                                             _i(max_context_len))
         part_o = part_lse = None
         if splits > 1:
             part_o = torch.empty((n * n_q * splits, head_dim), dtype=torch.float32, device=q.device)
