@@ -259,13 +259,54 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
         _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m), _i(n),
                                         _i(k), _stream()))
         return
+    if USE_TCGEN05_GEMM and m >= 128 and k % 8 == 0:
+        linear_tcgen05(x, weight, out)
+        return
     if out.dtype == torch.bfloat16:
         torch.mm(x, weight.t(), out=out)
     else:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
 
 
-SKINNY_MAX_ROWS = 8     # above this the weight-streaming kernel re-reads the activations too often
+# Products of 128 rows and more go to cuBLAS unless this is set (environment MINISERVE_B200_TCGEN05_GEMM=1):
+# the library's own tcgen05 kernel is correct but reaches 60-75 % of cuBLAS' speed so far.
+USE_TCGEN05_GEMM = __import__("os").environ.get("MINISERVE_B200_TCGEN05_GEMM", "0") == "1"
+
+_error_flags: dict = {}
+
+
+def device_error_flag(device: torch.device) -> torch.Tensor:
+    """One int32 on the device that kernels with bounded waits set when a wait runs out (0: all well)."""
+    key = torch.device(device).index or 0
+    if key not in _error_flags:
+        _error_flags[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _error_flags[key]
+
+
+def check_device_errors(device: torch.device) -> None:
+    """Raises if a kernel gave up waiting since the last check (synchronises the device)."""
+    flag = device_error_flag(device)
+    code = int(flag.item())
+    if code:
+        flag.zero_()
+        raise KernelError(f"a kernel gave up a bounded wait (code {code}: 1 producer, 2 MMA issue, 3 epilogue)")
+
+
+def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
+    """``out = x @ weight^T`` (``add``: ``out += ...`` on a float32 ``out``) by the library's tcgen05 kernel.
+
+    bfloat16 operands with an inner size that is a multiple of 8; meant for 128 rows and more.
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, (n, k))
+    _want(out, "out", torch.float32 if add else None, (m, n))
+    _check(library().ms_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(1 if add else 0), _i(m),
+                                     _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
+
+
+SKINNY_MAX_ROWS = 8    # above this the weight-streaming kernel re-reads the activations too often
 
 
 FUSE_GATED_INPUT = False    # applying the activation while streaming recomputes it in every block: slower

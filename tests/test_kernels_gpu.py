@@ -299,6 +299,25 @@ def test_gated_linear(kernels, dtype, m, n, inter):
     assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
 
 
+@pytest.mark.parametrize("m,n,k,out_dtype,add", [
+    (128, 128, 64, torch.bfloat16, False), (130, 264, 72, torch.bfloat16, False), (1, 40, 8, torch.float32, False),
+    (300, 331, 200, torch.float32, False), (2048, 2048, 2048, torch.bfloat16, False), (257, 6144, 2048, torch.bfloat16, False),
+    (512, 2048, 6144, torch.float32, True), (150, 96, 224, torch.float32, True)])
+def test_linear_tcgen05(kernels, m, n, k, out_dtype, add):
+    """The TMA + tcgen05 + tensor-memory product: whole and ragged tiles, both epilogues, no wait given up."""
+    x, w = rand((m, k), torch.bfloat16, 48, 0.5), rand((n, k), torch.bfloat16, 49, 0.1)
+    expected = x.double() @ w.double().T
+    if add:
+        out = rand((m, n), torch.float32, 50)
+        expected = expected + out.double()
+    else:
+        out = torch.full((m, n), 7.0, dtype=out_dtype).cuda()
+    kernels.linear_tcgen05(x, w, out, add=add)
+    kernels.check_device_errors(x.device)
+    bound = 1e-3 if out_dtype == torch.float32 else 1.5e-2
+    assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
+
+
 def records_tensor(rows):
     words = [struct.unpack("<8i", struct.pack("<ffiIIiii", t, p, k, seed & 0xFFFFFFFF, seed >> 32, 0, 0, 0))
              for (t, p, k, seed) in rows]
