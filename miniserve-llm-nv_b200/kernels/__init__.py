@@ -210,8 +210,17 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     _want(query_start, "query_start", torch.int32, (n_requests + 1,))
     _want(context_lens, "context_lens", torch.int32, (n_requests,))
     lib = library()
+    n_kv = k_pool.shape[1]
+    if (USE_TCGEN05_ATTENTION and q.dtype == torch.bfloat16 and n_q % n_kv == 0 and max_query_len * (n_q // n_kv) > 16
+            and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(k_pool.shape[2]))):
+        # prompt portions: the TMA + tcgen05 + tensor-memory kernel
+        _check(lib.ms_paged_attention_tcgen05(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(block_tables), _i(block_tables.shape[1]),
+            _ptr(query_start), _ptr(context_lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
+            _i(window if window else 0), _ptr(out), _i(n_requests), _i(max_query_len), _i(n),
+            _ptr(device_error_flag(q.device)), _stream()))
+        return
     if q.dtype == torch.bfloat16 and lib.ms_attention_mma_supports(_i(head_dim)):
-        n_kv = k_pool.shape[1]
         splits = lib.ms_attention_mma_splits(_i(head_dim), _i(n_requests), _i(n_kv), _i(n_q), _i(max_query_len),
                                              _i(max_context_len))
         part_o = part_lse = None
@@ -271,6 +280,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
 # Products of 128 rows and more go to cuBLAS unless this is set (environment MINISERVE_B200_TCGEN05_GEMM=1):
 # the library's own tcgen05 kernel is correct but reaches 60-75 % of cuBLAS' speed so far.
 USE_TCGEN05_GEMM = __import__("os").environ.get("MINISERVE_B200_TCGEN05_GEMM", "0") == "1"
+
+# Prompt portions in bfloat16 run the tcgen05 attention kernel where it takes the sizes (head size 64 or 128,
+# group size dividing 128, pages of 8..128 tokens); MINISERVE_B200_TCGEN05_ATTENTION=0 keeps them on the
+# mma.sync kernel.
+USE_TCGEN05_ATTENTION = __import__("os").environ.get("MINISERVE_B200_TCGEN05_ATTENTION", "1") == "1"
 
 _error_flags: dict = {}
 
