@@ -30,7 +30,7 @@ MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size
              hidden_act="silu", attention_bias=False, tie_word_embeddings=True)
 CONTEXT = 4096           # tokens each request holds at the end of the timed decode steps
 PREFILL_TOKENS = 2048
-PAGE_SIZE = 16
+PAGE_SIZE = 64           # tokens per cache page (one TMA box per page and key tile in the prompt attention)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 

@@ -5,7 +5,7 @@
 // value tile.  Keys are walked in tiles of 128:
 //   warp 0      one thread issues TMA loads: the query rows once (a 3-d box over tokens x heads x head
 //               size), then per tile one box per cache page for K and for V, looked up in the request's
-//               block table, into a two-stage ring in shared memory (128-byte swizzle);
+//               block table, into a ring of three or four tiles in shared memory (128-byte swizzle);
 //   warp 1      one thread issues tcgen05.mma:  S = Q K^T  into one of two score buffers in tensor memory
 //               (issued one tile ahead, so it overlaps the softmax of the tile before), and  PV = P V  with
 //               P read from tensor memory and V as an MN-major operand from shared memory;
@@ -24,10 +24,20 @@ namespace t5a {
 
 using namespace ms::t5;
 
-constexpr int ROWS = 128, BN = 128, THREADS = 192, KV_STAGES = 2, TMEM_COLUMNS = 512;
+constexpr int ROWS = 128, BN = 128, THREADS = 192, TMEM_COLUMNS = 512;
+// key/value tiles in shared memory: three for head size 128 (32 KB of queries + 3 x 64 KB), four for 64
+template <int D> constexpr int kv_stages() { return D == 128 ? 3 : 4; }
+
+// 2^x by the special-function unit (ex2.approx): relative error about 2^-22, -inf gives 0.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int D>
 struct Layout {
+  static constexpr int KV_STAGES = kv_stages<D>();
   static constexpr int DBLOCKS = D / 64;                 // 128-byte column blocks of a row
   static constexpr int Q_BYTES = ROWS * D * 2;
   static constexpr int TILE_BYTES = BN * D * 2;          // one K or V tile
@@ -42,6 +52,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                          int page_size, int n_q, int n_kv, float scale_log2, int window,
                          __nv_bfloat16* __restrict__ out, int* __restrict__ error_flag) {
   using L = Layout<D>;
+  constexpr int KV_STAGES = L::KV_STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* q_s = smem;
@@ -165,7 +176,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             tmem_fence_after();
             issue_scores(j + 1);
           }
-          ok = mbar_wait(&p_full[b], phase, error_flag, 15) && mbar_wait(&v_full[stage], phase, error_flag, 16);
+          ok = mbar_wait(&p_full[b], phase, error_flag, 15) &&
+               mbar_wait(&v_full[stage], (j / KV_STAGES) & 1, error_flag, 16);
           if (!ok) break;
           tmem_fence_after();
 #pragma unroll
@@ -204,19 +216,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         tmem_load_32_nowait(s_addr + 64, *reinterpret_cast<float(*)[32]>(&v[64]));
         tmem_load_32_nowait(s_addr + 96, *reinterpret_cast<float(*)[32]>(&v[96]));
         tmem_load_wait();
-        float tile_max = -INFINITY;
+        // eight independent partial maxima (and sums below): a single running value would chain 128 operations
+        float part_max[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part_max[e] = -INFINITY;
         if (full) {
 #pragma unroll
-          for (int i = 0; i < BN; ++i) tile_max = fmaxf(tile_max, v[i]);
+          for (int i = 0; i < BN; ++i) part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
         } else {
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
             const int key = key0 + i;
             const bool visible = key <= pos && (window <= 0 || key > pos - window);
             if (!visible) v[i] = -INFINITY;
-            tile_max = fmaxf(tile_max, v[i]);
+            part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
           }
         }
+        const float tile_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
+                                     fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
         const float candidate = fmaxf(m_used, tile_max);
         // rescale when the maximum has grown by more than 8 in the exponent (or was still -inf)
         const bool grow = candidate != -INFINITY && (m_used == -INFINITY || (candidate - m_used) * scale_log2 > 8.f);
@@ -242,20 +259,24 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           }
         }
         const float base = m_used == -INFINITY ? 0.f : m_used * scale_log2;
-        float sum = 0.f;
+        float part_sum[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) part_sum[e] = 0.f;
 #pragma unroll
         for (int c = 0; c < BN; c += 32) {
           unsigned packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(v[c + i] * scale_log2 - base);
-            const float p1 = exp2f(v[c + i + 1] * scale_log2 - base);
-            sum += p0 + p1;
+            const float p0 = fast_exp2(v[c + i] * scale_log2 - base);
+            const float p1 = fast_exp2(v[c + i + 1] * scale_log2 - base);
+            part_sum[(i >> 1) & 7] += p0 + p1;
             const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
             packed[i / 2] = *reinterpret_cast<const unsigned*>(&pair);
           }
           tmem_store_16(s_addr + c / 2, packed);
         }
+        const float sum = ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3])) +
+                          ((part_sum[4] + part_sum[5]) + (part_sum[6] + part_sum[7]));
         tmem_store_wait();
         tmem_fence_before();
         mbar_arrive(&p_full[b]);
