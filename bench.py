@@ -278,18 +278,25 @@ def main() -> int:
     # ---------------------------------------------------------------- end to end through the engine loop
     engine = build_engine(runtime)
     for index in range(args.batch):
-        engine.submit(f"e{index}", prompt(CONTEXT - args.steps - warmup - 1),
-                      SamplingParams(temperature=0.0, max_new_tokens=args.steps + warmup + 1))
+        # prompts finish on different steps (two fit a step's token budget): the margin keeps all of them
+        # decoding through the timed steps and inside the context limit
+        engine.submit(f"e{index}", prompt(CONTEXT - args.steps - warmup - 8),
+                      SamplingParams(temperature=0.0, max_new_tokens=args.steps + warmup + 8))
     while any(not s.is_decoding for s in engine.sequences.values()):
         engine.step()
     for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
+    step_times = []
     started = time.perf_counter()
     for _ in range(args.steps):
-        engine.step()
+        before_step = time.perf_counter()
+        engine.step()                      # returns after the step's token ids are on the host
+        step_times.append(time.perf_counter() - before_step)
     torch.cuda.synchronize()
     e2e_seconds = (time.perf_counter() - started) / args.steps
+    slow_steps = [index for index, t in enumerate(step_times) if t > 2 * sorted(step_times)[len(step_times) // 2]]
+    step_times.sort()
     graph = step_function.graphs[next(b for b in sorted(step_function.graphs) if b >= args.batch)]
     h2d_bytes = graph.host.numel() * 4
     d2h_bytes = args.batch * 4
@@ -307,7 +314,9 @@ def main() -> int:
                    "context_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "single GPU",
                    "decode_execution": "cuda_graph", "l2": "inputs larger than L2 (weights + cache read every step)"},
         "e2e": {"value": round(args.batch / e2e_seconds, 1), "unit": "tokens/s", "ms_per_step": round(e2e_seconds * 1e3, 4),
-                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes,
+                "ms_median_step": round(step_times[len(step_times) // 2] * 1e3, 4),
+                "ms_slowest_step": round(step_times[-1] * 1e3, 4), "slow_steps": slow_steps},
         "gpu_launches": launches * args.steps,
         "prefill": {"value": round(PREFILL_TOKENS / prefill_seconds, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_seconds * 1e3, 3),

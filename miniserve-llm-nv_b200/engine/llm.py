@@ -25,6 +25,7 @@ def build_engine(runtime: Runtime) -> Engine:
                           enable_chunked_prefill=config.enable_chunked_prefill,
                           prefill_chunk_size=config.prefill_chunk_size)
     executor = DeviceExecutor(runtime.step_function, runtime.storage)
+    runtime.step_function.capture_decode_graphs(config.max_num_seqs)
     return Engine(runtime.manager, scheduler, executor, vocab_size=runtime.model.spec.vocab_size,
                   max_model_len=runtime.max_model_len, max_pending_requests=config.max_pending_requests)
 

@@ -227,14 +227,29 @@ class StepFunction:
         self.eager_steps += 1
         return self.model.forward(ctx, self.storage)
 
-    def _replay(self, entries, reservation, draw_index) -> torch.Tensor:
-        n = len(entries)
+    def graph_for(self, n: int) -> "DecodeGraph":
+        """The captured decode step of the smallest bucket that holds ``n`` rows (captured on first use)."""
         rows = next(b for b in DECODE_BUCKETS if b >= n)
         graph = self.graphs.get(rows)
         if graph is None:
             if self.graph_pool is None:
                 self.graph_pool = torch.cuda.graph_pool_handle()
             graph = self.graphs[rows] = DecodeGraph(self, rows)
+        return graph
+
+    def capture_decode_graphs(self, max_rows: int) -> None:
+        """Captures every bucket up to ``max_rows`` now, so that no step pays for a capture later
+        (MiniServe captures its batched graphs at start-up too: miniserve/engine/graph.py:689-729)."""
+        if not self.use_graphs:
+            return
+        for bucket in DECODE_BUCKETS:
+            self.graph_for(min(bucket, max_rows))
+            if bucket >= max_rows:
+                break
+
+    def _replay(self, entries, reservation, draw_index) -> torch.Tensor:
+        n = len(entries)
+        graph = self.graph_for(n)
         manager, ps = self.manager, self.manager.page_size
         limit, scratch = self.storage.num_pages, self.storage.scratch_page
         o, host = graph.offsets, graph.host_np
