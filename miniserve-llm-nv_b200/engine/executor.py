@@ -31,6 +31,8 @@ class DeviceExecutor:
             return []
         if self.step_function.last_tokens is not None:      # a replayed graph sampled already
             return self.step_function.last_tokens.cpu().tolist()
+        # an eager step may have run kernels with bounded waits (the tcgen05 attention of prompt portions)
+        kernels.check_device_errors(self.device)
         meta = torch.tensor([[s.slot for s in samples], [s.draw_index for s in samples]], dtype=torch.int32,
                             pin_memory=self.device.type == "cuda").to(self.device, non_blocking=True)
         chosen = torch.empty(len(samples), dtype=torch.int32, device=self.device)

@@ -49,8 +49,15 @@ def _check(code: int) -> None:
     launch_count += 1
 
 
+_device_index: Optional[int] = None
+
+
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    """torch's current stream on the library's device (the raw handle: this is called for every launch)."""
+    global _device_index
+    if _device_index is None:
+        _device_index = torch.cuda.current_device()
+    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(_device_index))
 
 
 def _ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
@@ -299,7 +306,10 @@ def device_error_flag(device: torch.device) -> torch.Tensor:
 
 def check_device_errors(device: torch.device) -> None:
     """Raises if a kernel gave up waiting since the last check (synchronises the device)."""
-    flag = device_error_flag(device)
+    key = torch.device(device).index or 0
+    if key not in _error_flags:
+        return                      # no kernel with bounded waits has run on this device
+    flag = _error_flags[key]
     code = int(flag.item())
     if code:
         flag.zero_()

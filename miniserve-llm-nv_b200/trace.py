@@ -38,6 +38,7 @@ def main(argv=None) -> int:
     import numpy  # noqa: F401  (the logits are written through it)
     import torch
 
+    from . import kernels
     from .config.engine_config import EngineConfig
     from .engine.runtime import build_runtime
     from .engine.step import StepEntry
@@ -72,6 +73,7 @@ def main(argv=None) -> int:
                     logits.cpu().numpy().astype("<f4", copy=False).tofile(out_dir / f"{step}.f32")
                 else:
                     torch.cuda.synchronize()
+                kernels.check_device_errors(step_function.device)
             except BaseException:
                 manager.abort(reservation)
                 raise
