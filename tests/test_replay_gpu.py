@@ -86,6 +86,29 @@ def test_cuttings_match_plain(tmp_path, dtype, name, page_size, cutting):
     print(f"worst error / bound = {worst:.3f}")
 
 
+@pytest.mark.parametrize("name,page_size", [("d", 16), ("b", 8)])
+def test_whole_prompts_through_the_tcgen05_products(tmp_path, monkeypatch, name, page_size):
+    """The library's own tcgen05 matrix product in place of cuBLAS for portions of 128 rows and more."""
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200 import kernels
+
+    monkeypatch.setattr(kernels, "USE_TCGEN05_GEMM", True)
+    vocab = helpers.TINY[name]["vocab_size"]
+    requests = {f"r{i}": helpers.random_tokens(vocab, n, seed=300 + i) for i, n in enumerate((128, 150, 333))}
+    steps = helpers.cut_whole(requests)
+    folder = helpers.make_folder(tmp_path, name, seed=2)
+    runtime = build(folder, "bfloat16", (400 + page_size - 1) // page_size, page_size)
+    before = kernels.launch_count
+    got = helpers.collect(steps, replay(runtime, steps))
+    kernels.check_device_errors(runtime.model.device)
+    assert kernels.launch_count > before
+    for rid, tokens in requests.items():
+        expected = helpers.oracle_logits(folder, tokens)
+        bound = error_bounds("bfloat16", expected)
+        for position, row in got[rid].items():
+            assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name,page_size", [("b", 8), ("d", 16)])
 def test_long_decoding_and_first_tokens(tmp_path, dtype, name, page_size):
