@@ -451,21 +451,38 @@ using namespace ms;
 // Head sizes this kernel is built for; other sizes use the general kernel.
 MS_EXPORT int ms_attention_mma_supports(int head_dim) { return head_dim == 32 || head_dim == 64 || head_dim == 128; }
 
-// In how many parts the keys of a step of single tokens should be split: as many as fill the GPU
-// with one wave of thread blocks (a second, partly filled wave would double the time), each part
-// keeping at least 128 keys; 1 for anything else.
+// In how many parts the keys of a step of single tokens should be split (1 for anything else).  A merge
+// inside the attention kernel (the last split to finish merges, found by a ticket counter) was tried and
+// was slower than the separate merge kernel: the memory fence every block then needs costs more.
 MS_EXPORT int ms_attention_mma_splits(int d, int n_requests, int n_kv, int n_q, int max_query_len, int max_context_len) {
   if (n_kv <= 0 || (long long)max_query_len * (n_q / n_kv) > 16) return 1;
   int slots = 0;
-  if (d == 128) slots = attention_block_slots<128, 1, 32, 1, 3>();
-  else if (d == 64) slots = attention_block_slots<64, 1, 64, 1, 3>();
-  else if (d == 32) slots = attention_block_slots<32, 1, 64, 1, 3>();
+  if (d == 128) slots = attention_block_slots<128, 1, 32, 1, 2>();
+  else if (d == 64) slots = attention_block_slots<64, 1, 64, 1, 2>();
+  else if (d == 32) slots = attention_block_slots<32, 1, 64, 1, 2>();
   const int base = n_requests * n_kv;
   if (slots <= 0 || base <= 0) return 1;
-  int splits = slots / base;
-  const int by_length = max_context_len / 128;
-  if (splits > by_length) splits = by_length;
-  if (splits > 64) splits = 64;
+  // The blocks are one warp each, so what hides their latencies is how many of them are resident: pick the
+  // smallest split count whose blocks fill whole waves to at least 90 % (each part keeping 128 keys or
+  // more), else the count that fills them best.
+  int limit = max_context_len / 128;
+  if (limit > 64) limit = 64;
+  if (limit < 1) limit = 1;
+  int splits = 1;
+  double best = 0.0;
+  for (int s = 1; s <= limit; ++s) {
+    const long long blocks = (long long)base * s;
+    const long long waves = (blocks + slots - 1) / slots;
+    const double fill = (double)blocks / (double)(waves * slots);
+    if (fill >= 0.9) {
+      splits = s;
+      break;
+    }
+    if (fill > best + 1e-9) {
+      best = fill;
+      splits = s;
+    }
+  }
   return splits < 1 ? 1 : splits;
 }
 
@@ -484,16 +501,16 @@ MS_EXPORT int ms_paged_attention_mma(const void* q, const void* k_pool, const vo
   MS_REQUIRE(page_size > 0 && max_query_len > 0, "attention: page size %d, longest portion %d", page_size, max_query_len);
   MS_REQUIRE(num_splits >= 1 && num_splits <= 64 && (num_splits == 1 || (part_o && part_lse)),
              "attention: %d splits (1..64) need scratch", num_splits);
-  // Steps of single tokens: one warp per block (its 16 rows hold the group's query heads), three tiles in
-  // shared memory.  Prompt portions: four warps of 32 rows each, two tiles.
+  // Steps of single tokens: one warp per block (its 16 rows hold the group's query heads), two tiles in
+  // shared memory (small blocks: more of them are resident).  Prompt portions: four warps of 32 rows each, two tiles.
   const bool small = (long long)max_query_len * (n_q / n_kv) <= 16;
 #define MS_ATTENTION_CASE(D, W, BN, MT, STAGES)                                                                       \
   return launch_attention_mma<D, W, BN, MT, STAGES>(q, k_pool, v_pool, block_tables, table_stride, query_start,       \
                                                     context_lens, page_size, n_q, n_kv, scale, window, out, part_o,  \
                                                     part_lse, num_splits, n_requests, max_query_len, n_tokens, stream)
-  if (d == 128) { if (small) { MS_ATTENTION_CASE(128, 1, 32, 1, 3); } else { MS_ATTENTION_CASE(128, 4, 64, 2, 2); } }
-  if (d == 64) { if (small) { MS_ATTENTION_CASE(64, 1, 64, 1, 3); } else { MS_ATTENTION_CASE(64, 4, 64, 2, 2); } }
-  if (d == 32) { if (small) { MS_ATTENTION_CASE(32, 1, 64, 1, 3); } else { MS_ATTENTION_CASE(32, 4, 64, 2, 2); } }
+  if (d == 128) { if (small) { MS_ATTENTION_CASE(128, 1, 32, 1, 2); } else { MS_ATTENTION_CASE(128, 4, 64, 2, 2); } }
+  if (d == 64) { if (small) { MS_ATTENTION_CASE(64, 1, 64, 1, 2); } else { MS_ATTENTION_CASE(64, 4, 64, 2, 2); } }
+  if (d == 32) { if (small) { MS_ATTENTION_CASE(32, 1, 64, 1, 2); } else { MS_ATTENTION_CASE(32, 4, 64, 2, 2); } }
 #undef MS_ATTENTION_CASE
   MS_FAIL("attention: the tensor-core kernel is not built for head size %d", d);
 }
