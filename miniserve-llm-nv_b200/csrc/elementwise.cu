@@ -270,9 +270,19 @@ MS_EXPORT int ms_qk_norm_rope_append(const void* qkv, int dtype, const int* slot
   MS_REQUIRE(blocks < 2147483647LL, "qk_norm_rope_append: %lld heads in one launch is too many", items);
   const bool vector_ok = d % 8 == 0 && d <= 256 && (cos_sin == nullptr || interleaved || rotary_dim % 16 == 0);
   if (vector_ok) {
-    MS_DISPATCH(dtype, (ms::launch(qk_norm_rope_append_vec_kernel<T>, (unsigned)blocks, warps * 32, 0, stream, 
-                           (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, cos_sin, rotary_dim,
-                           interleaved, (T*)k_pool, (T*)v_pool, page_size, n_q, n_kv, d, (T*)q_out, n_tokens)));
+    const int lanes_needed = d / 8;
+    const bool pow2 = (lanes_needed & (lanes_needed - 1)) == 0;
+    const int lanes = pow2 ? lanes_needed : 32;            // lanes per head
+    const int heads_per_warp = 32 / lanes;
+    const long long warps_needed = (items + heads_per_warp - 1) / heads_per_warp;
+    const long long vec_blocks = (warps_needed + warps - 1) / warps;
+#define MS_ROPE_VEC(L)                                                                                              \
+  MS_DISPATCH(dtype, (ms::launch(qk_norm_rope_append_vec_kernel<T, L>, (unsigned)vec_blocks, warps * 32, 0, stream, \
+                                 (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, cos_sin, rotary_dim,  \
+                                 interleaved, (T*)k_pool, (T*)v_pool, page_size, n_q, n_kv, d, (T*)q_out, n_tokens)))
+    if (lanes == 2) { MS_ROPE_VEC(2); } else if (lanes == 4) { MS_ROPE_VEC(4); } else if (lanes == 8) { MS_ROPE_VEC(8); }
+    else if (lanes == 16) { MS_ROPE_VEC(16); } else { MS_ROPE_VEC(32); }
+#undef MS_ROPE_VEC
     MS_CHECK_LAUNCH("qk_norm_rope_append");
     return 0;
   }

@@ -101,10 +101,12 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
 }
 
 // ---------------------------------------------------------------- q/k norm + rotation + cache append
-// One warp per (token, head); lane l holds elements 8l .. 8l+7 of the head (d <= 256, d % 8 == 0).
-// Half-split rotation needs rotary_dim % 16 == 0 so that an element's partner sits at the same place
-// in another lane; interleaved pairs sit within a lane.
-template <typename T>
+// A group of d / 8 lanes per (token, head); lane l of the group holds elements 8l .. 8l+7 of the head.
+// LANES is the group size: 32 / LANES heads share a warp when d / 8 is a power of two, else a head has
+// the warp to itself (LANES = 32, lanes beyond d / 8 idle).  d <= 256, d % 8 == 0.  Half-split rotation
+// needs rotary_dim % 16 == 0 so that an element's partner sits at the same place in another lane of the
+// group; interleaved pairs sit within a lane.
+template <typename T, int LANES>
 __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const int* __restrict__ slots,
                                                const void* __restrict__ q_weight, const void* __restrict__ k_weight,
                                                int weight_dtype, float eps, const float* __restrict__ cos_sin,
@@ -113,61 +115,63 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
                                                T* __restrict__ q_out, int n_tokens) {
   grid_dependency_wait();
   grid_dependency_launch();
+  constexpr int HEADS_PER_WARP = 32 / LANES;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LANES, sub_lane = lane % LANES;
   const int heads = n_q + 2 * n_kv;
-  const long long item = (long long)blockIdx.x * warps_per_block + warp;
-  if (item >= (long long)n_tokens * heads) return;
-  const int n = (int)(item / heads), head = (int)(item % heads);
+  const long long total = (long long)n_tokens * heads;
+  const long long item = ((long long)blockIdx.x * warps_per_block + warp) * HEADS_PER_WARP + sub;
+  // No early exit: the lanes of a warp may serve different heads and all of them take part in the shuffles.
+  const bool item_ok = item < total;
+  const int n = item_ok ? (int)(item / heads) : 0, head = item_ok ? (int)(item % heads) : 0;
   const T* src = qkv + ((size_t)n * heads + head) * d;
-  const int c0 = lane * 8;
-  const bool active = c0 < d;
+  const int c0 = sub_lane * 8;
+  bool active = item_ok && c0 < d;
 
-  T* dst;
+  T* dst = nullptr;
   const void* weight = nullptr;
-  bool rotate = false;
+  bool is_value = false;
   if (head < n_q) {
     dst = q_out + ((size_t)n * n_q + head) * d;
     weight = q_weight;
-    rotate = cos_sin != nullptr;
   } else {
-    const int slot = slots[n];
-    if (slot < 0) return;
-    const int page = slot / page_size, offset = slot % page_size;
-    const bool is_key = head < n_q + n_kv;
-    const int kv_head = is_key ? head - n_q : head - n_q - n_kv;
-    dst = (is_key ? k_pool : v_pool) + (((size_t)page * n_kv + kv_head) * page_size + offset) * d;
-    if (!is_key) {
-      if (active) *reinterpret_cast<uint4*>(dst + c0) = *reinterpret_cast<const uint4*>(src + c0);
-      if (active && sizeof(T) == 4)
-        *reinterpret_cast<uint4*>(dst + c0 + 4) = *reinterpret_cast<const uint4*>(src + c0 + 4);
-      return;
+    const int slot = item_ok ? slots[n] : -1;
+    if (slot < 0) {
+      active = false;
+    } else {
+      const int page = slot / page_size, offset = slot % page_size;
+      const bool is_key = head < n_q + n_kv;
+      const int kv_head = is_key ? head - n_q : head - n_q - n_kv;
+      dst = (is_key ? k_pool : v_pool) + (((size_t)page * n_kv + kv_head) * page_size + offset) * d;
+      is_value = !is_key;
+      weight = is_key ? k_weight : nullptr;
     }
-    weight = k_weight;
-    rotate = cos_sin != nullptr;
   }
+  const bool rotate = cos_sin != nullptr && !is_value;
 
   Vec8 x;
 #pragma unroll
   for (int e = 0; e < 8; ++e) x.v[e] = 0.f;
   if (active) x = load8(src + c0);
-  if (weight) {
+  {
     float sum_sq = 0.f;
 #pragma unroll
     for (int e = 0; e < 8; ++e) sum_sq += x.v[e] * x.v[e];
-    sum_sq = warp_sum(sum_sq);
-    const float inv = 1.0f / sqrtf(sum_sq / (float)d + eps);
-    if (active) {
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, o);
+    if (weight && active) {
+      const float inv = 1.0f / sqrtf(sum_sq / (float)d + eps);
       const Vec8 w = load8_any(weight, weight_dtype, c0);
 #pragma unroll
       for (int e = 0; e < 8; ++e) x.v[e] = x.v[e] * inv * w.v[e];
     }
   }
-  if (rotate) {
+  if (cos_sin != nullptr) {                                  // uniform: every lane takes part in the shuffles
     const int half = rotary_dim >> 1;
     const float* table = cos_sin + (size_t)n * rotary_dim;       // [half][2] floats
     if (interleaved) {
-      if (active && c0 < rotary_dim) {
+      if (rotate && active && c0 < rotary_dim) {
         const Vec8 cs = load8(table + c0);                       // (cos, sin) of pairs c0/2 .. c0/2+3
         Vec8 y;
 #pragma unroll
@@ -180,13 +184,13 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
       }
     } else {
       const int lanes_half = half >> 3;                          // lanes that hold one half of the rotary part
-      const bool in_rotary = active && c0 < rotary_dim;
       const bool first = c0 < half;
-      const int partner_lane = first ? lane + lanes_half : lane - lanes_half;
+      const int partner_sub_lane = first ? sub_lane + lanes_half : sub_lane - lanes_half;
+      const int partner_lane = sub * LANES + (partner_sub_lane & (LANES - 1));
       Vec8 partner;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) partner.v[e] = __shfl_sync(0xffffffffu, x.v[e], partner_lane & 31);
-      if (in_rotary) {
+      for (int e = 0; e < 8; ++e) partner.v[e] = __shfl_sync(0xffffffffu, x.v[e], partner_lane);
+      if (rotate && active && c0 < rotary_dim) {
         const int j0 = first ? c0 : c0 - half;
         const Vec8 cs_a = load8(table + 2 * j0);
         const Vec8 cs_b = load8(table + 2 * j0 + 8);
@@ -200,7 +204,15 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
       }
     }
   }
-  if (active) store8(dst + c0, x);
+  if (active) {
+    if (is_value) {
+      // values are copied bit for bit
+      *reinterpret_cast<uint4*>(dst + c0) = *reinterpret_cast<const uint4*>(src + c0);
+      if (sizeof(T) == 4) *reinterpret_cast<uint4*>(dst + c0 + 4) = *reinterpret_cast<const uint4*>(src + c0 + 4);
+    } else {
+      store8(dst + c0, x);
+    }
+  }
 }
 
 // ---------------------------------------------------------------- gated activation
