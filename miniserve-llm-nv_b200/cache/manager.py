@@ -16,6 +16,8 @@ page depend on nothing but the tokens before it.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+
+import numpy
 from typing import Optional, Sequence
 
 from ..parts.base import PagedKVNeed, StateNeed
@@ -211,14 +213,12 @@ class CacheManager:
             new_pages = [self.allocators[g].allocate(max(n, 0)) for g, n in enumerate(fresh)]
             tables = [table + new for table, new in zip(entry.tables, new_pages)]
             slots = []
+            positions = numpy.arange(entry.length, end, dtype=numpy.int64)
             for table in tables:
-                row = []
-                for position in range(entry.length, end):
-                    page = table[position // self.page_size]
-                    if page == RELEASED:
-                        raise RuntimeError("a new token falls into a page that was given back")
-                    row.append(page * self.page_size + position % self.page_size)
-                slots.append(row)
+                pages = numpy.asarray(table, dtype=numpy.int64)[positions // self.page_size]
+                if (pages == RELEASED).any():
+                    raise RuntimeError("a new token falls into a page that was given back")
+                slots.append((pages * self.page_size + positions % self.page_size).tolist())
             reserved.append(ReservedItem(entry.request_id, entry.length, end, new_pages, tables, slots))
         reservation = StepReservation(self._next_step, reserved)
         self._next_step += 1

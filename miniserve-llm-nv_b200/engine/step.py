@@ -131,72 +131,81 @@ class StepFunction:
 
     # ------------------------------------------------------------------ batch building
     def build_context(self, entries: Sequence[StepEntry], reservation: StepReservation) -> StepContext:
+        import numpy
+
         manager, ps = self.manager, self.manager.page_size
         if len(entries) != len(reservation.items):
             raise ValueError("the reservation was made for other entries")
-        tokens: list[int] = []
-        positions: list[int] = []
-        request_of_token: list[int] = []
+        int32 = numpy.int32
+        token_parts, position_parts, request_parts, slot_parts = [], [], [], None
         query_start = [0]
         context_lens: list[int] = []
         state_slots: list[int] = []
         logit_rows: list[int] = []
         n_groups = len(manager.paged_needs)
-        slots: list[list[int]] = [[] for _ in range(n_groups)]
+        slot_parts = [[] for _ in range(n_groups)]
         width = 1
+        n = 0
         for row, (entry, item) in enumerate(zip(entries, reservation.items)):
-            if entry.request_id != item.request_id or len(entry.tokens) != item.end - item.start:
+            count = len(entry.tokens)
+            if entry.request_id != item.request_id or count != item.end - item.start:
                 raise ValueError(f"entry {row} does not match its reservation")
             if item.end > self.max_model_len:
                 raise ValueError(f"request {entry.request_id!r} would reach {item.end} tokens; the limit is {self.max_model_len}")
-            for token in entry.tokens:
-                if not 0 <= int(token) < self.vocab_size:
-                    raise ValueError(f"token id {token} outside the vocabulary of {self.vocab_size}")
-            base = len(tokens)
+            ids = numpy.asarray(entry.tokens, dtype=numpy.int64)
+            if count and (int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size):
+                raise ValueError(f"a token id of request {entry.request_id!r} lies outside the vocabulary of {self.vocab_size}")
             for index in entry.want:
-                if not 0 <= index < len(entry.tokens):
-                    raise ValueError(f"wanted index {index} outside the {len(entry.tokens)} tokens of the entry")
-                logit_rows.append(base + index)
-            tokens.extend(int(t) for t in entry.tokens)
-            positions.extend(range(item.start, item.end))
-            request_of_token.extend([row] * len(entry.tokens))
-            query_start.append(len(tokens))
+                if not 0 <= index < count:
+                    raise ValueError(f"wanted index {index} outside the {count} tokens of the entry")
+                logit_rows.append(n + index)
+            token_parts.append(ids.astype(int32))
+            position_parts.append(numpy.arange(item.start, item.end, dtype=int32))
+            request_parts.append(numpy.full(count, row, dtype=int32))
+            n += count
+            query_start.append(n)
             context_lens.append(item.end)
             state_slots.append(manager.requests[entry.request_id].slot)
             for group in range(n_groups):
-                slots[group].extend(item.slots[group])
+                slot_parts[group].append(numpy.asarray(item.slots[group], dtype=int32))
                 width = max(width, len(item.tables[group]))
 
         scratch = self.storage.scratch_page
         limit = self.storage.num_pages
-        tables: list[list[int]] = []
+        r = len(entries)
+        tables = []
+        slots = []
         for group in range(n_groups):
-            flat: list[int] = []
-            for item in reservation.items:
-                table = item.tables[group]
-                for page in table:
-                    if page != RELEASED and not 0 <= page < limit:
-                        raise ValueError(f"page {page} outside the pool of {limit}")
-                flat.extend(scratch if page == RELEASED else page for page in table)
-                flat.extend([scratch] * (width - len(table)))
-            tables.append(flat)
-            for slot in slots[group]:
-                if not 0 <= slot < limit * ps:
-                    raise ValueError(f"slot {slot} outside the pool")
+            table = numpy.full((r, width), scratch, dtype=int32)
+            for row, item in enumerate(reservation.items):
+                pages = numpy.asarray(item.tables[group], dtype=int32)
+                pages = numpy.where(pages == RELEASED, scratch, pages)
+                if pages.size and (int(pages.min()) < 0 or int(pages.max()) > limit):
+                    raise ValueError(f"a page of request {item.request_id!r} lies outside the pool of {limit}")
+                table[row, :pages.size] = pages
+            tables.append(table.reshape(-1))
+            group_slots = numpy.concatenate(slot_parts[group]) if slot_parts[group] else numpy.zeros(0, dtype=int32)
+            if group_slots.size and (int(group_slots.min()) < 0 or int(group_slots.max()) >= limit * ps):
+                raise ValueError("a slot lies outside the pool")
+            slots.append(group_slots)
 
-        n, r = len(tokens), len(entries)
-        pieces = [tokens, positions, request_of_token, query_start, context_lens, state_slots, logit_rows]
+        empty = numpy.zeros(0, dtype=int32)
+        pieces = [numpy.concatenate(token_parts) if token_parts else empty,
+                  numpy.concatenate(position_parts) if position_parts else empty,
+                  numpy.concatenate(request_parts) if request_parts else empty,
+                  numpy.asarray(query_start, dtype=int32), numpy.asarray(context_lens, dtype=int32),
+                  numpy.asarray(state_slots, dtype=int32), numpy.asarray(logit_rows, dtype=int32)]
         for group in range(n_groups):
             pieces += [tables[group], slots[group]]
-        total = sum(len(p) for p in pieces)
+        total = sum(p.size for p in pieces)
         staging = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=self.device.type == "cuda")
+        staging_np = staging.numpy()
         offset = 0
         spans = []
         for piece in pieces:
-            if piece:
-                staging[offset:offset + len(piece)] = torch.tensor(piece, dtype=torch.int32)
-            spans.append((offset, len(piece)))
-            offset += len(piece)
+            staging_np[offset:offset + piece.size] = piece
+            spans.append((offset, piece.size))
+            offset += piece.size
         on_device = staging.to(self.device, non_blocking=True)
         views = [on_device[start:start + length] for start, length in spans]
         group_views = []
