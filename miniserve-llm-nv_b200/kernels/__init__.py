@@ -192,16 +192,21 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                     request_of_token: torch.Tensor, positions: torch.Tensor, query_start: torch.Tensor,
                     context_lens: torch.Tensor, max_query_len: int, max_context_len: int, scale: float,
-                    window: Optional[int], out: torch.Tensor) -> None:
+                    window: Optional[int], out: torch.Tensor, host_query_start: Optional[list] = None) -> None:
     """Causal grouped-query attention of every token over its request's paged keys and values.
 
     q, out ``[N, n_q, d]``; pools of one layer ``[pages, n_kv, page_size, d]``; block_tables
     int32 ``[R, width]``; request_of_token, positions int32 ``[N]``; query_start ``[R + 1]`` and
     context_lens ``[R]`` describe the same batch per request (a request's tokens are the last
     ones of its context).  A token at position p sees keys ``max(0, p - window + 1) .. p`` of
-    its own request, which must be in the pool already.  bfloat16 with a head size the
-    tensor-core kernel is built for runs there (``max_query_len``/``max_context_len`` are upper
-    bounds used to shape its grid); everything else runs the general float32-arithmetic kernel.
+    its own request, which must be in the pool already.
+
+    bfloat16 with a head size the tensor-core kernels are built for runs there
+    (``max_query_len``/``max_context_len`` are upper bounds used to shape their grids); everything
+    else runs the general float32-arithmetic kernel.  With ``host_query_start`` (the same numbers
+    as ``query_start``, on the host) a batch that begins with single-token requests and goes on
+    with prompt portions is run as two launches, so that the single tokens get their keys split
+    over many thread blocks instead of one block walking a whole context.
     """
     n, n_q, head_dim = q.shape
     _want(q, "q")
@@ -218,32 +223,47 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     _want(context_lens, "context_lens", torch.int32, (n_requests,))
     lib = library()
     n_kv = k_pool.shape[1]
-    if (USE_TCGEN05_ATTENTION and q.dtype == torch.bfloat16 and n_q % n_kv == 0 and max_query_len * (n_q // n_kv) > 16
-            and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(k_pool.shape[2]))):
-        # prompt portions: the TMA + tcgen05 + tensor-memory kernel
-        _check(lib.ms_paged_attention_tcgen05(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(block_tables), _i(block_tables.shape[1]),
-            _ptr(query_start), _ptr(context_lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
-            _i(window if window else 0), _ptr(out), _i(n_requests), _i(max_query_len), _i(n),
-            _ptr(device_error_flag(q.device)), _stream()))
+    if q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+        _check(lib.ms_paged_attention_generic(
+            _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
+            _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim),
+            _f(scale), _i(window if window else 0), _ptr(out), _i(n), _stream()))
         return
-    if q.dtype == torch.bfloat16 and lib.ms_attention_mma_supports(_i(head_dim)):
-        splits = lib.ms_attention_mma_splits(_i(head_dim), _i(n_requests), _i(n_kv), _i(n_q), _i(max_query_len),
-                                             _i(max_context_len))
+
+    def run(first: int, last: int, longest: int) -> None:
+        """Requests first .. last - 1 (their tokens are found through query_start, which holds absolute rows)."""
+        tables, starts, lens = block_tables[first:last], query_start[first:last + 1], context_lens[first:last]
+        count = last - first
+        group = n_q // n_kv
+        if (USE_TCGEN05_ATTENTION and longest * group > 16
+                and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(k_pool.shape[2]))):
+            # prompt portions: the TMA + tcgen05 + tensor-memory kernel
+            _check(lib.ms_paged_attention_tcgen05(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(tables), _i(block_tables.shape[1]),
+                _ptr(starts), _ptr(lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
+                _i(window if window else 0), _ptr(out), _i(count), _i(longest), _i(n),
+                _ptr(device_error_flag(q.device)), _stream()))
+            return
+        splits = lib.ms_attention_mma_splits(_i(head_dim), _i(count), _i(n_kv), _i(n_q), _i(longest), _i(max_context_len))
         part_o = part_lse = None
         if splits > 1:
             part_o = torch.empty((n * n_q * splits, head_dim), dtype=torch.float32, device=q.device)
             part_lse = torch.empty((n * n_q * splits,), dtype=torch.float32, device=q.device)
         _check(lib.ms_paged_attention_mma(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]), _ptr(query_start),
-            _ptr(context_lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
-            _i(window if window else 0), _ptr(out), _ptr(part_o), _ptr(part_lse), _i(splits), _i(n_requests),
-            _i(max_query_len), _i(n), _stream()))
-        return
-    _check(lib.ms_paged_attention_generic(
-        _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
-        _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(k_pool.shape[1]), _i(head_dim),
-        _f(scale), _i(window if window else 0), _ptr(out), _i(n), _stream()))
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(tables), _i(block_tables.shape[1]), _ptr(starts), _ptr(lens),
+            _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale), _i(window if window else 0), _ptr(out),
+            _ptr(part_o), _ptr(part_lse), _i(splits), _i(count), _i(longest), _i(n), _stream()))
+
+    leading_single = 0
+    if host_query_start and max_query_len > 1 and len(host_query_start) == n_requests + 1:
+        while (leading_single < n_requests
+               and host_query_start[leading_single + 1] - host_query_start[leading_single] == 1):
+            leading_single += 1
+    if 0 < leading_single < n_requests:
+        run(0, leading_single, 1)
+        run(leading_single, n_requests, max_query_len)
+    else:
+        run(0, n_requests, max_query_len)
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -91,7 +91,8 @@ class Attention(Part):
         attended = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
         kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
                                 ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
-                                ctx.max_context_len, self.scale, self.window, attended)
+                                ctx.max_context_len, self.scale, self.window, attended,
+                                ctx.host_query_start or None)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
         return out

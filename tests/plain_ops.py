@@ -95,7 +95,7 @@ def silu_mul(gate_up, out):
 
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
-                    max_query_len, max_context_len, scale, window, out):
+                    max_query_len, max_context_len, scale, window, out, host_query_start=None):
     n, n_q, d = q.shape
     n_kv, page_size = k_pool.shape[1], k_pool.shape[2]
     group = n_q // n_kv

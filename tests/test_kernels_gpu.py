@@ -172,11 +172,12 @@ def _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, seed):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def _check_attention(kernels, dtype, case, d, window):
+def _check_attention(kernels, dtype, case, d, window, with_host_lengths=False):
     q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = case
     out = torch.empty_like(q)
     kernels.paged_attention(q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
-                            max_ctx, d ** -0.5, window, out)
+                            max_ctx, d ** -0.5, window, out, query_start.tolist() if with_host_lengths else None)
+    kernels.check_device_errors(q.device)
     expected = torch.empty(q.shape, dtype=torch.float64).cuda()
     plain_ops.paged_attention(q.cpu(), k_pool.cpu(), v_pool.cpu(), tables.cpu(), request_of_token.cpu(), positions.cpu(),
                               query_start.cpu(), context_lens.cpu(), max_q, max_ctx, d ** -0.5, window, expected)
@@ -203,6 +204,15 @@ def test_paged_attention_decode_steps(kernels, dtype, n_q, n_kv, d, page_size, w
     _check_attention(kernels, dtype, _attention_case(dtype, n_q, n_kv, d, page_size, lengths, [1] * len(lengths), 21), d, window)
     lengths = [2500]
     _check_attention(kernels, dtype, _attention_case(dtype, n_q, n_kv, d, page_size, lengths, [1], 22), d, window)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,window", [(16, 8, 128, 16, None), (8, 2, 64, 64, None), (6, 2, 32, 8, 40), (4, 4, 48, 4, None)])
+def test_paged_attention_single_tokens_before_portions(kernels, dtype, n_q, n_kv, d, page_size, window):
+    """A mixed step as the scheduler builds it: decoded tokens first, then prompt portions (two launches)."""
+    lengths, query_lens = [700, 1500, 1, 64, 333], [1, 1, 1, 64, 300]
+    _check_attention(kernels, dtype, _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 23), d, window,
+                     with_host_lengths=True)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
