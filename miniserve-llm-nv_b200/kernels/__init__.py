@@ -290,8 +290,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     _want(x, "x", torch.bfloat16)
     _want(weight, "weight", torch.bfloat16)
     _want(out, "out")
+    if m <= STREAM_MAX_ROWS and k % 8 == 0 and _stream_units_per_block(x.device, n, k) >= STREAM_MIN_UNITS:
+        # few rows and a large weight (the output matrix): it streams through the tcgen05 tensor cores
+        linear_stream(x, weight, out)
+        return
     if m <= SKINNY_MAX_ROWS and k % 8 == 0:
-        # few rows (decode steps): the library's weight-streaming kernel
+        # few rows (decode steps): the mma.sync weight-streaming kernel
         _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m), _i(n),
                                         _i(k), _stream()))
         return
@@ -348,6 +352,45 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add
     _want(out, "out", torch.float32 if add else None, (m, n))
     _check(library().ms_gemm_tcgen05(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(1 if add else 0), _i(m),
                                      _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
+
+
+_stream_buffers: dict = {}
+
+# Products of up to STREAM_MAX_ROWS rows whose weight gives every thread block at least STREAM_MIN_UNITS units
+# (256 rows x 64 k, 32 KB each) run the streaming tcgen05 kernel.  Its start and its sum over the blocks
+# that share a tile cost some microseconds, which a smaller weight does not win back: there the mma.sync
+# kernel, several blocks of which share a multiprocessor, is faster.
+STREAM_MAX_ROWS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MAX_ROWS", "16"))
+STREAM_MIN_UNITS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MIN_UNITS", "32"))
+_multiprocessors: dict = {}
+
+
+def _stream_units_per_block(device: torch.device, n: int, k: int) -> float:
+    key = torch.device(device).index or 0
+    if key not in _multiprocessors:
+        _multiprocessors[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return ((n + 255) // 256) * ((k + 63) // 64) / _multiprocessors[key]
+
+
+def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = x @ weight^T`` for up to 64 rows of bfloat16 ``x`` (inner size a multiple of 8) by the
+    library's weight-streaming tcgen05 kernel; ``out`` bfloat16 or float32."""
+    m, k = x.shape
+    n = weight.shape[0]
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, (n, k))
+    _want(out, "out", None, (m, n))
+    key = torch.device(x.device).index or 0
+    tiles = (n + 255) // 256
+    buffers = _stream_buffers.get(key)
+    if buffers is None or buffers[1].numel() < tiles:
+        floats, ints = ctypes.c_longlong(0), ctypes.c_longlong(0)
+        _check(library().ms_gemm_stream_buffers(_i(max(n, 1 << 20)), ctypes.byref(floats), ctypes.byref(ints)))
+        buffers = (torch.empty(floats.value, dtype=torch.float32, device=x.device),
+                   torch.zeros(ints.value, dtype=torch.int32, device=x.device))
+        _stream_buffers[key] = buffers
+    _check(library().ms_gemm_stream(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m), _i(n), _i(k),
+                                    _ptr(buffers[0]), _ptr(buffers[1]), _ptr(device_error_flag(x.device)), _stream()))
 
 
 SKINNY_MAX_ROWS = 8    # above this the weight-streaming kernel re-reads the activations too often

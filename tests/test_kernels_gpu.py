@@ -297,6 +297,29 @@ def test_linear_few_rows(kernels, out_dtype, m, n, k):
         assert torch.allclose(alone[0].double(), out[m // 2].double(), atol=bound * max(1.0, float(expected.abs().max())))
 
 
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 16, 8), (1, 331, 72), (3, 2048, 2048), (8, 4096, 2048), (8, 2048, 6144), (8, 500, 1032),
+                                   (9, 100, 256), (16, 12288, 2048), (17, 384, 200), (33, 640, 6144), (64, 331, 264),
+                                   (5, 40000, 512), (64, 4096, 2048)])
+def test_linear_stream(kernels, out_dtype, m, n, k):
+    """The weight-streaming tcgen05 product: one unit, ragged N and K, tiles split over many blocks (summed
+    through the workspace), every row-count class; twice, so that the tickets are seen to be left clean."""
+    x, w = rand((m, k), torch.bfloat16, 51, 0.5), rand((n, k), torch.bfloat16, 52, 0.1)
+    expected = x.double() @ w.double().T
+    bound = 1e-3 if out_dtype == torch.float32 else 1.5e-2
+    outs = []
+    for _ in range(2):
+        out = torch.full((m, n), 7.0, dtype=out_dtype).cuda()
+        kernels.linear_stream(x, w, out)
+        kernels.check_device_errors(x.device)
+        assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    alone = torch.empty((1, n), dtype=out_dtype).cuda()
+    kernels.linear_stream(x[m // 2:m // 2 + 1].contiguous(), w, alone)
+    assert torch.equal(alone[0], outs[0][m // 2])      # a row does not depend on the rows beside it
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,n,inter", [(1, 72, 200), (8, 2048, 6144), (20, 96, 224), (64, 331, 128), (100, 96, 224), (5, 64, 100)])
 def test_gated_linear(kernels, dtype, m, n, inter):
