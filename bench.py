@@ -28,6 +28,14 @@ MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size
              num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128, vocab_size=151936,
              max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_dropout=0.0,
              hidden_act="silu", attention_bias=False, tie_word_embeddings=True)
+# Other sizes of the same architecture, for runs beside the default one (--shape).
+SHAPES = {
+    "1.7b": {},
+    "8b": dict(hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+               num_key_value_heads=8, tie_word_embeddings=False),
+    "32b": dict(hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                num_key_value_heads=8, tie_word_embeddings=False),
+}
 CONTEXT = 4096           # tokens each request holds at the end of the timed decode steps
 PREFILL_TOKENS = 2048
 PAGE_SIZE = 64           # tokens per cache page (one TMA box per page and key tile in the prompt attention)
@@ -113,7 +121,8 @@ def reference_arm(args) -> int:
         print(json.dumps(result))
         return 0
     line = {
-        "metric": "Qwen3-1.7B bf16 decode tok/s @ batch 8 (context 4096); prefill tok/s @ 2,048 tokens",
+        "metric": f"Qwen3-{args.shape.upper()} bf16 decode tok/s @ batch {args.batch} (context {CONTEXT}); "
+                  f"prefill tok/s @ 2,048 tokens",
         "impl": "reference", "value": result["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random weights)",
@@ -129,6 +138,7 @@ def reference_arm(args) -> int:
 
 
 def main() -> int:
+    global CONTEXT
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=64)
@@ -138,9 +148,13 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="1.7b",
+                        help="layer sizes of another model of the family (the default is the benchmark's)")
+    parser.add_argument("--context", type=int, default=CONTEXT, help="tokens a request holds at the end of the timed steps")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run only a few eager steps of one phase and exit (a small case for ncu; times nothing)")
     args = parser.parse_args()
+    CONTEXT = args.context
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:
@@ -158,7 +172,10 @@ def main() -> int:
     from miniserve_b200.engine.step import StepEntry
     from miniserve_b200.sampling import SamplingParams
 
-    config = dict(MODEL, num_hidden_layers=args.layers)
+    shape = dict(MODEL, **SHAPES[args.shape])
+    if args.layers == MODEL["num_hidden_layers"]:
+        args.layers = shape["num_hidden_layers"]
+    config = dict(shape, num_hidden_layers=args.layers)
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
     pages = max_batch * ((CONTEXT + PAGE_SIZE - 1) // PAGE_SIZE) + 64
     runtime = build_runtime(None, EngineConfig(
@@ -264,6 +281,7 @@ def main() -> int:
     with ClockSampler() as clocks:
         step_seconds, mean_context, launches = measure_decode(args.batch, args.steps)
     clock_summary = clocks.summary()
+    # the output matrix is read whole, tied or not; of the embedding only the rows of the step's tokens
     weight_bytes = 2 * (matrix_params + vocab * h) + 2 * h * (2 * layers + 1) + 2 * 2 * d * layers
     kv_bytes_per_token = 2 * layers * nkv * d * 2
     step_bytes = weight_bytes + kv_bytes_per_token * mean_context * args.batch
@@ -303,14 +321,16 @@ def main() -> int:
 
     value = args.batch / step_seconds
     line = {
-        "metric": "Qwen3-1.7B bf16 decode tok/s @ batch 8 (context 4096); prefill tok/s @ 2,048 tokens",
+        "metric": f"Qwen3-{args.shape.upper()} bf16 decode tok/s @ batch {args.batch} (context {CONTEXT}); "
+                  f"prefill tok/s @ 2,048 tokens",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(step_seconds * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random weights)",
         "impl": "ours",
-        "config": {"model": "Qwen3-1.7B shape", "layers": layers, "layers_of_model": MODEL["num_hidden_layers"],
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": layers,
+                   "layers_of_model": shape["num_hidden_layers"],
                    "hidden": h, "q_heads": nq, "kv_heads": nkv, "head_dim": d, "intermediate": i_, "vocab": vocab,
-                   "tied_embeddings": True, "global_batch": args.batch, "seq_len": CONTEXT,
+                   "tied_embeddings": config["tie_word_embeddings"], "global_batch": args.batch, "seq_len": CONTEXT,
                    "context_len": CONTEXT, "page_size": PAGE_SIZE, "parallelism": "single GPU",
                    "decode_execution": "cuda_graph", "l2": "inputs larger than L2 (weights + cache read every step)"},
         "e2e": {"value": round(args.batch / e2e_seconds, 1), "unit": "tokens/s", "ms_per_step": round(e2e_seconds * 1e3, 4),

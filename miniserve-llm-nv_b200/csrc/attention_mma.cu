@@ -377,12 +377,22 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
   const float total = warp_sum(w_a + w_b);
   float acc[D / 32] = {};
   const float* base = part_o + (size_t)item * num_splits * D;
-#pragma unroll 8
-  for (int s = 0; s < num_splits; ++s) {
-    const float w = __shfl_sync(0xffffffffu, s < 32 ? w_a : w_b, s & 31);
-    if (w == 0.f) continue;                 // uniform across the warp
+  // eight splits at a time: their loads are all on the way before the first is used (a split without
+  // keys has weight 0 and whatever its buffer holds is not added)
+  for (int s0 = 0; s0 < num_splits; s0 += 8) {
+    float v[8][D / 32];
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) acc[i] += w * base[(size_t)s * D + lane + 32 * i];
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i)
+        v[j][i] = s0 + j < num_splits ? __ldcg(base + (size_t)(s0 + j) * D + lane + 32 * i) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int s = s0 + j;
+      const float w = __shfl_sync(0xffffffffu, s < 32 ? w_a : w_b, s & 31);
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) acc[i] += (s < num_splits && w != 0.f) ? w * v[j][i] : 0.f;
+    }
   }
   const float inv = total > 0.f ? 1.f / total : 0.f;
 #pragma unroll

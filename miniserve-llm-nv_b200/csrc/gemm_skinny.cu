@@ -188,13 +188,15 @@ int launch_skinny_nt(const __nv_bfloat16* x, int ldx, const __nv_bfloat16* w, Ou
   config.blockDim = dim3(SK_WARPS * 32, 1, 1);
   config.dynamicSmemBytes = 0;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
+  cudaLaunchAttribute attribute[2];
   attribute[0].id = cudaLaunchAttributeClusterDimension;
   attribute[0].val.clusterDim.x = 1;
   attribute[0].val.clusterDim.y = k_blocks;
   attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // as ms::launch gives every kernel
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
-  config.numAttrs = 1;
+  config.numAttrs = dependent_launch_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&config, gemm_skinny_kernel<NT, MODE, OutT, true>, x, ldx, w, o, M, N, K);
   if (e != cudaSuccess) MS_FAIL("gemm_skinny: launch failed: %s", cudaGetErrorString(e));
   return 0;

@@ -1,4 +1,9 @@
-// Next-token choice on the device, one thread block per row of float32 logits.
+// Next-token choice on the device from rows of float32 logits.
+//
+// A row without filters (argmax, or temperature alone) is an argmax over the vocabulary, of the logits or
+// of the logits plus noise: a first kernel takes it in chunks, many thread blocks per row, and the second
+// kernel merges the chunks' candidates.  A row with top-k or top-p goes through the second kernel alone,
+// one thread block for the row.
 //
 // temperature == 0: argmax, the lowest index among equal maxima.
 // otherwise, in this order: divide by the temperature; keep the top_k largest
@@ -110,9 +115,71 @@ __device__ int index_bound(const float* row, float temperature, int vocab, unsig
   return b;
 }
 
+constexpr int kChunkThreads = 256;
+constexpr int kChunk = 4096;                 // logits per block of the first kernel (a multiple of 4)
+
+__device__ __forceinline__ bool without_filters(const SamplingRecord& rec, int vocab) {
+  return rec.temperature == 0.f || ((rec.top_k <= 0 || rec.top_k >= vocab) && rec.top_p >= 1.0f);
+}
+
+// Block (chunk, row): the best of logits (or logits / temperature + noise) [chunk * kChunk, + kChunk) of a
+// row without filters, to candidates[row * chunks + chunk].  The arithmetic is that of sample_kernel.
+__global__ void __launch_bounds__(kChunkThreads)
+sample_chunk_kernel(const float* __restrict__ logits, int row_stride, int vocab,
+                    const SamplingRecord* __restrict__ records, const int* __restrict__ slot_of_row,
+                    const int* __restrict__ draw_index, ArgBest* __restrict__ candidates) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ ArgBest ascratch[32];
+  const int r = blockIdx.y, chunk = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  SamplingRecord rec;
+  if (records) {
+    rec = records[slot_of_row[r]];
+  } else {
+    rec.temperature = 0.f;
+    rec.top_k = 0;
+    rec.top_p = 1.f;
+  }
+  if (!without_filters(rec, vocab)) return;
+  const bool greedy = rec.temperature == 0.f;
+  const unsigned step = greedy ? 0u : (unsigned)draw_index[r];
+  const bool vector_ok = (row_stride % 4 == 0) && (reinterpret_cast<uintptr_t>(logits) % 16 == 0);
+  ArgBest best{-INFINITY, 0x7fffffff};
+  const int first_group = chunk * (kChunk / 4), groups = (vocab + 3) / 4;
+  for (int g = first_group + threadIdx.x; g < first_group + kChunk / 4 && g < groups; g += kChunkThreads) {
+    float x[4];
+    const int i0 = 4 * g;
+    if (vector_ok && i0 + 4 <= vocab) {
+      const float4 v = *reinterpret_cast<const float4*>(row + i0);
+      x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[j] = i0 + j < vocab ? row[i0 + j] : -INFINITY;
+    }
+    if (greedy) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (i0 + j < vocab && x[j] > best.value) best = ArgBest{x[j], i0 + j};
+    } else {
+      unsigned words[4];
+      philox4x32_10((unsigned)g, step, 0u, 0u, rec.seed_lo, rec.seed_hi, words);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (i0 + j >= vocab) break;
+        const float v = x[j] / rec.temperature + gumbel_from_word(words[j]);
+        if (v > best.value) best = ArgBest{v, i0 + j};
+      }
+    }
+  }
+  best = block_argmax(best, ascratch);
+  if (threadIdx.x == 0) candidates[(size_t)r * gridDim.x + chunk] = best;
+}
+
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, int row_stride, int vocab, const SamplingRecord* __restrict__ records,
-              const int* __restrict__ slot_of_row, const int* __restrict__ draw_index, int* __restrict__ out) {
+              const int* __restrict__ slot_of_row, const int* __restrict__ draw_index, int* __restrict__ out,
+              const ArgBest* __restrict__ candidates, int chunks) {
   grid_dependency_wait();
   grid_dependency_launch();
   __shared__ float fscratch[32];
@@ -125,6 +192,16 @@ sample_kernel(const float* __restrict__ logits, int row_stride, int vocab, const
     rec = records[slot_of_row[r]];
   } else {
     rec.temperature = 0.f;
+    rec.top_k = 0;
+    rec.top_p = 1.f;
+  }
+
+  if (candidates != nullptr && without_filters(rec, vocab)) {      // the first kernel has been over this row
+    ArgBest best{-INFINITY, 0x7fffffff};
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) best = better(best, candidates[(size_t)r * chunks + c]);
+    best = block_argmax(best, ascratch);
+    if (threadIdx.x == 0) out[r] = best.index == 0x7fffffff ? 0 : best.index;
+    return;
   }
 
   if (rec.temperature == 0.f) {
@@ -253,14 +330,25 @@ using namespace ms;
 // logits [n_rows, row_stride] float32, the first `vocab` entries of a row are used.
 // records: [slots, 8] 32-bit words (temperature, top_p as float; top_k, seed low, seed high
 // as integers; three unused), or null for argmax on every row.  slot_of_row, draw_index [n_rows].
+// scratch: room for n_rows * ms_sample_chunks(vocab) pairs of 32-bit words (contents arbitrary), or null,
+// in which case every row is handled by one thread block.
+MS_EXPORT int ms_sample_chunks(int vocab) { return (vocab + kChunk - 1) / kChunk; }
+
 MS_EXPORT int ms_sample(const float* logits, int row_stride, int vocab, const void* records, const int* slot_of_row,
-                        const int* draw_index, int* out, int n_rows, cudaStream_t stream) {
+                        const int* draw_index, int* out, int n_rows, void* scratch, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   MS_REQUIRE(vocab > 0 && row_stride >= vocab, "sample: vocabulary %d, row stride %d", vocab, row_stride);
   MS_REQUIRE(records == nullptr || (slot_of_row != nullptr && draw_index != nullptr),
              "sample: sampling records need slot and draw index arrays");
+  const int chunks = ms_sample_chunks(vocab);
+  if (scratch != nullptr) {
+    MS_REQUIRE(n_rows <= 65535, "sample: %d rows in one call is too many", n_rows);
+    ms::launch(sample_chunk_kernel, dim3(chunks, n_rows), dim3(kChunkThreads), 0, stream, logits, row_stride, vocab,
+               (const SamplingRecord*)records, slot_of_row, draw_index, (ArgBest*)scratch);
+    MS_CHECK_LAUNCH("sample (chunks)");
+  }
   ms::launch(sample_kernel, n_rows, kSampleThreads, 0, stream, logits, row_stride, vocab, (const SamplingRecord*)records,
-                                                       slot_of_row, draw_index, out);
+             slot_of_row, draw_index, out, (const ArgBest*)scratch, chunks);
   MS_CHECK_LAUNCH("sample");
   return 0;
 }

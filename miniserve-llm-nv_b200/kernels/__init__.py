@@ -444,5 +444,7 @@ def sample(logits: torch.Tensor, records: Optional[torch.Tensor], slot_of_row: O
             raise KernelError(f"records must be [slots, {SAMPLING_RECORD_WORDS}] int32")
         _want(slot_of_row, "slot_of_row", torch.int32, (k,))
         _want(draw_index, "draw_index", torch.int32, (k,))
+    # candidates of the first of the two kernels: (value, index) for every chunk of every row
+    scratch = torch.empty((k, library().ms_sample_chunks(_i(vocab)), 2), dtype=torch.int32, device=logits.device)
     _check(library().ms_sample(_ptr(logits), _i(logits.stride(0)), _i(vocab), _ptr(records), _ptr(slot_of_row),
-                               _ptr(draw_index), _ptr(out), _i(k), _stream()))
+                               _ptr(draw_index), _ptr(out), _i(k), _ptr(scratch), _stream()))
