@@ -24,6 +24,7 @@ class EngineConfig:
     enable_chunked_prefill: bool = True
     prefill_chunk_size: Optional[int] = None
     decode_execution: str = "cuda_graph"         # "cuda_graph" or "eager"
+    decode_look_ahead: bool = True               # with graphs: start the next decode step before reading the last tokens
     gpu_memory_utilization: float = 0.85         # share of free memory given to pages when num_kv_blocks is None
     device: str = "cuda:0"
 

@@ -1,5 +1,14 @@
 """The engine loop: admit, plan, reserve, run, sample, commit, finish and free.
 
+With ``look_ahead`` (and an executor that can defer reading a step's tokens) decoding runs one step
+ahead of the host: a step of decoded tokens is started and its tokens are read only during the next
+call, after that call has started the following step, whose input tokens the device takes from the
+sampled ones directly.  The host's work for a step then overlaps the device's work for the step before.
+A request that ends on a stop token is found one step late; the extra token computed for it is dropped
+with its pages.  Whenever the next step would not be the same rows again (a request reaches its token
+budget, another waits or is part-way through its prompt, pages run short), the pending tokens are read
+first and the step is planned as usual.
+
 One call of :meth:`Engine.step` is one transaction, in the order of
 miniserve/engine/core.py:278-439: finished requests give back what they hold; the scheduler
 plans; newly planned requests are admitted to the cache (a state slot, reusable prefix pages);
@@ -34,6 +43,10 @@ class SampleRequest:
 
 
 class Executor(Protocol):
+    """``execute`` is required; an executor may also offer ``can_defer(entries)`` and
+    ``execute_deferred(entries, reservation, samples, feed_back)`` returning an object whose ``tokens()``
+    waits for the step's tokens, which the engine's look-ahead uses."""
+
     def admit(self, slot: int, params: SamplingParams, seed: int) -> None: ...
 
     def execute(self, entries: Seq[StepEntry], reservation: StepReservation,
@@ -67,8 +80,10 @@ class RequestRejected(ValueError):
 
 class Engine:
     def __init__(self, manager: CacheManager, scheduler: Scheduler, executor: Executor, *, vocab_size: int,
-                 max_model_len: int, max_pending_requests: int = 64) -> None:
+                 max_model_len: int, max_pending_requests: int = 64, look_ahead: bool = False) -> None:
         self.manager, self.scheduler, self.executor = manager, scheduler, executor
+        self.look_ahead = look_ahead and hasattr(executor, "execute_deferred")
+        self._pending: Optional[tuple[list[Sequence], object]] = None    # a started step whose tokens are unread
         self.vocab_size, self.max_model_len = vocab_size, max_model_len
         self.max_pending_requests = max_pending_requests
         self.sequences: dict[str, Sequence] = {}
@@ -122,7 +137,59 @@ class Engine:
         seq.preempt()
         self.stats.preemptions += 1
 
+    # ------------------------------------------------------------------ decoding one step ahead
+    def _read_pending(self) -> None:
+        """Reads the tokens of the started step and gives them to their sequences."""
+        sequences, handle = self._pending
+        self._pending = None
+        for seq, token in zip(sequences, handle.tokens()):
+            if not seq.done:
+                seq.append_sampled(token)
+
+    def _step_ahead(self) -> Optional[StepPlan]:
+        """Starts the step after the pending one if it is the same rows again, then reads the pending
+        tokens; None if the next step has to be planned in the usual way."""
+        sequences, _ = self._pending
+        if any(s.done or len(s.generated) + 2 > s.params.max_new_tokens for s in sequences):
+            return None                      # a row ends with the pending token: the rows change
+        if len(sequences) != len(self.sequences):
+            return None                      # another request waits or is part-way through its prompt
+        try:
+            reservation = self.manager.prepare([(s.request_id, 1) for s in sequences])
+        except OutOfPagesError:
+            return None
+        # the pending token of a row is token number `total` of its sequence; its value is still on the device
+        entries = [StepEntry(s.request_id, [0], [0]) for s in sequences]
+        samples = [SampleRequest(i, self.manager.requests[s.request_id].slot, len(s.generated) + 1)
+                   for i, s in enumerate(sequences)]
+        try:
+            handle = self.executor.execute_deferred(entries, reservation, samples, feed_back=True)
+        except BaseException:
+            self.manager.abort(reservation)
+            raise
+        self.manager.commit(reservation)
+        self._read_pending()                 # the device is busy with the new step meanwhile
+        running = []
+        for seq in sequences:
+            if not seq.done:                 # (a stop token ended it: the step just started has a row to drop)
+                seq.advance(seq.total)
+                self.stats.decode_tokens += 1
+                self.stats.scheduled_tokens += 1
+            running.append(seq)
+        self._pending = (running, handle)
+        self.stats.steps += 1
+        self.last_step_ran = True
+        self.last_plan = plan = self.scheduler.repeat_decode_plan([(r.request_id, r.start, r.end)
+                                                                   for r in reservation.items])
+        self._finalize()
+        return plan
+
     def step(self) -> StepPlan:
+        if self._pending is not None:
+            plan = self._step_ahead()
+            if plan is not None:
+                return plan
+            self._read_pending()
         self._finalize()
         live = list(self.sequences.values())
         plan = self.scheduler.schedule(live, self.manager.capacity())
@@ -180,8 +247,14 @@ class Engine:
                    for seq, start, end, _ in items]
         samples = [SampleRequest(index, self.manager.requests[seq.request_id].slot, len(seq.generated))
                    for index, (seq, start, end, _) in enumerate(items) if end == seq.total]
+        defer = (self.look_ahead and len(samples) == len(entries) and all(d for *_, d in items)
+                 and self.executor.can_defer(entries))
         try:
-            tokens = self.executor.execute(entries, reservation, samples)
+            if defer:
+                handle = self.executor.execute_deferred(entries, reservation, samples)
+                tokens = []
+            else:
+                tokens = self.executor.execute(entries, reservation, samples)
         except BaseException as error:
             self.manager.abort(reservation)
             self.stats.failed_steps += 1
@@ -200,6 +273,8 @@ class Engine:
                 self.stats.decode_tokens += 1
             else:
                 self.stats.prefill_tokens += end - start
+        if defer:
+            self._pending = ([seq for seq, *_ in items], handle)
         for sample, token in zip(samples, tokens):
             items[sample.entry][0].append_sampled(token)
         for seq, *_ in items:
@@ -212,7 +287,7 @@ class Engine:
 
     # ------------------------------------------------------------------ driving
     def has_unfinished(self) -> bool:
-        return any(not s.done for s in self.sequences.values())
+        return self._pending is not None or any(not s.done for s in self.sequences.values())
 
     def run_until_done(self, max_steps: int = 1_000_000) -> None:
         stalled = 0
@@ -223,6 +298,8 @@ class Engine:
             stalled = 0 if self.last_step_ran else stalled + 1
             if stalled > 8:
                 raise RuntimeError("the scheduler cannot make progress: no request fits the free pages and state slots")
+        if self._pending is not None:
+            self._read_pending()
         self._finalize()
 
     def take_result(self, request_id: str) -> GenerationResult:

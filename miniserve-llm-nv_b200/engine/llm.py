@@ -3,7 +3,8 @@
 Token ids in, token ids out (tokenizers are outside this engine).  The engine options carry
 MiniServe's names (``max_model_len``, ``num_kv_blocks``, ``max_num_seqs``, ``kv_block_size``,
 ``max_num_batched_tokens``, ``max_pending_requests``, ``enable_prefix_cache``,
-``enable_chunked_prefill``, ``prefill_chunk_size``, ``decode_execution``).
+``enable_chunked_prefill``, ``prefill_chunk_size``, ``decode_execution``); ``decode_look_ahead`` is this
+engine's own.
 """
 
 from __future__ import annotations
@@ -27,7 +28,8 @@ def build_engine(runtime: Runtime) -> Engine:
     executor = DeviceExecutor(runtime.step_function, runtime.storage)
     runtime.step_function.capture_decode_graphs(config.max_num_seqs)
     return Engine(runtime.manager, scheduler, executor, vocab_size=runtime.model.spec.vocab_size,
-                  max_model_len=runtime.max_model_len, max_pending_requests=config.max_pending_requests)
+                  max_model_len=runtime.max_model_len, max_pending_requests=config.max_pending_requests,
+                  look_ahead=config.decode_look_ahead and config.decode_execution == "cuda_graph")
 
 
 class LLM:

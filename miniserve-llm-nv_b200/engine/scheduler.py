@@ -56,6 +56,12 @@ class Scheduler:
         self.prefill_chunk_size = prefill_chunk_size
         self._next_step = 0
 
+    def repeat_decode_plan(self, rows: Seq[tuple[str, int, int]]) -> StepPlan:
+        """The plan of a step that decodes the same requests as the step before: (request, start, end) each."""
+        step_id = self._next_step
+        self._next_step += 1
+        return StepPlan(step_id, tuple(PlanItem(r, start, end, True) for r, start, end in rows), len(rows))
+
     @staticmethod
     def _pages(start: int, end: int, page_size: int) -> int:
         return (end + page_size - 1) // page_size - (start + page_size - 1) // page_size

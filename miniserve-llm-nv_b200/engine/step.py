@@ -59,6 +59,7 @@ class DecodeGraph:
         self.host = torch.empty(self.offsets[-1], dtype=torch.int32, pin_memory=True)
         self.host_np = self.host.numpy()             # same memory, cheaper to fill from Python lists
         self.live_rows = -1
+        self.copied: Optional[torch.cuda.Event] = None     # recorded after the last copy of the host mirror
         self.row_owner: list = [None] * rows         # per row: (request id, pages already written per group)
         self.has_windows = any(need.window is not None for need in manager.paged_needs)
         self.meta = torch.zeros(self.offsets[-1], dtype=torch.int32, device=sf.device)
@@ -128,6 +129,7 @@ class StepFunction:
         self.graph_replays = 0
         self.eager_steps = 0
         self.last_tokens: Optional[torch.Tensor] = None   # tokens sampled inside the last replayed graph
+        self.last_graph: Optional[DecodeGraph] = None
 
     # ------------------------------------------------------------------ batch building
     def build_context(self, entries: Sequence[StepEntry], reservation: StepReservation) -> StepContext:
@@ -220,18 +222,26 @@ class StepFunction:
             group_views=group_views)
 
     # ------------------------------------------------------------------ running
+    def replays(self, entries: Sequence[StepEntry]) -> bool:
+        """Whether these entries run as a captured graph: single tokens, all of whose logits are wanted."""
+        return bool(self.use_graphs and entries and len(entries) <= DECODE_BUCKETS[-1]
+                    and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
+
     def run(self, entries: Sequence[StepEntry], reservation: StepReservation,
-            draw_index: Optional[Sequence[int]] = None) -> torch.Tensor:
+            draw_index: Optional[Sequence[int]] = None, feed_back: bool = False) -> torch.Tensor:
         """float32 logits ``[number of wanted positions, vocab]`` on the device, in entry order.
 
         A step of single tokens whose logits are all wanted replays a captured graph when graphs
         are on; the graph also samples, and ``last_tokens`` then holds one token per entry
-        (``draw_index``: each request's draw count, for its random stream).
+        (``draw_index``: each request's draw count, for its random stream).  ``feed_back``: the
+        entries are the rows of the last replay, in its order, and each row's token is the one that
+        replay sampled for it; it is taken on the device, and the entries' own token ids are ignored.
         """
         self.last_tokens = None
-        if (self.use_graphs and entries and len(entries) <= DECODE_BUCKETS[-1]
-                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)):
-            return self._replay(entries, reservation, draw_index)
+        if self.replays(entries):
+            return self._replay(entries, reservation, draw_index, feed_back)
+        if feed_back:
+            raise ValueError("only a replayed step can take its tokens from the step before")
         ctx = self.build_context(entries, reservation)
         self.eager_steps += 1
         return self.model.forward(ctx, self.storage)
@@ -256,9 +266,13 @@ class StepFunction:
             if bucket >= max_rows:
                 break
 
-    def _replay(self, entries, reservation, draw_index) -> torch.Tensor:
+    def _replay(self, entries, reservation, draw_index, feed_back: bool = False) -> torch.Tensor:
         n = len(entries)
         graph = self.graph_for(n)
+        if feed_back and (graph is not self.last_graph or graph.live_rows != n):
+            raise ValueError("the step before was not a replay of the same rows")
+        if graph.copied is not None:
+            graph.copied.synchronize()       # the host mirror is free once the last copy of it has run
         manager, ps = self.manager, self.manager.page_size
         limit, scratch = self.storage.num_pages, self.storage.scratch_page
         o, host = graph.offsets, graph.host_np
@@ -281,6 +295,8 @@ class StepFunction:
             lens.append(item.end)
             slots_state.append(manager.requests[entry.request_id].slot)
             owner = graph.row_owner[row]
+            if feed_back and (owner is None or owner[0] != entry.request_id):
+                raise ValueError(f"row {row} of the step before belonged to another request")
             same = owner is not None and owner[0] == entry.request_id and not graph.has_windows
             for g in range(graph.n_groups):
                 table = item.tables[g]
@@ -307,6 +323,12 @@ class StepFunction:
         host[o[5]:o[5] + n] = slots_state
         host[o[7]:o[7] + n] = 0 if draw_index is None else list(draw_index)
         graph.meta.copy_(graph.host, non_blocking=True)
+        if graph.copied is None:
+            graph.copied = torch.cuda.Event()
+        graph.copied.record()
+        if feed_back:
+            graph.meta[o[0]:o[0] + n].copy_(graph.tokens_out[:n])
+        self.last_graph = graph
         graph.graph.replay()
         self.graph_replays += 1
         self.last_tokens = graph.tokens_out[:n]

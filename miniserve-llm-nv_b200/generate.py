@@ -44,6 +44,8 @@ def build_cli_parser() -> argparse.ArgumentParser:
     parser.add_argument("--max-num-batched-tokens", type=int, default=None)
     parser.add_argument("--kv-block-size", type=int, default=16)
     parser.add_argument("--decode-execution", choices=("cuda_graph", "eager"), default="cuda_graph")
+    parser.add_argument("--no-decode-look-ahead", action="store_true",
+                        help="read every decode step's tokens before the next step starts")
     parser.add_argument("--no-prefix-cache", action="store_true")
     chunk = parser.add_mutually_exclusive_group()
     chunk.add_argument("--chunked-prefill", dest="enable_chunked_prefill", action="store_true")
@@ -85,7 +87,7 @@ def main(argv=None) -> int:
     llm = LLM(model_dir, dtype=args.dtype, max_model_len=args.max_model_len, num_kv_blocks=args.num_kv_blocks,
               max_num_seqs=args.max_num_seqs, max_pending_requests=args.max_pending_requests,
               max_num_batched_tokens=args.max_num_batched_tokens, kv_block_size=args.kv_block_size,
-              decode_execution=args.decode_execution, enable_prefix_cache=not args.no_prefix_cache,
+              decode_execution=args.decode_execution, decode_look_ahead=not args.no_decode_look_ahead, enable_prefix_cache=not args.no_prefix_cache,
               enable_chunked_prefill=args.enable_chunked_prefill, prefill_chunk_size=args.prefill_chunk_size)
     params = [SamplingParams(temperature=args.temperature, top_p=args.top_p, top_k=args.top_k,
                              max_new_tokens=args.max_new_tokens, stop_token_ids=tuple(_ids(args.stop_token_ids)),

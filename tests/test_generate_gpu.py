@@ -116,3 +116,35 @@ def test_command_line(tmp_path):
     assert len(lines) == 2 and all(len(line["token_ids"]) == 5 for line in lines)
     from miniserve_b200.sampling import SamplingParams
     check_against_plain(folder, [5, 17, 3], lines[0]["token_ids"], SamplingParams(), "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decoding_one_step_ahead_on_the_device(tmp_path, dtype):
+    """Replayed decode steps started before the last tokens are read (the device feeds them back itself)
+    give the tokens of the step-by-step engine: greedy and seeded sampling, budgets that end at different
+    steps, and stop tokens that are found one step late."""
+    from miniserve_b200.engine.llm import LLM
+    from miniserve_b200.sampling import SamplingParams
+
+    folder = helpers.make_folder(tmp_path, "b", seed=9)
+    vocab = helpers.TINY_B["vocab_size"]
+    prompts = [helpers.random_tokens(vocab, n, seed=700 + n) for n in (5, 11, 2, 19)]
+    outcomes = {}
+    for look_ahead in (False, True):
+        llm = LLM(str(folder), dtype=dtype, kv_block_size=8, num_kv_blocks=40, max_num_seqs=4,
+                  max_num_batched_tokens=64, decode_execution="cuda_graph", decode_look_ahead=look_ahead)
+        assert llm.engine.look_ahead == look_ahead
+        free = llm.generate(prompts, [SamplingParams(temperature=(0.0, 0.9)[i % 2], seed=50 + i,
+                                                     max_new_tokens=(24, 7, 16, 30)[i]) for i in range(4)])
+        # now stop each request on a token it is known to produce part-way
+        stops = [(r.token_ids[len(r.token_ids) // 2],) for r in free]
+        stopped = llm.generate(prompts, [SamplingParams(temperature=(0.0, 0.9)[i % 2], seed=50 + i, stop_token_ids=stops[i],
+                                                        max_new_tokens=(24, 7, 16, 30)[i]) for i in range(4)])
+        for r, stop in zip(stopped, stops):
+            assert r.finish_reason == "stop" and r.token_ids[-1] == stop[0] and stop[0] not in r.token_ids[:-1]
+        outcomes[look_ahead] = [(r.token_ids, r.finish_reason) for r in free + stopped]
+        llm.runtime.manager.check_invariants()
+        assert not llm.runtime.manager.requests
+        if look_ahead:
+            assert llm.runtime.step_function.graph_replays > 0
+    assert outcomes[True] == outcomes[False]

@@ -206,3 +206,83 @@ def test_preemption_with_reusable_prefix_makes_progress():
     assert engine.stats.preemptions >= 1
     for rid, prompt in prompts.items():
         assert results[rid].token_ids == expected_tokens(prompt, 18), rid
+
+
+class DeferringExecutor(ScriptedExecutor):
+    """The scripted executor with deferred reads: a deferred step's tokens are computed only when they are
+    read, and a step fed back from the one before takes its input tokens from that step's results, as the
+    device does; the token ids in its entries are placeholders."""
+
+    def __init__(self, vocab=97):
+        super().__init__(vocab)
+        self.deferred_steps = self.fed_back_steps = 0
+        self._last = None                      # the last deferred step's handle
+
+    def can_defer(self, entries):
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def execute_deferred(self, entries, reservation, samples, feed_back=False):
+        executor, previous = self, self._last
+        self.deferred_steps += 1
+        self.fed_back_steps += bool(feed_back)
+        if feed_back:
+            assert previous is not None and [e.request_id for e in entries] == previous.ids
+
+        class Handle:
+            ids = [e.request_id for e in entries]
+            result = None
+
+            def tokens(self):
+                if self.result is None:
+                    fed = previous.tokens() if feed_back else [e.tokens[0] for e in entries]
+                    real = [type(e)(e.request_id, [t], e.want) for e, t in zip(entries, fed)]
+                    self.result = ScriptedExecutor.execute(executor, real, reservation, samples)
+                return self.result
+
+        self._last = Handle()
+        return self._last
+
+
+@pytest.mark.parametrize("stop", [(), (5, 11, 23, 42, 77)])
+def test_decoding_one_step_ahead_gives_the_same_tokens(stop):
+    """With deferred reads the engine starts each decode step before it has read the tokens of the step
+    before; results, finish reasons and the cache's books are as without."""
+    prompts = {"a": [3, 1, 4, 1, 5], "b": [9, 2, 6], "c": list(range(20, 31)), "d": [7]}
+    budgets = {"a": 12, "b": 3, "c": 9, "d": 17}
+    outcomes = []
+    for look_ahead in (False, True):
+        manager = CacheManager([GROUP], 4, 32, 4, enable_prefix_cache=False)
+        scheduler = Scheduler(max_num_seqs=4, max_num_batched_tokens=24)
+        executor = DeferringExecutor()
+        engine = Engine(manager, scheduler, executor, vocab_size=97, max_model_len=256, look_ahead=look_ahead)
+        for rid, prompt in prompts.items():
+            engine.submit(rid, prompt, SamplingParams(max_new_tokens=budgets[rid], stop_token_ids=stop))
+        engine.run_until_done()
+        outcomes.append({rid: (engine.finished[rid].token_ids, engine.finished[rid].finish_reason) for rid in prompts})
+        for rid, prompt in prompts.items():
+            assert outcomes[-1][rid][0] == expected_tokens(prompt, budgets[rid], stop=stop)
+        manager.check_invariants()
+        assert not manager.requests and manager.capacity().free_pages == (32,)
+        assert (executor.fed_back_steps > 0) == look_ahead
+    assert outcomes[0] == outcomes[1]
+
+
+def test_look_ahead_yields_to_a_new_request():
+    """A request that arrives while decoding runs ahead is planned in the next step: the pending tokens
+    are read first and the step is an ordinary mixed one."""
+    manager = CacheManager([GROUP], 4, 32, 4, enable_prefix_cache=False)
+    executor = DeferringExecutor()
+    engine = Engine(manager, Scheduler(max_num_seqs=4, max_num_batched_tokens=24), executor, vocab_size=97,
+                    max_model_len=256, look_ahead=True)
+    engine.submit("a", [1, 2, 3], SamplingParams(max_new_tokens=10))
+    for _ in range(4):
+        engine.step()
+    fed_back = executor.fed_back_steps
+    assert fed_back >= 2
+    engine.submit("b", [4, 5, 6, 7, 8], SamplingParams(max_new_tokens=6))
+    engine.step()
+    assert executor.fed_back_steps == fed_back            # no look-ahead past a waiting request
+    assert {item.request_id for item in engine.last_plan.items} == {"a", "b"}
+    engine.run_until_done()
+    assert engine.finished["a"].token_ids == expected_tokens([1, 2, 3], 10)
+    assert engine.finished["b"].token_ids == expected_tokens([4, 5, 6, 7, 8], 6)
