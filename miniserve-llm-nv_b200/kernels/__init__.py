@@ -290,15 +290,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     _want(x, "x", torch.bfloat16)
     _want(weight, "weight", torch.bfloat16)
     _want(out, "out")
-    if m <= STREAM_MAX_ROWS and k % 8 == 0 and _stream_units_per_block(x.device, n, k) >= STREAM_MIN_UNITS:
-        # few rows and a large weight (the output matrix): it streams through the tcgen05 tensor cores
-        linear_stream(x, weight, out)
-        return
-    if m <= SKINNY_MAX_ROWS and k % 8 == 0:
-        # few rows (decode steps): the mma.sync weight-streaming kernel
-        _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m), _i(n),
-                                        _i(k), _stream()))
-        return
+    if m <= STREAM_MAX_ROWS and k % 8 == 0:
+        # few rows (decode steps): one of the two weight-streaming kernels, or the library, by measurement
+        choice = _few_rows_choice(x, weight, m)
+        if choice == "stream":
+            linear_stream(x, weight, out)
+            return
+        if choice == "skinny":
+            _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m),
+                                            _i(n), _i(k), _stream()))
+            return
     if USE_TCGEN05_GEMM and m >= 128 and k % 8 == 0:
         linear_tcgen05(x, weight, out)
         return
@@ -356,13 +357,19 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add
 
 _stream_buffers: dict = {}
 
-# Products of up to STREAM_MAX_ROWS rows whose weight gives every thread block at least STREAM_MIN_UNITS units
-# (256 rows x 64 k, 32 KB each) run the streaming tcgen05 kernel.  Its start and its sum over the blocks
-# that share a tile cost some microseconds, which a smaller weight does not win back: there the mma.sync
-# kernel, several blocks of which share a multiprocessor, is faster.
+# Products of few rows (decode steps) read every weight once; which kernel streams a given weight fastest
+# depends on its shape.  For up to SKINNY_MAX_ROWS rows the choice between the mma.sync kernel ("skinny":
+# many small blocks, K split over a cluster for narrow weights), the tcgen05 kernel ("stream": one block
+# per multiprocessor, its start and the sum over blocks sharing a tile cost some microseconds, which only a
+# large weight wins back) and the library is measured once per weight shape, on the weight itself with the
+# L2 cache flushed between runs, at the first eager call that meets the shape; MINISERVE_B200_LINEAR_TUNING=0
+# turns the measurement off, and then (and while a graph is being captured before any eager call) the rule
+# below decides.  From SKINNY_MAX_ROWS + 1 to STREAM_MAX_ROWS rows it is the rule alone.
 STREAM_MAX_ROWS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MAX_ROWS", "16"))
 STREAM_MIN_UNITS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MIN_UNITS", "32"))
+LINEAR_TUNING = __import__("os").environ.get("MINISERVE_B200_LINEAR_TUNING", "1") == "1"
 _multiprocessors: dict = {}
+_linear_choices: dict = {}           # (device index, N, K) -> "skinny" | "stream" | "library"
 
 
 def _stream_units_per_block(device: torch.device, n: int, k: int) -> float:
@@ -370,6 +377,61 @@ def _stream_units_per_block(device: torch.device, n: int, k: int) -> float:
     if key not in _multiprocessors:
         _multiprocessors[key] = torch.cuda.get_device_properties(device).multi_processor_count
     return ((n + 255) // 256) * ((k + 63) // 64) / _multiprocessors[key]
+
+
+def _few_rows_rule(device: torch.device, m: int, n: int, k: int) -> str:
+    if _stream_units_per_block(device, n, k) >= STREAM_MIN_UNITS:
+        return "stream"
+    return "skinny" if m <= SKINNY_MAX_ROWS else "library"
+
+
+def _few_rows_choice(x: torch.Tensor, weight: torch.Tensor, m: int) -> str:
+    n, k = weight.shape
+    if m > SKINNY_MAX_ROWS:
+        return _few_rows_rule(x.device, m, n, k)
+    key = (torch.device(x.device).index or 0, n, k)
+    choice = _linear_choices.get(key)
+    if choice is None:
+        if not LINEAR_TUNING or torch.cuda.is_current_stream_capturing():
+            return _few_rows_rule(x.device, m, n, k)
+        choice = _linear_choices[key] = _measure_few_rows(weight)
+    return choice
+
+
+def linear_choices() -> dict:
+    """What was measured so far: (device index, N, K) -> the kernel chosen for products of few rows."""
+    return dict(_linear_choices)
+
+
+def _measure_few_rows(weight: torch.Tensor) -> str:
+    """Times the candidates for ``[8, K] @ weight[N, K]^T`` on the device: the faster of this library's two
+    kernels, unless the vendor library is clearly (3 %) faster than both."""
+    n, k = weight.shape
+    device = weight.device
+    x = torch.zeros((SKINNY_MAX_ROWS, k), dtype=torch.bfloat16, device=device)
+    out = torch.empty((SKINNY_MAX_ROWS, n), dtype=torch.bfloat16, device=device)
+    flush = torch.empty(64 << 20, dtype=torch.float32, device=device)      # 256 MB: larger than the L2 cache
+    candidates = {
+        "skinny": lambda: _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)),
+                                                          _i(SKINNY_MAX_ROWS), _i(n), _i(k), _stream())),
+        "stream": lambda: linear_stream(x, weight, out),
+        "library": lambda: torch.mm(x, weight.t(), out=out),
+    }
+    times = {}
+    for name, run in candidates.items():
+        run()                                                               # lazy set-up outside the timing
+        samples = []
+        for _ in range(5):
+            flush.zero_()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            run()
+            end.record()
+            end.synchronize()
+            samples.append(start.elapsed_time(end))
+        times[name] = sorted(samples)[len(samples) // 2]
+    own = "stream" if times["stream"] < times["skinny"] else "skinny"
+    return "library" if times["library"] < 0.97 * times[own] else own
 
 
 def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
