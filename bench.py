@@ -148,6 +148,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                         help="fewer layers than the model has (named in the output); for quick checks only")
     parser.add_argument("--skip-points", action="store_true")
+    parser.add_argument("--timeline", metavar="FILE", default=None,
+                        help="with --profile: replay the decode step as a graph (or run the prompt step) under the "
+                             "framework profiler and write every kernel's start, duration and exposed time to FILE")
     parser.add_argument("--shape", choices=sorted(SHAPES), default="1.7b",
                         help="layer sizes of another model of the family (the default is the benchmark's)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="tokens a request holds at the end of the timed steps")
@@ -181,7 +184,7 @@ def main() -> int:
     runtime = build_runtime(None, EngineConfig(
         dtype="bfloat16", max_model_len=CONTEXT, max_num_seqs=max_batch, kv_block_size=PAGE_SIZE, num_kv_blocks=pages,
         max_num_batched_tokens=8192, enable_prefix_cache=False,
-        decode_execution="eager" if args.profile else "cuda_graph"),
+        decode_execution="eager" if args.profile and not args.timeline else "cuda_graph"),
         config_dict=config, weights_seed=0)
     manager, step_function = runtime.manager, runtime.step_function
     vocab = config["vocab_size"]
@@ -236,6 +239,67 @@ def main() -> int:
         for rid in ids:
             manager.release(rid)
         return seconds, mean_context, launches
+
+    if args.profile and args.timeline:
+        # The step under the framework's profiler (CUPTI): kernels of a replayed graph keep their programmatic
+        # overlap, so "exposed" (how far a kernel's end lies past the end of everything before it) is what
+        # the kernel adds to the step.
+        from torch.profiler import ProfilerActivity, profile
+        ids = [f"p{i}" for i in range(args.batch)]
+
+        def one_step() -> None:
+            if args.profile == "decode":
+                entries = [StepEntry(rid, [1], [0]) for rid in ids]
+                reservation = manager.prepare([(rid, 1) for rid in ids])
+                step_function.run(entries, reservation, [0] * len(ids))
+                manager.abort(reservation)                       # the context stays as long as it was
+            else:
+                manager.admit("p")
+                reservation = manager.prepare([("p", PREFILL_TOKENS)])
+                step_function.run([StepEntry("p", prefill_tokens, [PREFILL_TOKENS - 1])], reservation)
+                manager.commit(reservation)
+                manager.release("p")
+
+        prefill_tokens = prompt(PREFILL_TOKENS)
+        if args.profile == "decode":
+            for rid in ids:
+                manager.admit(rid)
+                manager.commit(manager.prepare([(rid, CONTEXT - 1)]))
+        for _ in range(warmup):
+            one_step()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as profiler:
+            one_step()
+            torch.cuda.synchronize()
+        trace_file = args.timeline + ".trace.json"
+        profiler.export_chrome_trace(trace_file)
+        with open(trace_file) as handle:
+            events = [e for e in json.load(handle)["traceEvents"] if e.get("cat") in ("kernel", "gpu_memcpy")]
+        os.remove(trace_file)
+        events.sort(key=lambda e: e["ts"])
+        origin = next((e["ts"] for e in events if e.get("cat") == "kernel"), events[0]["ts"])   # the first kernel
+        reached = origin
+        totals: dict[str, list[float]] = {}
+        lines = [f"{'start us':>10} {'duration':>9} {'exposed':>8}  grid          kernel"]
+        for event in events:
+            end = event["ts"] + event["dur"]
+            exposed = max(0.0, end - max(reached, event["ts"]))
+            name = event["name"].split("(")[0].replace("void ", "")[:70]
+            lines.append(f"{event['ts'] - origin:10.2f} {event['dur']:9.2f} {exposed:8.2f}  "
+                         f"{str(event['args'].get('grid', '')):13s} {name}")
+            entry = totals.setdefault(name, [0, 0.0, 0.0])
+            entry[0] += 1
+            entry[1] += event["dur"]
+            entry[2] += exposed
+            reached = max(reached, end)
+        summary = [f"{'launches':>8} {'duration us':>12} {'exposed us':>11}  kernel"]
+        for name, (count, duration, exposed) in sorted(totals.items(), key=lambda kv: -kv[1][2]):
+            summary.append(f"{count:8d} {duration:12.2f} {exposed:11.2f}  {name}")
+        with open(args.timeline, "w") as handle:
+            handle.write(f"step: {args.profile}, batch {args.batch}, layers {args.layers}, context {CONTEXT}, "
+                         f"span {reached - origin:.2f} us\n\n" + "\n".join(summary) + "\n\n" + "\n".join(lines) + "\n")
+        print(json.dumps({"profile": args.profile, "timeline": args.timeline, "span_us": round(reached - origin, 2)}))
+        return 0
 
     if args.profile:
         # A small, self-ending case for a profiler: the cache is reserved but not computed (its content
