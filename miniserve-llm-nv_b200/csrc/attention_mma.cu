@@ -67,7 +67,9 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ query_start, const int* __restrict__ context_lens, int page_size, int n_q,
                      int n_kv, float scale_log2, int window, __nv_bfloat16* __restrict__ out,
                      float* __restrict__ part_o, float* __restrict__ part_lse, int num_splits) {
-  grid_dependency_wait();
+  // The kernel before this one on the stream wrote the queries and the keys and values of this step's
+  // tokens.  What the batch looks like (set up before the step's first kernel) and the keys and values of
+  // earlier steps do not depend on it, so the first tiles of old keys are requested before the wait below.
   grid_dependency_launch();
   constexpr int BM = 16 * MT * W, THREADS = 32 * W, CHUNKS = D / 8;
   constexpr bool Q_IN_REGISTERS = MT == 1;
@@ -88,7 +90,10 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   // Query tiles are taken from the end of the request: under the causal mask the last tiles have the
   // most keys, and starting them first keeps the tail of the launch short.
   const int row0 = ((rows_total + BM - 1) / BM - 1 - (int)blockIdx.x) * BM;
-  if (row0 < 0) return;
+  if (row0 < 0) {
+    grid_dependency_wait();
+    return;
+  }
   const int first_pos = ctx - q_len;                     // position of the request's first query token
   const int t_lo = row0 / group;
   const int last_row = min(rows_total, row0 + BM) - 1;
@@ -109,6 +114,7 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   auto thread_row = [&](int mt, int half) { return warp_row0 + mt * 16 + quad_row + half * 8; };
 
   if (tile_lo >= tile_hi) {                               // nothing to do for this split
+    grid_dependency_wait();
     if (num_splits > 1 && quad_col == 0) {
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
@@ -123,17 +129,6 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     }
     return;
   }
-
-  // ---- Q tile to shared memory
-  for (int i = tid; i < BM * CHUNKS; i += THREADS) {
-    const int r = i / CHUNKS, c = i % CHUNKS;
-    const int row = row0 + r;
-    const bool valid = row < rows_total;
-    const __nv_bfloat16* src = q;
-    if (valid) src = q + ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group) * D + c * 8;
-    cp_async_16(tile_ptr<D>(q_s, r, c), src, valid);
-  }
-  cp_async_commit();
 
   // Where each key row of a tile lies in the pool is looked up once per row (block table, page
   // arithmetic) and kept in shared memory; the copies then only add the chunk offset.  The offsets of
@@ -168,12 +163,28 @@ attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
 #pragma unroll
   for (int s = 0; s < STAGES; ++s) find_rows(tile_lo + s, s);
   __syncthreads();
+  // a tile that ends before the request's first new token holds keys of earlier steps only
+  auto old_keys_only = [&](int s) { return tile_begin + (tile_lo + s + 1) * BN <= first_pos; };
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
-    if (tile_lo + s < tile_hi) load_tile(s);
-    cp_async_commit();
+  for (int s = 0; s < STAGES - 1; ++s)
+    if (tile_lo + s < tile_hi && old_keys_only(s)) load_tile(s);
+  cp_async_commit();
+  grid_dependency_wait();
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s)
+    if (tile_lo + s < tile_hi && !old_keys_only(s)) load_tile(s);
+  // ---- Q tile to shared memory
+  for (int i = tid; i < BM * CHUNKS; i += THREADS) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int row = row0 + r;
+    const bool valid = row < rows_total;
+    const __nv_bfloat16* src = q;
+    if (valid) src = q + ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group) * D + c * 8;
+    cp_async_16(tile_ptr<D>(q_s, r, c), src, valid);
   }
-  cp_async_wait<STAGES - 1>();   // Q has landed
+  cp_async_commit();
+
+  cp_async_wait<0>();            // Q and the first tiles have landed
   __syncthreads();
 
   unsigned q_frag[Q_IN_REGISTERS ? D / 16 : 1][4];
