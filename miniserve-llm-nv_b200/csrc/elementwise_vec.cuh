@@ -124,7 +124,16 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
   const long long item = ((long long)blockIdx.x * warps_per_block + warp) * HEADS_PER_WARP + sub;
   // No early exit: the lanes of a warp may serve different heads and all of them take part in the shuffles.
   const bool item_ok = item < total;
-  const int n = item_ok ? (int)(item / heads) : 0, head = item_ok ? (int)(item % heads) : 0;
+  int n = 0, head = 0;
+  if (item_ok) {
+    if (total <= 0x7fffffffLL) {                       // 32-bit division where it is enough
+      n = (int)((unsigned)item / (unsigned)heads);
+      head = (int)((unsigned)item % (unsigned)heads);
+    } else {
+      n = (int)(item / heads);
+      head = (int)(item % heads);
+    }
+  }
   const T* src = qkv + ((size_t)n * heads + head) * d;
   const int c0 = sub_lane * 8;
   bool active = item_ok && c0 < d;
@@ -217,20 +226,39 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
 
 // ---------------------------------------------------------------- gated activation
 // Eight outputs per thread; requires inter % 8 == 0.
+// silu(g) * u.  With bfloat16 data the exponential and the division are the fast ones (relative error about
+// 2^-21, far below the rounding of the result to 8 bits of mantissa); float32 data keeps the accurate ones.
+template <typename T>
+__device__ __forceinline__ float silu_times(float g, float u) {
+  if (sizeof(T) == 2) {
+    const float e = __expf(-fabsf(g));                 // in (0, 1]: nothing overflows
+    const float r = __fdividef(1.0f, 1.0f + e);
+    return g * (g >= 0.f ? r : e * r) * u;
+  }
+  return g / (1.0f + expf(-g)) * u;
+}
+
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total8) {
   grid_dependency_wait();
   grid_dependency_launch();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total8) return;
-  const int per_row = inter >> 3;
-  const size_t n = i / per_row;
-  const int c = (int)(i % per_row) * 8;
+  const unsigned per_row = (unsigned)inter >> 3;
+  size_t n;
+  int c;
+  if (total8 <= 0xffffffffu) {                         // 32-bit division where it is enough
+    n = (unsigned)i / per_row;
+    c = (int)((unsigned)i % per_row) * 8;
+  } else {
+    n = i / per_row;
+    c = (int)(i % per_row) * 8;
+  }
   const Vec8 g = load8(gate_up + n * 2 * inter + c);
   const Vec8 u = load8(gate_up + n * 2 * inter + inter + c);
   Vec8 y;
 #pragma unroll
-  for (int e = 0; e < 8; ++e) y.v[e] = g.v[e] / (1.0f + expf(-g.v[e])) * u.v[e];
+  for (int e = 0; e < 8; ++e) y.v[e] = silu_times<T>(g.v[e], u.v[e]);
   store8(out + n * inter + c, y);
 }
 
