@@ -369,3 +369,207 @@ def test_toy_architecture_with_stateful_mixer(tmp_path, dtype, cutting):
         bound = (3e-5 if dtype == "float32" else 4e-2) * max(1.0, float(expected.abs().max()))
         for position, row in got[rid].items():
             assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
+
+
+# --------------------------------------------------------------------------- a second toy: routing and another position encoding
+
+
+@dataclass(frozen=True)
+class RoutedConfig:
+    hidden_size: int
+    vocab_size: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    experts: int
+    expert_size: int
+    inter: int
+    window: int
+    amplitude: float
+    eps: float
+    theta: float
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: data[k] for k in cls.__dataclass_fields__})
+
+
+def sinusoid(positions, head_dim, amplitude, dtype):
+    """amplitude * sin(position / 50^(j / d)) for j < d / 2, cos of the same for the other half."""
+    half = head_dim // 2
+    rates = 1.0 / (50.0 ** (torch.arange(half, dtype=torch.float64, device=positions.device) / half))
+    angles = positions.to(torch.float64)[:, None] * rates[None, :]
+    return (amplitude * torch.cat([angles.sin(), angles.cos()], dim=1)).to(dtype)
+
+
+def register_routed_toy():
+    """A feed-forward that routes every token to two of its experts and a position encoding that is added
+    to queries and keys, registered with the package's public registries; and an architecture that uses
+    them in one layer beside the package's own parts (a windowed attention with rotation, a gated MLP) in
+    the other."""
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200 import kernels
+    from miniserve_b200.config import register_architecture
+    from miniserve_b200.parts import (LayerRun, LayerSpec, ModelSpec, ParamSpec, Part, PartSpec,
+                                      register_feed_forward, register_position)
+
+    @register_position("toy_sinusoid")
+    class AddedSinusoid(Part):
+        """No fused form: the mixer norms the heads, calls ``apply`` and appends what comes back."""
+
+        def __init__(self, *, head_dim, amplitude):
+            self.head_dim, self.amplitude = head_dim, amplitude
+
+        def fused_args(self, ctx):
+            return None
+
+        def apply(self, q, k, ctx):
+            table = sinusoid(ctx.positions, self.head_dim, self.amplitude, torch.float32)[:, None, :]
+            return (q.float() + table).to(q.dtype), (k.float() + table).to(k.dtype)
+
+    @register_feed_forward("toy_routed")
+    class RoutedExperts(Part):
+        """y = sum over the two best experts e of p_e * down_e(relu(up_e x)), p = softmax of the two router
+        scores; router scores in float32.  Every expert runs on every row and the unchosen ones are
+        weighted 0, so nothing depends on the host knowing the choice."""
+
+        def __init__(self, *, prefix, hidden_size, experts, expert_size):
+            self.prefix, self.hidden, self.experts, self.size = prefix, hidden_size, experts, expert_size
+
+        def param_specs(self):
+            specs = [ParamSpec(self.prefix + "router.weight", (self.experts, self.hidden), "vector")]
+            for e in range(self.experts):
+                specs += [ParamSpec(f"{self.prefix}experts.{e}.up.weight", (self.size, self.hidden)),
+                          ParamSpec(f"{self.prefix}experts.{e}.down.weight", (self.hidden, self.size))]
+            return specs
+
+        def load(self, tensors):
+            self.router = tensors[self.prefix + "router.weight"].float()
+            self.up = [tensors[f"{self.prefix}experts.{e}.up.weight"] for e in range(self.experts)]
+            self.down = [tensors[f"{self.prefix}experts.{e}.down.weight"] for e in range(self.experts)]
+
+        def forward(self, x, ctx):
+            n = x.shape[0]
+            scores = x.float() @ self.router.T
+            best = scores.topk(2, dim=1)
+            weights = torch.zeros_like(scores).scatter_(1, best.indices, best.values.softmax(dim=1))
+            total = torch.zeros((n, self.hidden), dtype=torch.float32, device=x.device)
+            hidden = torch.empty((n, self.size), dtype=x.dtype, device=x.device)
+            out = torch.empty((n, self.hidden), dtype=x.dtype, device=x.device)
+            for e in range(self.experts):
+                kernels.linear(x, self.up[e], hidden)          # the package's own matrix product
+                kernels.linear(hidden.clamp_(min=0), self.down[e], out)
+                total += weights[:, e:e + 1] * out.float()
+            return total.to(x.dtype)
+
+    def build_spec(config: RoutedConfig):
+        rms = lambda name: PartSpec("rms", dict(name=name, size=config.hidden_size, eps=config.eps))
+        common = dict(hidden_size=config.hidden_size, num_heads=config.heads, num_kv_heads=config.kv_heads,
+                      head_dim=config.head_dim, eps=config.eps)
+        layers = [
+            LayerSpec("blocks.0.",
+                      PartSpec("attention", dict(common, qk_norm=True,
+                                                 position=PartSpec("toy_sinusoid", dict(amplitude=config.amplitude)))),
+                      PartSpec("toy_routed", dict(hidden_size=config.hidden_size, experts=config.experts,
+                                                  expert_size=config.expert_size)),
+                      rms("norm_a.weight"), rms("norm_b.weight")),
+            LayerSpec("blocks.1.",
+                      PartSpec("attention", dict(common, qk_norm=False, window=config.window,
+                                                 position=PartSpec("rope", dict(theta=config.theta)))),
+                      PartSpec("gated_mlp", dict(hidden_size=config.hidden_size, intermediate_size=config.inter)),
+                      rms("norm_a.weight"), rms("norm_b.weight")),
+        ]
+        return ModelSpec(vocab_size=config.vocab_size, hidden_size=config.hidden_size, embedding_name="embed.weight",
+                         layers=layers, order=[LayerRun(0), LayerRun(1)], final_norm=rms("final_norm.weight"),
+                         output_name="head.weight", max_positions=4096)
+
+    register_architecture("ToyRoutedForCausalLM", RoutedConfig, build_spec)
+
+
+ROUTED = dict(architectures=["ToyRoutedForCausalLM"], hidden_size=80, vocab_size=131, heads=4, kv_heads=2, head_dim=16,
+              experts=4, expert_size=40, inter=72, window=11, amplitude=0.6, eps=1e-6, theta=3e3)
+
+
+def routed_plain_logits(tokens, w, c):
+    """The routed toy on one whole sequence; also the smallest gap between the second and third router
+    score over all tokens (how far the choice of experts is from a tie)."""
+    n = len(tokens)
+    positions = torch.arange(n)
+    x = w["embed.weight"][torch.tensor(tokens)]
+    heads, kv, d = c["heads"], c["kv_heads"], c["head_dim"]
+
+    def project(h, prefix):
+        return ((h @ w[prefix + "q_proj.weight"].T).view(n, heads, d), (h @ w[prefix + "k_proj.weight"].T).view(n, kv, d),
+                (h @ w[prefix + "v_proj.weight"].T).view(n, kv, d))
+
+    # layer 0: normed heads plus a sinusoid, all keys; two of four experts
+    h = plain.plain_rmsnorm(x, w["blocks.0.norm_a.weight"], c["eps"])
+    q, k, v = project(h, "blocks.0.")
+    table = sinusoid(positions, d, c["amplitude"], torch.float64)[:, None, :]
+    q = plain.plain_rmsnorm(q, w["blocks.0.q_norm.weight"], c["eps"]) + table
+    k = plain.plain_rmsnorm(k, w["blocks.0.k_norm.weight"], c["eps"]) + table
+    x = x + plain.plain_attention(q, k, v, positions).reshape(n, -1) @ w["blocks.0.o_proj.weight"].T
+    h = plain.plain_rmsnorm(x, w["blocks.0.norm_b.weight"], c["eps"])
+    scores = h @ w["blocks.0.router.weight"].T
+    ranked = scores.sort(dim=1, descending=True)
+    gap = float((ranked.values[:, 1] - ranked.values[:, 2]).min())
+    weights = ranked.values[:, :2].softmax(dim=1)
+    mixed = torch.zeros_like(x)
+    for t in range(n):
+        for j in range(2):
+            e = int(ranked.indices[t, j])
+            up, down = w[f"blocks.0.experts.{e}.up.weight"], w[f"blocks.0.experts.{e}.down.weight"]
+            mixed[t] += weights[t, j] * (down @ (up @ h[t]).clamp(min=0))
+    x = x + mixed
+    # layer 1: rotation, a window of keys, gated MLP
+    h = plain.plain_rmsnorm(x, w["blocks.1.norm_a.weight"], c["eps"])
+    q, k, v = project(h, "blocks.1.")
+    cos, sin = plain.plain_rope_tables(positions, d, c["theta"], torch.float64)
+    q, k = plain.plain_apply_rope(q, cos, sin), plain.plain_apply_rope(k, cos, sin)
+    x = x + plain.plain_attention(q, k, v, positions, window=c["window"]).reshape(n, -1) @ w["blocks.1.o_proj.weight"].T
+    h = plain.plain_rmsnorm(x, w["blocks.1.norm_b.weight"], c["eps"])
+    x = x + plain.plain_swiglu(h, w["blocks.1.gate_proj.weight"], w["blocks.1.up_proj.weight"], w["blocks.1.down_proj.weight"])
+    return plain.plain_rmsnorm(x, w["final_norm.weight"], c["eps"]) @ w["head.weight"].T, gap
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
+def test_toy_architecture_with_routing_and_added_positions(tmp_path, dtype, cutting):
+    """A feed-forward with routing and a position encoding without a fused form, both defined above, in
+    one layer; the package's windowed attention (a cache group of its own, pages given back behind the
+    window) and gated MLP in the other.  So that rounding cannot flip the choice of experts, the first
+    columns of the embedding carry a clear mark of (token id mod experts) and the router reads it."""
+    from safetensors.torch import load_file, save_file
+    from test_replay_gpu import CUTTINGS, build, replay
+
+    register_routed_toy()
+    from miniserve_b200.weights import write_random_model
+
+    folder = write_random_model(tmp_path / "routed", ROUTED, seed=12, matrix_std=0.08)
+    tensors = {k: v.clone() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    experts = ROUTED["experts"]
+    ids = torch.arange(ROUTED["vocab_size"])
+    tensors["embed.weight"][:, :experts] = 0
+    tensors["embed.weight"][ids, ids % experts] = 3.0
+    second = (ids % experts + 1 + (ids // experts) % (experts - 1)) % experts      # another column, always
+    tensors["embed.weight"][ids, second] = 1.5                                     # a clear second choice too
+    router = tensors["blocks.0.router.weight"]
+    router.copy_((router.float() - 1.0) * 0.5)                                     # (vectors are drawn around 1)
+    router[:, :experts] += 2.0 * torch.eye(experts).to(router.dtype)
+    save_file(tensors, str(folder / "model.safetensors"))
+
+    requests = {f"t{i}": helpers.random_tokens(ROUTED["vocab_size"], n, seed=800 + i) for i, n in enumerate((2, 13, 31, 45, 66))}
+    steps = CUTTINGS[cutting](requests)
+    pages = (helpers.max_live_tokens(steps, granule=16) + 3) // 4
+    runtime = build(folder, dtype, pages, 4)
+    groups = runtime.model.cache_groups
+    assert [(type(g.need).__name__, g.need.window) for g in groups] == [("PagedKVNeed", None), ("PagedKVNeed", ROUTED["window"])]
+    got = helpers.collect(steps, replay(runtime, steps))
+    _, weights = plain.load_folder(folder, torch.float64)
+    for rid, tokens in requests.items():
+        expected, gap = routed_plain_logits(tokens, weights, ROUTED)
+        assert gap > 0.2, "the router's choice is too close to a tie for this test to mean anything"
+        bound = (3e-5 if dtype == "float32" else 4e-2) * max(1.0, float(expected.abs().max()))
+        for position, row in got[rid].items():
+            assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
+    runtime.manager.check_invariants()
