@@ -180,9 +180,9 @@ def main() -> int:
         args.layers = shape["num_hidden_layers"]
     config = dict(shape, num_hidden_layers=args.layers)
     max_batch = args.batch if args.skip_points else max(args.batch, 64)
-    pages = max_batch * ((CONTEXT + PAGE_SIZE - 1) // PAGE_SIZE) + 64
+    pages = max(max_batch * ((CONTEXT + PAGE_SIZE - 1) // PAGE_SIZE), PREFILL_TOKENS // PAGE_SIZE) + 64
     runtime = build_runtime(None, EngineConfig(
-        dtype="bfloat16", max_model_len=CONTEXT, max_num_seqs=max_batch, kv_block_size=PAGE_SIZE, num_kv_blocks=pages,
+        dtype="bfloat16", max_model_len=max(CONTEXT, PREFILL_TOKENS), max_num_seqs=max_batch, kv_block_size=PAGE_SIZE, num_kv_blocks=pages,
         max_num_batched_tokens=8192, enable_prefix_cache=False,
         decode_execution="eager" if args.profile and not args.timeline else "cuda_graph"),
         config_dict=config, weights_seed=0)

@@ -9,9 +9,13 @@
 //   warp 1      one thread issues tcgen05.mma:  S = Q K^T  into one of two score buffers in tensor memory
 //               (issued one tile ahead, so it overlaps the softmax of the tile before), and  PV = P V  with
 //               P read from tensor memory and V as an MN-major operand from shared memory;
-//   warps 2..5  one thread per query row: read the row of S from tensor memory, mask by absolute position,
-//               keep the running maximum and sum (float32, exp2 with the scale folded in) and write P as
-//               bfloat16 back into tensor memory over the scores it came from.  The output accumulates in
+//   warps 2..9  two threads per query row, one for each half of a tile's keys (a warp reaches only its own
+//               quarter of the tensor-memory lanes, so warps 2..5 take the first half and warps 6..9, which
+//               own the same quarters, the second): read the row of S from tensor memory, mask by absolute
+//               position, agree on the row maximum through shared memory, keep a running sum each
+//               (float32, exp2 with the scale folded in) and write P as bfloat16 back into tensor memory
+//               over the scores it came from.  The softmax sets the pace of the kernel (the MMAs of the
+//               next tile run beside it), so halving a thread's share shortens every tile.  The output accumulates in
 //               tensor memory across the tiles; it is rescaled only when a row's maximum has grown by more
 //               than 2^8 since the last rescale (the exponent then stays small enough for bfloat16 and
 //               float32, and the final division by the row sum makes the result exact all the same).
@@ -24,7 +28,8 @@ namespace t5a {
 
 using namespace ms::t5;
 
-constexpr int ROWS = 128, BN = 128, THREADS = 192, TMEM_COLUMNS = 512;
+constexpr int ROWS = 128, BN = 128, THREADS = 320, TMEM_COLUMNS = 512;
+constexpr int HALF = BN / 2;               // keys of a tile per softmax thread
 // key/value tiles in shared memory: three for head size 128 (32 KB of queries + 3 x 64 KB), four for 64
 template <int D> constexpr int kv_stages() { return D == 128 ? 3 : 4; }
 
@@ -61,15 +66,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   __shared__ uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
   __shared__ uint64_t s_full[2], p_full[2], pv_done;
   __shared__ unsigned tmem_base_s;
+  // [tile parity][half][row]: the two threads of a row agree on its maximum.  Shared memory is full to the
+  // last kilobyte, so the maxima are exchanged as bfloat16, rounded up (any bound above the true maximum
+  // serves: sums and output stay relative to the same value), and the same bytes carry the two row sums
+  // at the end.
+  __shared__ __align__(16) __nv_bfloat16 half_max_s[2][2][ROWS];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_head = blockIdx.y, request = blockIdx.z;
+  // Blocks are handed out in the order of blockIdx.x, then y: with the kv head in x and the query tile in y
+  // (last tiles, which have the most keys, first) the longest blocks of all heads start first, and the short
+  // ones fill the gaps at the end.
+  const int kv_head = blockIdx.x, request = blockIdx.z;
   const int group = n_q / n_kv;
   const int q0 = query_start[request];
   const int q_len = query_start[request + 1] - q0;
   const int ctx = context_lens[request];
   const int rows_total = q_len * group;
-  const int row0 = ((rows_total + ROWS - 1) / ROWS - 1 - (int)blockIdx.x) * ROWS;   // last tiles first
+  const int row0 = ((rows_total + ROWS - 1) / ROWS - 1 - (int)blockIdx.y) * ROWS;   // last tiles first
   const bool active = row0 >= 0;
   const int first_pos = ctx - q_len;
   const int t_lo = active ? row0 / group : 0;
@@ -92,7 +105,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&p_full[b], ROWS);
+      mbar_init(&p_full[b], 2 * ROWS);
     }
     mbar_init(&pv_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -191,49 +204,66 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         }
       }
     } else {
-      // ---------------- softmax and output: one thread per query row
-      const int quarter = warp & 3;
+      // ---------------- softmax and output: two threads per query row, one per half of the tile's keys
+      const int quarter = warp & 3, half = warp >= 6 ? 1 : 0;
       const int local_row = quarter * 32 + lane;
       const int row = row0 + local_row;
       const int pos = first_pos + row / group;
       const unsigned lane_field = (unsigned)(quarter * 32) << 16;
-      const unsigned o_addr = tmem_base + lane_field + o_column;
+      const unsigned o_addr = tmem_base + lane_field + o_column + half * (D / 2);     // this thread's half of the output row
+      // All 256 threads pass this barrier together; it also tells everyone whether anyone gave up a wait,
+      // so that the threads leave the loop together and nobody waits at a barrier alone.
+      auto all_ok = [](bool mine) {
+        unsigned result;
+        asm volatile("{\n.reg .pred p, q;\nsetp.ne.u32 p, %1, 0;\nbar.red.and.pred q, 1, 256, p;\nselp.u32 %0, 1, 0, q;\n}"
+                     : "=r"(result) : "r"((unsigned)mine) : "memory");
+        return result != 0;
+      };
       float m_used = -INFINITY;      // the maximum the exponents and the output are currently relative to
-      float l = 0.f;
+      float l = 0.f;                 // the sum over this thread's half of the keys
       bool ok = true;
-      for (int j = 0; j < n_tiles && ok; ++j) {
+      for (int j = 0; j < n_tiles; ++j) {
         const int b = j & 1;
         const unsigned phase = (j / 2) & 1;
-        const int key0 = tile_begin + j * BN;
-        const bool full = (key0 + BN - 1 <= first_pos + t_lo) && (window <= 0 || key0 >= first_pos + t_hi - window + 1);
-        ok = mbar_wait(&s_full[b], phase, error_flag, 18);
-        if (!ok) break;
-        tmem_fence_after();
-        const unsigned s_addr = tmem_base + lane_field + s_column(b);
-        float v[BN];
-        tmem_load_32_nowait(s_addr, *reinterpret_cast<float(*)[32]>(&v[0]));
-        tmem_load_32_nowait(s_addr + 32, *reinterpret_cast<float(*)[32]>(&v[32]));
-        tmem_load_32_nowait(s_addr + 64, *reinterpret_cast<float(*)[32]>(&v[64]));
-        tmem_load_32_nowait(s_addr + 96, *reinterpret_cast<float(*)[32]>(&v[96]));
-        tmem_load_wait();
-        // eight independent partial maxima (and sums below): a single running value would chain 128 operations
-        float part_max[8];
+        const int key0 = tile_begin + j * BN + half * HALF;
+        const bool full = (tile_begin + j * BN + BN - 1 <= first_pos + t_lo) &&
+                          (window <= 0 || tile_begin + j * BN >= first_pos + t_hi - window + 1);
+        ok = ok && mbar_wait(&s_full[b], phase, error_flag, 18);
+        ok = __all_sync(0xffffffffu, ok);
+        const unsigned s_addr = tmem_base + lane_field + s_column(b) + half * HALF;
+        float v[HALF];
+        float tile_max = -INFINITY;
+        if (ok) {
+          tmem_fence_after();
+          tmem_load_32_nowait(s_addr, *reinterpret_cast<float(*)[32]>(&v[0]));
+          tmem_load_32_nowait(s_addr + 32, *reinterpret_cast<float(*)[32]>(&v[32]));
+          tmem_load_wait();
+          // eight independent partial maxima (and sums below): a single running value would chain 64 operations
+          float part_max[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) part_max[e] = -INFINITY;
-        if (full) {
+          for (int e = 0; e < 8; ++e) part_max[e] = -INFINITY;
+          if (full) {
 #pragma unroll
-          for (int i = 0; i < BN; ++i) part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
-        } else {
+            for (int i = 0; i < HALF; ++i) part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
+          } else {
 #pragma unroll
-          for (int i = 0; i < BN; ++i) {
-            const int key = key0 + i;
-            const bool visible = key <= pos && (window <= 0 || key > pos - window);
-            if (!visible) v[i] = -INFINITY;
-            part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
+            for (int i = 0; i < HALF; ++i) {
+              const int key = key0 + i;
+              const bool visible = key <= pos && (window <= 0 || key > pos - window);
+              if (!visible) v[i] = -INFINITY;
+              part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
+            }
           }
+          tile_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
+                           fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
         }
-        const float tile_max = fmaxf(fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])),
-                                     fmaxf(fmaxf(part_max[4], part_max[5]), fmaxf(part_max[6], part_max[7])));
+        const __nv_bfloat16 bound = __float2bfloat16_ru(tile_max);
+        half_max_s[b][half][local_row] = bound;
+        if (!all_ok(ok)) {
+          ok = false;
+          break;
+        }
+        tile_max = fmaxf(__bfloat162float(bound), __bfloat162float(half_max_s[b][half ^ 1][local_row]));
         const float candidate = fmaxf(m_used, tile_max);
         // rescale when the maximum has grown by more than 8 in the exponent (or was still -inf)
         const bool grow = candidate != -INFINITY && (m_used == -INFINITY || (candidate - m_used) * scale_log2 > 8.f);
@@ -244,51 +274,59 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           if (j > 0) {
             ok = mbar_wait(&pv_done, (j - 1) & 1, error_flag, 19);     // the output must be complete up to tile j - 1
             ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tmem_fence_after();
+            if (ok) {
+              tmem_fence_after();
 #pragma unroll
-            for (int c = 0; c < D; c += 32) {
-              float o[32];
-              tmem_load_32(o_addr + c, o);
-              unsigned scaled[32];
+              for (int c = 0; c < D / 2; c += 32) {
+                float o[32];
+                tmem_load_32(o_addr + c, o);
+                unsigned scaled[32];
 #pragma unroll
-              for (int i = 0; i < 32; ++i) scaled[i] = __float_as_uint(o[i] * factor);
-              tmem_store_32(o_addr + c, scaled);
+                for (int i = 0; i < 32; ++i) scaled[i] = __float_as_uint(o[i] * factor);
+                tmem_store_32(o_addr + c, scaled);
+              }
+              tmem_store_wait();
             }
-            tmem_store_wait();
           }
         }
-        const float base = m_used == -INFINITY ? 0.f : m_used * scale_log2;
-        float part_sum[8];
+        if (ok) {
+          const float base = m_used == -INFINITY ? 0.f : m_used * scale_log2;
+          float part_sum[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) part_sum[e] = 0.f;
+          for (int e = 0; e < 8; ++e) part_sum[e] = 0.f;
 #pragma unroll
-        for (int c = 0; c < BN; c += 32) {
-          unsigned packed[16];
+          for (int c = 0; c < HALF; c += 32) {
+            unsigned packed[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = fast_exp2(v[c + i] * scale_log2 - base);
-            const float p1 = fast_exp2(v[c + i + 1] * scale_log2 - base);
-            part_sum[(i >> 1) & 7] += p0 + p1;
-            const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-            packed[i / 2] = *reinterpret_cast<const unsigned*>(&pair);
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = fast_exp2(v[c + i] * scale_log2 - base);
+              const float p1 = fast_exp2(v[c + i + 1] * scale_log2 - base);
+              part_sum[(i >> 1) & 7] += p0 + p1;
+              const __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+              packed[i / 2] = *reinterpret_cast<const unsigned*>(&pair);
+            }
+            tmem_store_16(tmem_base + lane_field + s_column(b) + (half * HALF + c) / 2, packed);
           }
-          tmem_store_16(s_addr + c / 2, packed);
+          const float sum = ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3])) +
+                            ((part_sum[4] + part_sum[5]) + (part_sum[6] + part_sum[7]));
+          tmem_store_wait();
+          tmem_fence_before();
+          mbar_arrive(&p_full[b]);
+          l += sum;
         }
-        const float sum = ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3])) +
-                          ((part_sum[4] + part_sum[5]) + (part_sum[6] + part_sum[7]));
-        tmem_store_wait();
-        tmem_fence_before();
-        mbar_arrive(&p_full[b]);
-        l += sum;
       }
       if (ok) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, error_flag, 20);
-      if (__all_sync(0xffffffffu, ok)) {
+      ok = __all_sync(0xffffffffu, ok);
+      ok = all_ok(ok);                                 // nobody reads the maxima any more
+      float* half_sum_s = reinterpret_cast<float*>(&half_max_s[0][0][0]);      // [half][row]
+      half_sum_s[half * ROWS + local_row] = l;
+      if (all_ok(ok)) {
         tmem_fence_after();
+        l = half_sum_s[local_row] + half_sum_s[ROWS + local_row];      // the same sum in either thread of the row
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* dst = out + ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group) * D;
+        __nv_bfloat16* dst = out + ((size_t)(q0 + row / group) * n_q + kv_head * group + row % group) * D + half * (D / 2);
 #pragma unroll
-        for (int c = 0; c < D; c += 32) {
+        for (int c = 0; c < D / 2; c += 32) {
           float o[32];
           tmem_load_32(o_addr + c, o);
           if (row < rows_total) {
@@ -352,8 +390,8 @@ int launch(const void* q, const void* k_pool, const void* v_pool, int n_pages, c
     configured = true;
   }
   const long long tiles = ((long long)max_query_len * group + ROWS - 1) / ROWS;
-  MS_REQUIRE(tiles <= 2147483647LL && n_requests <= 65535 && n_kv <= 65535, "attention_tcgen05: grid exceeds the launch limits");
-  dim3 grid((unsigned)tiles, n_kv, n_requests);
+  MS_REQUIRE(tiles <= 65535 && n_requests <= 65535, "attention_tcgen05: grid exceeds the launch limits");
+  dim3 grid(n_kv, (unsigned)tiles, n_requests);
   cudaError_t e = ms::launch(kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, block_tables, table_stride,
                              query_start, context_lens, page_size, n_q, n_kv, scale * 1.4426950408889634f, window,
                              (__nv_bfloat16*)out, error_flag);
