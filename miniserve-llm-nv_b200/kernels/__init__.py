@@ -458,7 +458,7 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> N
 SKINNY_MAX_ROWS = 8    # above this the weight-streaming kernel re-reads the activations too often
 
 
-FUSE_GATED_INPUT = False    # applying the activation while streaming recomputes it in every block: slower
+FUSE_GATED_INPUT = False    # applying the activation while streaming recomputes it in every block: slower (measured twice)
 
 
 def gated_linear(gate_up: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
