@@ -1,15 +1,18 @@
 // out[M, N] = X[M, K] * W[N, K]^T on the fifth-generation tensor cores (tcgen05), for the many-row
 // products of prompt portions.  bfloat16 operands, float32 accumulation in tensor memory.
 //
-// One thread block computes one 128 x BN tile of the output:
+// One thread block per multiprocessor walks over 128 x BN tiles of the output (tile blockIdx.x, then every
+// gridDim.x-th; tiles that are neighbours in this order share their W tile, so the blocks running at a time
+// read few different W tiles):
 //   warp 0      one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of the X and W
 //               tiles of each 64-wide k-block into a ring of shared-memory stages and announces them on
-//               per-stage "full" mbarriers;
-//   warp 1      allocates BN columns of tensor memory; one thread issues tcgen05.mma (M 128, N BN, K 16,
-//               four per k-block) reading the stages through shared-memory descriptors, and releases each
-//               stage with tcgen05.commit on its "empty" mbarrier; a last commit announces the accumulator;
-//   warps 2..5  read the accumulator out of tensor memory (tcgen05.ld, one output row per thread),
-//               apply the epilogue and store.
+//               per-stage "full" mbarriers; it runs on into the next tile while the last is finished;
+//   warp 1      allocates tensor memory for two accumulators; one thread issues tcgen05.mma (M 128, N BN,
+//               K 16, four per k-block) reading the stages through shared-memory descriptors, and releases
+//               each stage with tcgen05.commit on its "empty" mbarrier; a last commit per tile announces
+//               the accumulator, and the next tile goes to the other one;
+//   warps 2..5  read an accumulator out of tensor memory (tcgen05.ld, one output row per thread),
+//               apply the epilogue and store, while the next tile is being accumulated.
 // Epilogues: plain store (bfloat16 or float32), or add into a float32 matrix in place (the residual
 // stream), which spares a separate pass over it.
 //
@@ -37,13 +40,15 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     OutT* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
   using Layout = SharedLayout<BN, STAGES>;
+  constexpr int ACCUMULATORS = 2;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACCUMULATORS], acc_empty[ACCUMULATORS];
   __shared__ unsigned tmem_base_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
   const int num_k = (K + BK - 1) / BK;
 
   if (warp == 0 && lane == 0) {
@@ -52,11 +57,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&accum_bar, 1);
+#pragma unroll
+    for (int b = 0; b < ACCUMULATORS; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);         // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ACCUMULATORS * BN) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tmem_fence_before();
@@ -69,22 +78,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
   if (warp == 0) {
     if (lane == 0) {
-      // ---------------- producer: TMA loads
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int stage = kb % STAGES;
-        const unsigned phase = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty_bar[stage], phase ^ 1, error_flag, 1)) break;
-        unsigned char* a_s = smem + (size_t)stage * Layout::STAGE_BYTES;
-        unsigned char* b_s = a_s + Layout::A_BYTES;
-        mbar_expect_tx(&full_bar[stage], Layout::STAGE_BYTES);
-        tma_load_2d(a_s, &map_x, &full_bar[stage], kb * BK, tile_m * BM);
-        if (!W_TRANSPOSED) {
-          tma_load_2d(b_s, &map_w, &full_bar[stage], kb * BK, tile_n * BN);
-        } else {
-          // W stored [K, N]: one box of 64 n x 64 k per block of 64 output columns
+      // ---------------- producer: TMA loads, one running count of k-blocks over all tiles of this block
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int stage = it % STAGES;
+          const unsigned phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, error_flag, 1))) break;
+          unsigned char* a_s = smem + (size_t)stage * Layout::STAGE_BYTES;
+          unsigned char* b_s = a_s + Layout::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], Layout::STAGE_BYTES);
+          tma_load_2d(a_s, &map_x, &full_bar[stage], kb * BK, tile_m * BM);
+          if (!W_TRANSPOSED) {
+            tma_load_2d(b_s, &map_w, &full_bar[stage], kb * BK, tile_n * BN);
+          } else {
+            // W stored [K, N]: one box of 64 n x 64 k per block of 64 output columns
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_2d(b_s + j * (BK * 128), &map_w, &full_bar[stage], tile_n * BN + j * 64, kb * BK);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_s + j * (BK * 128), &map_w, &full_bar[stage], tile_n * BN + j * 64, kb * BK);
+          }
         }
       }
     }
@@ -92,41 +106,53 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     if (lane == 0) {
       // ---------------- MMA issue
       constexpr unsigned idesc = umma_idesc(BM, BN, W_TRANSPOSED);
+      int it = 0, done = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_k && ok; ++kb) {
-        const int stage = kb % STAGES;
-        const unsigned phase = (kb / STAGES) & 1;
-        ok = mbar_wait(&full_bar[stage], phase, error_flag, 2);
-        if (!ok) break;
-        tmem_fence_after();
-        unsigned char* a_s = smem + (size_t)stage * Layout::STAGE_BYTES;
-        unsigned char* b_s = a_s + Layout::A_BYTES;
-        const uint64_t a_desc = umma_desc(a_s), b_desc = umma_desc(b_s);
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++done) {
+        const int buf = done % ACCUMULATORS;
+        if (!(ok = mbar_wait(&acc_empty[buf], ((done / ACCUMULATORS) & 1) ^ 1, error_flag, 4))) break;
+        const unsigned accumulator = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int stage = it % STAGES;
+          const unsigned phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&full_bar[stage], phase, error_flag, 2))) break;
+          tmem_fence_after();
+          unsigned char* a_s = smem + (size_t)stage * Layout::STAGE_BYTES;
+          unsigned char* b_s = a_s + Layout::A_BYTES;
+          const uint64_t a_desc = umma_desc(a_s), b_desc = umma_desc(b_s);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          // advancing 16 elements (32 bytes) along K inside the 128-byte swizzled row: +2 in 16-byte units
-          if (!W_TRANSPOSED) {
-            umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          } else {
-            // 16 k-rows of 128 bytes further per step; the blocks of 64 n are BK * 128 bytes apart
-            umma_bf16(tmem_base, a_desc + 2 * k, umma_desc_mn_major(b_s + k * (UMMA_K * 128), BK * 128), idesc,
-                      (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 elements (32 bytes) along K inside the 128-byte swizzled row: +2 in 16-byte units
+            if (!W_TRANSPOSED) {
+              umma_bf16(accumulator, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            } else {
+              // 16 k-rows of 128 bytes further per step; the blocks of 64 n are BK * 128 bytes apart
+              umma_bf16(accumulator, a_desc + 2 * k, umma_desc_mn_major(b_s + k * (UMMA_K * 128), BK * 128), idesc,
+                        (kb | k) != 0 ? 1u : 0u);
+            }
           }
+          umma_commit(&empty_bar[stage]);      // the stage is free once these MMAs have read it
         }
-        umma_commit(&empty_bar[stage]);      // the stage is free once these MMAs have read it
+        if (ok) umma_commit(&acc_full[buf]);   // the accumulator is complete once all MMAs have finished
       }
-      umma_commit(&accum_bar);               // the accumulator is complete once all MMAs have finished
     }
   } else {
     // ---------------- epilogue: warps 2..5 own the tensor-memory lane quarters 2, 3, 0, 1
     const int quarter = warp & 3;
-    const int row = tile_m * BM + quarter * 32 + lane;
-    if (mbar_wait(&accum_bar, 0, error_flag, 3)) {
+    int done = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++done) {
+      const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+      const int buf = done % ACCUMULATORS;
+      const int row = tile_m * BM + quarter * 32 + lane;
+      ok = ok && mbar_wait(&acc_full[buf], (done / ACCUMULATORS) & 1, error_flag, 3);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tmem_fence_after();
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         float v[32];
-        tmem_load_32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c, v);
+        tmem_load_32(tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * BN + c), v);
         const int col = tile_n * BN + c;
         if (row < M && col < N) {
           OutT* dst = out + (size_t)row * N + col;
@@ -167,6 +193,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
         }
       }
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);      // the accumulator may be overwritten
     }
   }
 
@@ -174,7 +203,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tmem_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(BN) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACCUMULATORS * BN) : "memory");
   }
 }
 
@@ -206,8 +235,16 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int* er
     if (e != cudaSuccess) MS_FAIL("gemm_tcgen05: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  MS_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d rows in one launch is too many", M);
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 1;
+  }
+  const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  MS_REQUIRE(tiles <= 2147483647LL, "gemm_tcgen05: %lld tiles in one launch is too many", tiles);
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms));
   cudaError_t e = ms::launch(kernel, grid, dim3(THREADS), smem, stream, map_x, map_w, (OutT*)out, M, N, K, error_flag);
   if (e != cudaSuccess) MS_FAIL("gemm_tcgen05: launch failed: %s", cudaGetErrorString(e));
   return 0;
@@ -229,7 +266,15 @@ MS_EXPORT int ms_gemm_tcgen05(const void* X, const void* W, void* out, int out_d
   MS_REQUIRE(K > 0 && K % 8 == 0, "gemm_tcgen05: inner size %d is not a multiple of 8", K);
   MS_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05: operands must be 16-byte aligned");
   MS_REQUIRE(error_flag != nullptr, "gemm_tcgen05: an error flag on the device is required");
-  const bool narrow = N <= 2048;      // more, smaller tiles when the output is narrow
+  // 128 x 256 tiles unless the narrower 128 x 128 ones fill the multiprocessors' waves better
+  int sms = 148;
+  {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const long long rows = (M + 127) / 128;
+  const long long waves_wide = (rows * ((N + 255) / 256) + sms - 1) / sms, waves_narrow = (rows * ((N + 127) / 128) + sms - 1) / sms;
+  const bool narrow = waves_narrow * 128 * 5 < waves_wide * 256 * 4;     // (a narrow tile does less per byte it loads)
   if (epilogue == t5::EPI_ADD_F32) {
     MS_REQUIRE(out_dtype == MS_F32, "gemm_tcgen05: the adding epilogue works on a float32 matrix");
     return narrow ? t5::launch<128, 6, t5::EPI_ADD_F32, float>(X, W, out, M, N, K, error_flag, stream)
