@@ -1,6 +1,6 @@
 """The reference arm of ``bench.py``: MiniServe-LLM-NV itself, unmodified, from ``baseline/_ref``.
 
-Install (once, offline; recorded in DESIGN.md):
+Install (once, offline):
 
     cp -r /path/to/MiniServe-LLM-NV /tmp/ref_copy
     python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse \
