@@ -65,8 +65,10 @@ def run(model: dict, batch: int, context: int, steps: int, warmup: int, page_siz
                       kv_manager=manager)
 
     generator = torch.Generator().manual_seed(1)
-    prompt_len = context - steps - warmup - 1
-    new_tokens = steps + warmup + 1
+    # MiniServe runs one whole prompt per step while the earlier requests already decode: the first request
+    # has decoded `batch` tokens before the last prompt is in, so every request gets that many tokens more
+    new_tokens = steps + warmup + batch + 2
+    prompt_len = context - new_tokens
     with torch.no_grad():
         for index in range(batch):
             prompt = tuple(torch.randint(0, model["vocab_size"], (prompt_len,), generator=generator).tolist())
