@@ -115,6 +115,9 @@ def reference_arm(args) -> int:
         print(json.dumps({"impl": "reference", "unavailable": "MiniServe runs on one GPU only"}))
         return 0
     warmup = max(args.warmup, 3)
+    if args.steps < 1 or args.steps + warmup + 16 > CONTEXT:
+        print(f"bench.py: --steps {args.steps} does not fit the context of {CONTEXT} tokens (or is not positive)")
+        return 2
     steps = min(args.steps, 64)
     result = arm.main(dict(MODEL), args.batch, CONTEXT, steps, warmup, PAGE_SIZE)
     if "unavailable" in result:
@@ -411,6 +414,8 @@ def main() -> int:
                      "bytes_per_step": int(step_bytes)},
         "points": points,
         "clocks": clock_summary,
+        # which kernel the measurement at start-up chose for the few-row products of each weight shape
+        "few_row_products": {f"{n}x{k}": choice for (_, n, k), choice in sorted(kernels.linear_choices().items())},
     }
     print(json.dumps(line))
     return 0

@@ -421,7 +421,7 @@ def _measure_few_rows(weight: torch.Tensor) -> str:
     for name, run in candidates.items():
         run()                                                               # lazy set-up outside the timing
         samples = []
-        for _ in range(5):
+        for _ in range(9):
             flush.zero_()
             start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             start.record()
