@@ -86,6 +86,49 @@ def test_cuttings_match_plain(tmp_path, dtype, name, page_size, cutting):
     print(f"worst error / bound = {worst:.3f}")
 
 
+REAL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=2048, intermediate_size=6144,
+            num_hidden_layers=2, num_attention_heads=16, num_key_value_heads=8, head_dim=128, vocab_size=151936,
+            max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_dropout=0.0,
+            hidden_act="silu", attention_bias=False, tie_word_embeddings=True)
+_real: dict = {}
+
+
+@pytest.fixture(scope="module")
+def real_model(tmp_path_factory):
+    """Two layers of Qwen3-1.7B's sizes (full vocabulary, tied) with random weights, and the plain logits
+    of three short requests; made once for the tests below."""
+    if not _real:
+        import miniserve_b200  # noqa: F401
+        from miniserve_b200.weights import write_random_model
+
+        folder = write_random_model(tmp_path_factory.mktemp("real") / "model", REAL, seed=3)
+        requests = {f"q{i}": helpers.random_tokens(REAL["vocab_size"], n, seed=900 + i) for i, n in enumerate((5, 70, 41))}
+        _real.update(folder=folder, requests=requests,
+                     expected={rid: helpers.oracle_logits(folder, tokens) for rid, tokens in requests.items()})
+    return _real
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["tail", "mixed"])
+def test_layers_of_real_size(real_model, dtype, cutting):
+    """Qwen3-1.7B's layer sizes (hidden 2,048, 16 / 8 heads of 128, intermediate 6,144, 151,936 tokens):
+    the kernels that the benchmark times (tcgen05 attention of prompt portions, split-key decode attention,
+    the few-row products in whichever form was measured fastest, the output matrix) against the plain
+    implementation, with 64-token pages as there."""
+    requests = real_model["requests"]
+    steps = CUTTINGS[cutting](requests)
+    pages = (helpers.max_live_tokens(steps, granule=128) + 63) // 64
+    runtime = build(real_model["folder"], dtype, pages, 64)
+    got = helpers.collect(steps, replay(runtime, steps))
+    for rid, tokens in requests.items():
+        expected = real_model["expected"][rid]
+        bound = error_bounds(dtype, expected)
+        assert sorted(got[rid]) == list(range(len(tokens)))
+        for position, row in got[rid].items():
+            assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
+    assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
+
+
 @pytest.mark.parametrize("name,page_size", [("d", 16), ("b", 8)])
 def test_whole_prompts_through_the_tcgen05_products(tmp_path, monkeypatch, name, page_size):
     """The library's own tcgen05 matrix product in place of cuBLAS for portions of 128 rows and more."""
