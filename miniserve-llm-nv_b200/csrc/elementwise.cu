@@ -276,12 +276,21 @@ MS_EXPORT int ms_qk_norm_rope_append(const void* qkv, int dtype, const int* slot
     const int heads_per_warp = 32 / lanes;
     const long long warps_needed = (items + heads_per_warp - 1) / heads_per_warp;
     const long long vec_blocks = (warps_needed + warps - 1) / warps;
-#define MS_ROPE_VEC(L)                                                                                              \
-  MS_DISPATCH(dtype, (ms::launch(qk_norm_rope_append_vec_kernel<T, L>, (unsigned)vec_blocks, warps * 32, 0, stream, \
-                                 (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, cos_sin, rotary_dim,  \
+    // half-split rotation over the whole head: each lane holds an element group and its partner group
+    const bool pairs = cos_sin != nullptr && !interleaved && rotary_dim == d && pow2;
+#define MS_ROPE_VEC(L, P)                                                                                              \
+  MS_DISPATCH(dtype, (ms::launch(qk_norm_rope_append_vec_kernel<T, L, P>, (unsigned)vec_blocks, warps * 32, 0, stream, \
+                                 (const T*)qkv, slots, q_weight, k_weight, weight_dtype, eps, cos_sin, rotary_dim,     \
                                  interleaved, (T*)k_pool, (T*)v_pool, page_size, n_q, n_kv, d, (T*)q_out, n_tokens)))
-    if (lanes == 2) { MS_ROPE_VEC(2); } else if (lanes == 4) { MS_ROPE_VEC(4); } else if (lanes == 8) { MS_ROPE_VEC(8); }
-    else if (lanes == 16) { MS_ROPE_VEC(16); } else { MS_ROPE_VEC(32); }
+    if (pairs) {
+      if (lanes == 2) { MS_ROPE_VEC(2, true); } else if (lanes == 4) { MS_ROPE_VEC(4, true); }
+      else if (lanes == 8) { MS_ROPE_VEC(8, true); } else if (lanes == 16) { MS_ROPE_VEC(16, true); }
+      else { MS_ROPE_VEC(32, true); }
+    } else {
+      if (lanes == 2) { MS_ROPE_VEC(2, false); } else if (lanes == 4) { MS_ROPE_VEC(4, false); }
+      else if (lanes == 8) { MS_ROPE_VEC(8, false); } else if (lanes == 16) { MS_ROPE_VEC(16, false); }
+      else { MS_ROPE_VEC(32, false); }
+    }
 #undef MS_ROPE_VEC
     MS_CHECK_LAUNCH("qk_norm_rope_append");
     return 0;

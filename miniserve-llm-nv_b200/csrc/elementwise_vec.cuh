@@ -52,6 +52,36 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const Vec8& x) {
   *reinterpret_cast<uint4*>(p) = raw;
 }
 
+// Four consecutive elements into v[offset .. offset + 3].
+__device__ __forceinline__ void load4(const float* p, Vec8& r, int offset) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  r.v[offset] = a.x; r.v[offset + 1] = a.y; r.v[offset + 2] = a.z; r.v[offset + 3] = a.w;
+}
+
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, Vec8& r, int offset) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 a = __bfloat1622float2(pairs[0]), b = __bfloat1622float2(pairs[1]);
+  r.v[offset] = a.x; r.v[offset + 1] = a.y; r.v[offset + 2] = b.x; r.v[offset + 3] = b.y;
+}
+
+__device__ __forceinline__ void load4_any(const void* p, int dtype, size_t index, Vec8& r, int offset) {
+  if (dtype == MS_F32) load4(reinterpret_cast<const float*>(p) + index, r, offset);
+  else load4(reinterpret_cast<const __nv_bfloat16*>(p) + index, r, offset);
+}
+
+__device__ __forceinline__ void store4(float* p, const Vec8& x, int offset) {
+  *reinterpret_cast<float4*>(p) = make_float4(x.v[offset], x.v[offset + 1], x.v[offset + 2], x.v[offset + 3]);
+}
+
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const Vec8& x, int offset) {
+  uint2 raw;
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+  pairs[0] = __floats2bfloat162_rn(x.v[offset], x.v[offset + 1]);
+  pairs[1] = __floats2bfloat162_rn(x.v[offset + 2], x.v[offset + 3]);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 // One block per output row; each thread keeps up to CHUNKS groups of eight elements in registers,
 // so the row is read once.  Requires hidden % 8 == 0 and hidden <= 8 * blockDim.x * CHUNKS.
@@ -106,7 +136,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
 // the warp to itself (LANES = 32, lanes beyond d / 8 idle).  d <= 256, d % 8 == 0.  Half-split rotation
 // needs rotary_dim % 16 == 0 so that an element's partner sits at the same place in another lane of the
 // group; interleaved pairs sit within a lane.
-template <typename T, int LANES>
+// PAIRS (half-split rotation over the whole head, the usual case): lane l holds elements 4l .. 4l+3 and
+// their partners d/2 + 4l .. d/2 + 4l+3 instead, so the rotation needs no exchange between lanes (the
+// kernel is bound by the shuffles and loads it issues, not by arithmetic or bandwidth).
+template <typename T, int LANES, bool PAIRS = false>
 __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const int* __restrict__ slots,
                                                const void* __restrict__ q_weight, const void* __restrict__ k_weight,
                                                int weight_dtype, float eps, const float* __restrict__ cos_sin,
@@ -135,8 +168,9 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
     }
   }
   const T* src = qkv + ((size_t)n * heads + head) * d;
-  const int c0 = sub_lane * 8;
-  bool active = item_ok && c0 < d;
+  const int c0 = PAIRS ? sub_lane * 4 : sub_lane * 8;      // PAIRS: also elements c0 + d/2 ..
+  const int c1 = c0 + (d >> 1);
+  bool active = item_ok && (PAIRS ? c0 < (d >> 1) : c0 < d);
 
   T* dst = nullptr;
   const void* weight = nullptr;
@@ -162,7 +196,14 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
   Vec8 x;
 #pragma unroll
   for (int e = 0; e < 8; ++e) x.v[e] = 0.f;
-  if (active) x = load8(src + c0);
+  if (active) {
+    if (PAIRS) {
+      load4(src + c0, x, 0);
+      load4(src + c1, x, 4);
+    } else {
+      x = load8(src + c0);
+    }
+  }
   {
     float sum_sq = 0.f;
 #pragma unroll
@@ -171,7 +212,13 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
     for (int o = LANES / 2; o > 0; o >>= 1) sum_sq += __shfl_xor_sync(0xffffffffu, sum_sq, o);
     if (weight && active) {
       const float inv = 1.0f / sqrtf(sum_sq / (float)d + eps);
-      const Vec8 w = load8_any(weight, weight_dtype, c0);
+      Vec8 w;
+      if (PAIRS) {
+        load4_any(weight, weight_dtype, c0, w, 0);
+        load4_any(weight, weight_dtype, c1, w, 4);
+      } else {
+        w = load8_any(weight, weight_dtype, c0);
+      }
 #pragma unroll
       for (int e = 0; e < 8; ++e) x.v[e] = x.v[e] * inv * w.v[e];
     }
@@ -179,7 +226,18 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
   if (cos_sin != nullptr) {                                  // uniform: every lane takes part in the shuffles
     const int half = rotary_dim >> 1;
     const float* table = cos_sin + (size_t)n * rotary_dim;       // [half][2] floats
-    if (interleaved) {
+    if (PAIRS) {
+      if (rotate && active) {
+        const Vec8 cs = load8(table + 2 * c0);                   // (cos, sin) of pairs c0 .. c0+3
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float c = cs.v[2 * e], sn = cs.v[2 * e + 1];
+          const float a = x.v[e], b = x.v[4 + e];
+          x.v[e] = a * c - b * sn;
+          x.v[4 + e] = b * c + a * sn;
+        }
+      }
+    } else if (interleaved) {
       if (rotate && active && c0 < rotary_dim) {
         const Vec8 cs = load8(table + c0);                       // (cos, sin) of pairs c0/2 .. c0/2+3
         Vec8 y;
@@ -214,7 +272,11 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
     }
   }
   if (active) {
-    if (is_value) {
+    if (PAIRS) {
+      // (a value passed through float and back is the same value)
+      store4(dst + c0, x, 0);
+      store4(dst + c1, x, 4);
+    } else if (is_value) {
       // values are copied bit for bit
       *reinterpret_cast<uint4*>(dst + c0) = *reinterpret_cast<const uint4*>(src + c0);
       if (sizeof(T) == 4) *reinterpret_cast<uint4*>(dst + c0 + 4) = *reinterpret_cast<const uint4*>(src + c0 + 4);
