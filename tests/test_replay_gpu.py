@@ -129,6 +129,37 @@ def test_layers_of_real_size(real_model, dtype, cutting):
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
 
 
+def test_generation_at_real_size_graph_against_eager(real_model):
+    """Greedy tokens at Qwen3-1.7B's layer sizes: replayed graphs with decoding one step ahead (the path the
+    benchmark times) against eager steps, and the first tokens against the plain implementation."""
+    import plain_qwen3 as plain
+    from miniserve_b200.engine.llm import LLM
+    from miniserve_b200.sampling import SamplingParams
+
+    prompts = [tokens for tokens in real_model["requests"].values()]
+    params = SamplingParams(temperature=0.0, max_new_tokens=12)
+    outcomes = {}
+    for execution, look_ahead in (("eager", False), ("cuda_graph", True)):
+        llm = LLM(str(real_model["folder"]), dtype="bfloat16", kv_block_size=64, num_kv_blocks=16, max_num_seqs=4,
+                  max_model_len=256, decode_execution=execution, decode_look_ahead=look_ahead)
+        outcomes[execution] = [r.token_ids for r in llm.generate(prompts, params)]
+        del llm
+        torch.cuda.empty_cache()
+    config, weights = plain.load_folder(real_model["folder"], torch.float64)
+    for prompt, eager, graph in zip(prompts, outcomes["eager"], outcomes["cuda_graph"]):
+        tokens = list(prompt)
+        for index, (a, b) in enumerate(zip(eager, graph)):
+            if a != b or index < 3:
+                # a difference between the two paths, like one from the plain rule, must be a near tie
+                logits = plain.plain_logits(tokens, weights, config)[-1]
+                limit = 4e-2 * max(1.0, float(logits.abs().max()))
+                best = int(logits.argmax())
+                assert float(logits[best] - logits[a]) <= limit and float(logits[best] - logits[b]) <= limit, (index, a, b, best)
+            if a != b:
+                break                      # after a tie broken differently the sequences are different ones
+            tokens.append(a)
+
+
 @pytest.mark.parametrize("name,page_size", [("d", 16), ("b", 8)])
 def test_whole_prompts_through_the_tcgen05_products(tmp_path, monkeypatch, name, page_size):
     """The library's own tcgen05 matrix product in place of cuBLAS for portions of 128 rows and more."""
