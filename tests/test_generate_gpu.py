@@ -148,3 +148,45 @@ def test_decoding_one_step_ahead_on_the_device(tmp_path, dtype):
         if look_ahead:
             assert llm.runtime.step_function.graph_replays > 0
     assert outcomes[True] == outcomes[False]
+
+
+def test_requests_arriving_while_others_decode(tmp_path):
+    """Thirty requests of random lengths, budgets and sampling settings arrive a few at a time while the
+    engine runs (replayed graphs, decoding ahead, a prefix cache, so few pages that requests are preempted
+    and recomputed); every request's tokens follow the plain rule from its own prompt and seed."""
+    import random
+
+    from miniserve_b200.engine.llm import LLM
+    from miniserve_b200.sampling import SamplingParams
+
+    folder = helpers.make_folder(tmp_path, "c", seed=11)
+    vocab = helpers.TINY["c"]["vocab_size"]
+    rng = random.Random(5)
+    llm = LLM(str(folder), dtype="float32", kv_block_size=4, num_kv_blocks=24, max_num_seqs=4, max_num_batched_tokens=32,
+              max_pending_requests=64, decode_execution="cuda_graph")
+    engine = llm.engine
+    shared = helpers.random_tokens(vocab, 12, seed=77)
+    submitted = {}
+    for index in range(30):
+        prompt = (shared if index % 3 == 0 else []) + helpers.random_tokens(vocab, rng.randint(1, 40), seed=1000 + index)
+        params = SamplingParams(temperature=rng.choice([0.0, 0.0, 0.7]), top_k=rng.choice([0, 0, 5]), seed=index,
+                                max_new_tokens=rng.randint(1, 20))
+        submitted[f"s{index}"] = (prompt, params)
+    waiting = list(submitted.items())
+    steps = 0
+    while waiting or engine.has_unfinished():
+        for _ in range(rng.randint(0, 2)):
+            if waiting:
+                rid, (prompt, params) = waiting.pop(0)
+                engine.submit(rid, prompt, params)
+        engine.step()
+        steps += 1
+        assert steps < 3000
+    engine.run_until_done()
+    assert engine.stats.preemptions > 0 and engine.stats.prefix_hit_tokens > 0
+    for rid, (prompt, params) in submitted.items():
+        result = engine.finished[rid]
+        assert result.finish_reason == "length" and len(result.token_ids) == params.max_new_tokens
+        check_against_plain(folder, prompt, result.token_ids, params, "float32", seed=params.seed)
+    llm.runtime.manager.check_invariants()
+    assert not llm.runtime.manager.requests
