@@ -141,7 +141,7 @@ def reference_arm(args) -> int:
 
 
 def main() -> int:
-    global CONTEXT
+    global CONTEXT, PREFILL_TOKENS
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=64)
@@ -157,10 +157,13 @@ def main() -> int:
     parser.add_argument("--shape", choices=sorted(SHAPES), default="1.7b",
                         help="layer sizes of another model of the family (the default is the benchmark's)")
     parser.add_argument("--context", type=int, default=CONTEXT, help="tokens a request holds at the end of the timed steps")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                        help="tokens of the timed prompt step (the benchmark's is 2,048; others for profiles)")
     parser.add_argument("--profile", choices=("decode", "prefill"), default=None,
                         help="run only a few eager steps of one phase and exit (a small case for ncu; times nothing)")
     args = parser.parse_args()
     CONTEXT = args.context
+    PREFILL_TOKENS = args.prefill_tokens
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:
@@ -186,7 +189,7 @@ def main() -> int:
     pages = max(max_batch * ((CONTEXT + PAGE_SIZE - 1) // PAGE_SIZE), PREFILL_TOKENS // PAGE_SIZE) + 64
     runtime = build_runtime(None, EngineConfig(
         dtype="bfloat16", max_model_len=max(CONTEXT, PREFILL_TOKENS), max_num_seqs=max_batch, kv_block_size=PAGE_SIZE, num_kv_blocks=pages,
-        max_num_batched_tokens=8192, enable_prefix_cache=False,
+        max_num_batched_tokens=max(8192, PREFILL_TOKENS), enable_prefix_cache=False,
         decode_execution="eager" if args.profile and not args.timeline else "cuda_graph"),
         config_dict=config, weights_seed=0)
     manager, step_function = runtime.manager, runtime.step_function
