@@ -125,7 +125,7 @@ def reference_arm(args) -> int:
         return 0
     line = {
         "metric": f"Qwen3-{args.shape.upper()} bf16 decode tok/s @ batch {args.batch} (context {CONTEXT}); "
-                  f"prefill tok/s @ 2,048 tokens",
+                  f"prefill tok/s @ {PREFILL_TOKENS:,} tokens",
         "impl": "reference", "value": result["value"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": result["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random weights)",
@@ -392,7 +392,7 @@ def main() -> int:
     value = args.batch / step_seconds
     line = {
         "metric": f"Qwen3-{args.shape.upper()} bf16 decode tok/s @ batch {args.batch} (context {CONTEXT}); "
-                  f"prefill tok/s @ 2,048 tokens",
+                  f"prefill tok/s @ {PREFILL_TOKENS:,} tokens",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": round(step_seconds * 1e3, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random weights)",
