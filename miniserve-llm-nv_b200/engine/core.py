@@ -164,8 +164,17 @@ class Engine:
                    for i, s in enumerate(sequences)]
         try:
             handle = self.executor.execute_deferred(entries, reservation, samples, feed_back=True)
-        except BaseException:
+        except BaseException as error:
+            # as in an ordinary step: pages and lengths as before it, its requests failed; the tokens of the
+            # step before are still read
             self.manager.abort(reservation)
+            self.stats.failed_steps += 1
+            self._read_pending()
+            for seq in sequences:
+                if not seq.done:
+                    seq.finish(f"error: {type(error).__name__}", failed=True)
+            if isinstance(error, Exception):
+                self._finalize()
             raise
         self.manager.commit(reservation)
         self._read_pending()                 # the device is busy with the new step meanwhile

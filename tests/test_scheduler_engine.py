@@ -286,3 +286,30 @@ def test_look_ahead_yields_to_a_new_request():
     engine.run_until_done()
     assert engine.finished["a"].token_ids == expected_tokens([1, 2, 3], 10)
     assert engine.finished["b"].token_ids == expected_tokens([4, 5, 6, 7, 8], 6)
+
+
+def test_failure_of_a_step_started_ahead():
+    """The device refuses the step that was started ahead: the reservation is undone, the tokens of the
+    step before are kept, the requests end as failed and give their pages back."""
+    manager = CacheManager([GROUP], 4, 32, 4, enable_prefix_cache=False)
+    executor = DeferringExecutor()
+    engine = Engine(manager, Scheduler(max_num_seqs=4, max_num_batched_tokens=24), executor, vocab_size=97,
+                    max_model_len=256, look_ahead=True)
+    engine.submit("a", [1, 2, 3], SamplingParams(max_new_tokens=10))
+    for _ in range(3):
+        engine.step()
+    produced = len(engine.sequences["a"].generated)
+    original = executor.execute_deferred
+
+    def refuse(*args, **kwargs):
+        raise RuntimeError("device lost")
+
+    executor.execute_deferred = refuse
+    with pytest.raises(RuntimeError):
+        engine.step()
+    executor.execute_deferred = original
+    result = engine.finished["a"]
+    assert result.finish_reason == "error: RuntimeError"
+    assert result.token_ids == expected_tokens([1, 2, 3], produced + 1)      # the pending token was still read
+    manager.check_invariants()
+    assert not manager.requests and manager.capacity().free_pages == (32,)
