@@ -405,7 +405,9 @@ def linear_choices() -> dict:
 
 def _measure_few_rows(weight: torch.Tensor) -> str:
     """Times the candidates for ``[8, K] @ weight[N, K]^T`` on the device: the faster of this library's two
-    kernels, unless the vendor library is clearly (3 %) faster than both."""
+    kernels, unless the vendor library is clearly (8 %) faster than both.  The margin is what this library's
+    kernels gain inside a step, where they start while the kernel before them ends (programmatic dependent
+    launch) and the vendor's do not: measured alone, 3 % apart, they come out even in the step."""
     n, k = weight.shape
     device = weight.device
     x = torch.zeros((SKINNY_MAX_ROWS, k), dtype=torch.bfloat16, device=device)
@@ -431,7 +433,7 @@ def _measure_few_rows(weight: torch.Tensor) -> str:
             samples.append(start.elapsed_time(end))
         times[name] = sorted(samples)[len(samples) // 2]
     own = "stream" if times["stream"] < times["skinny"] else "skinny"
-    return "library" if times["library"] < 0.97 * times[own] else own
+    return "library" if times["library"] < 0.92 * times[own] else own
 
 
 def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
