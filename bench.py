@@ -418,7 +418,8 @@ def main() -> int:
         "points": points,
         "clocks": clock_summary,
         # which kernel the measurement at start-up chose for the few-row products of each weight shape
-        "few_row_products": {f"{n}x{k}": choice for (_, n, k), choice in sorted(kernels.linear_choices().items())},
+        "few_row_products": {**{f"{n}x{k}": choice for (_, n, k), choice in sorted(kernels.linear_choices().items())},
+                             **{f"gated {n}x{k}": choice for (_, n, k), choice in sorted(kernels.gated_choices().items())}},
     }
     print(json.dumps(line))
     return 0

@@ -304,15 +304,17 @@ MS_EXPORT int ms_qk_norm_rope_append(const void* qkv, int dtype, const int* slot
   return 0;
 }
 
-MS_EXPORT int ms_silu_mul(const void* gate_up, int dtype, void* out, int n_tokens, int inter, cudaStream_t stream) {
+// paired != 0: gate and up columns alternate in blocks of eight (inter must be a multiple of 8 then).
+MS_EXPORT int ms_silu_mul(const void* gate_up, int dtype, void* out, int n_tokens, int inter, int paired, cudaStream_t stream) {
   const size_t total = (size_t)n_tokens * inter;
   if (total == 0) return 0;
+  MS_REQUIRE(!paired || inter % 8 == 0, "silu_mul: paired columns need a multiple of 8 features, not %d", inter);
   if (inter % 8 == 0) {
     const size_t total8 = total / 8;
     const size_t blocks8 = (total8 + 255) / 256;
     MS_REQUIRE(blocks8 < 2147483647ULL, "silu_mul: %zu elements in one launch is too many", total);
     MS_DISPATCH(dtype, (ms::launch(silu_mul_vec_kernel<T>, (unsigned)blocks8, 256, 0, stream, (const T*)gate_up, (T*)out, inter,
-                                                                                    total8)));
+                                                                                    total8, paired)));
     MS_CHECK_LAUNCH("silu_mul");
     return 0;
   }

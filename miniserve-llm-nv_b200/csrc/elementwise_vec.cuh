@@ -287,7 +287,9 @@ __global__ void qk_norm_rope_append_vec_kernel(const T* __restrict__ qkv, const 
 }
 
 // ---------------------------------------------------------------- gated activation
-// Eight outputs per thread; requires inter % 8 == 0.
+// Eight outputs per thread; requires inter % 8 == 0.  `paired`: the columns of gate_up come in blocks of
+// sixteen, eight gate columns followed by the up columns of the same eight features (the layout that the
+// fused product of few rows wants of the weight's rows); else all gate columns precede all up columns.
 // silu(g) * u.  With bfloat16 data the exponential and the division are the fast ones (relative error about
 // 2^-21, far below the rounding of the result to 8 bits of mantissa); float32 data keeps the accurate ones.
 template <typename T>
@@ -301,7 +303,7 @@ __device__ __forceinline__ float silu_times(float g, float u) {
 }
 
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total8) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total8, int paired) {
   grid_dependency_wait();
   grid_dependency_launch();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -316,8 +318,9 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
     n = i / per_row;
     c = (int)(i % per_row) * 8;
   }
-  const Vec8 g = load8(gate_up + n * 2 * inter + c);
-  const Vec8 u = load8(gate_up + n * 2 * inter + inter + c);
+  const T* row = gate_up + n * 2 * inter;
+  const Vec8 g = load8(row + (paired ? 2 * c : c));
+  const Vec8 u = load8(row + (paired ? 2 * c + 8 : inter + c));
   Vec8 y;
 #pragma unroll
   for (int e = 0; e < 8; ++e) y.v[e] = silu_times<T>(g.v[e], u.v[e]);

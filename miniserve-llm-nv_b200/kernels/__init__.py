@@ -15,7 +15,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 _library: Optional[ctypes.CDLL] = None
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -178,12 +178,18 @@ def qk_norm_rope_append(qkv: torch.Tensor, slots: torch.Tensor, q_weight: Option
         _i(n_q), _i(n_kv), _i(head_dim), _ptr(q_out), _i(n), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[n, c] = silu(gate_up[n, c]) * gate_up[n, I + c]`` for gate_up ``[N, 2 I]``."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> None:
+    """``out[n, c] = silu(gate_up[n, c]) * gate_up[n, I + c]`` for gate_up ``[N, 2 I]``.
+
+    ``paired``: the columns come as :func:`interleave_gate_up` orders a weight's rows (eight gate columns, then
+    the up columns of the same features, and so on): ``out[n, 8 j + r] = silu(gate_up[n, 16 j + r]) *
+    gate_up[n, 16 j + 8 + r]``.
+    """
     n, inter = out.shape
     _want(gate_up, "gate_up", None, (n, 2 * inter))
     _want(out, "out", gate_up.dtype)
-    _check(library().ms_silu_mul(_ptr(gate_up), _i(_code(gate_up.dtype)), _ptr(out), _i(n), _i(inter), _stream()))
+    _check(library().ms_silu_mul(_ptr(gate_up), _i(_code(gate_up.dtype)), _ptr(out), _i(n), _i(inter),
+                                 _i(1 if paired else 0), _stream()))
 
 
 # --------------------------------------------------------------------------- attention
@@ -361,15 +367,20 @@ _stream_buffers: dict = {}
 # depends on its shape.  For up to SKINNY_MAX_ROWS rows the choice between the mma.sync kernel ("skinny":
 # many small blocks, K split over a cluster for narrow weights), the tcgen05 kernel ("stream": one block
 # per multiprocessor, its start and the sum over blocks sharing a tile cost some microseconds, which only a
-# large weight wins back) and the library is measured once per weight shape, on the weight itself with the
-# L2 cache flushed between runs, at the first eager call that meets the shape; MINISERVE_B200_LINEAR_TUNING=0
-# turns the measurement off, and then (and while a graph is being captured before any eager call) the rule
-# below decides.  From SKINNY_MAX_ROWS + 1 to STREAM_MAX_ROWS rows it is the rule alone.
+# large weight wins back) and the library is measured once per weight shape, on the weight itself, in captured
+# graphs as a decode step runs them (_sample_times), at the first eager call that meets the shape;
+# MINISERVE_B200_LINEAR_TUNING=0 turns the measurement off, and then (and while a graph is being captured
+# before any eager call) the rule below decides.  From SKINNY_MAX_ROWS + 1 to STREAM_MAX_ROWS rows it is the
+# rule alone.  The gated product of a feed-forward (gated_up) chooses the same way between the kernel that
+# applies the activation as it stores ("wide") and a plain product followed by the activation kernel.
 STREAM_MAX_ROWS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MAX_ROWS", "16"))
 STREAM_MIN_UNITS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MIN_UNITS", "32"))
 LINEAR_TUNING = __import__("os").environ.get("MINISERVE_B200_LINEAR_TUNING", "1") == "1"
 _multiprocessors: dict = {}
 _linear_choices: dict = {}           # (device index, N, K) -> "skinny" | "stream" | "library"
+_gated_choices: dict = {}            # (device index, 2 I, K) -> "wide" | "separate"
+FLUSH_BYTES = 256 << 20              # larger than the L2 cache
+LIBRARY_MARGIN = 0.97                # the vendor library replaces an own kernel if it takes less than this share of its time
 
 
 def _stream_units_per_block(device: torch.device, n: int, k: int) -> float:
@@ -403,37 +414,66 @@ def linear_choices() -> dict:
     return dict(_linear_choices)
 
 
+TUNING_REPEATS = 8      # a candidate this many times in one captured graph
+
+
+def _sample_times(candidates: dict, x: torch.Tensor, rounds: int = 7) -> dict:
+    """Device time in milliseconds of each of ``candidates`` (name -> callable reading ``x``), measured the way
+    a decode step runs them: in a captured graph, after a small kernel of this library that writes ``x`` (so
+    that a candidate which can start before its predecessor ends does so), with the L2 cache overwritten
+    before it.  A graph holds that sequence TUNING_REPEATS times; the same graph without the candidate is
+    timed too and subtracted.  The graphs take turns, round after round, so that a clock that is still rising
+    meets all of them alike; the figure is the lower quartile of a graph's samples."""
+    device = x.device
+    flush = torch.empty(FLUSH_BYTES // 4, dtype=torch.float32, device=device)
+    source, weight = torch.zeros_like(x), torch.ones(x.shape[-1], dtype=x.dtype, device=device)
+
+    def capture(run) -> torch.cuda.CUDAGraph:
+        def sequence() -> None:
+            for _ in range(TUNING_REPEATS):
+                flush.zero_()
+                rmsnorm(source, weight, 1e-6, x)
+                if run is not None:
+                    run()
+        sequence()                                          # lazy set-up outside the capture
+        torch.cuda.synchronize(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            sequence()
+        return graph
+
+    graphs = {name: capture(run) for name, run in candidates.items()}
+    graphs[None] = capture(None)
+    samples = {name: [] for name in graphs}
+    for round_index in range(rounds + 2):
+        for name, graph in graphs.items():
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            graph.replay()
+            end.record()
+            end.synchronize()
+            if round_index >= 2:                            # the first rounds bring the clocks up
+                samples[name].append(start.elapsed_time(end))
+    quartile = {name: sorted(times)[len(times) // 4] for name, times in samples.items()}
+    return {name: (quartile[name] - quartile[None]) / TUNING_REPEATS for name in candidates}
+
+
 def _measure_few_rows(weight: torch.Tensor) -> str:
     """Times the candidates for ``[8, K] @ weight[N, K]^T`` on the device: the faster of this library's two
-    kernels, unless the vendor library is clearly (8 %) faster than both.  The margin is what this library's
-    kernels gain inside a step, where they start while the kernel before them ends (programmatic dependent
-    launch) and the vendor's do not: measured alone, 3 % apart, they come out even in the step."""
+    kernels, unless the vendor library is faster than both by more than the measurement can be trusted for."""
     n, k = weight.shape
     device = weight.device
     x = torch.zeros((SKINNY_MAX_ROWS, k), dtype=torch.bfloat16, device=device)
     out = torch.empty((SKINNY_MAX_ROWS, n), dtype=torch.bfloat16, device=device)
-    flush = torch.empty(64 << 20, dtype=torch.float32, device=device)      # 256 MB: larger than the L2 cache
     candidates = {
         "skinny": lambda: _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)),
                                                           _i(SKINNY_MAX_ROWS), _i(n), _i(k), _stream())),
         "stream": lambda: linear_stream(x, weight, out),
         "library": lambda: torch.mm(x, weight.t(), out=out),
     }
-    times = {}
-    for name, run in candidates.items():
-        run()                                                               # lazy set-up outside the timing
-        samples = []
-        for _ in range(9):
-            flush.zero_()
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            run()
-            end.record()
-            end.synchronize()
-            samples.append(start.elapsed_time(end))
-        times[name] = sorted(samples)[len(samples) // 2]
+    times = _sample_times(candidates, x)
     own = "stream" if times["stream"] < times["skinny"] else "skinny"
-    return "library" if times["library"] < 0.92 * times[own] else own
+    return "library" if times["library"] < LIBRARY_MARGIN * times[own] else own
 
 
 def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
@@ -455,6 +495,98 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> N
         _stream_buffers[key] = buffers
     _check(library().ms_gemm_stream(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m), _i(n), _i(k),
                                     _ptr(buffers[0]), _ptr(buffers[1]), _ptr(device_error_flag(x.device)), _stream()))
+
+
+def wide_supports(n: int, k: int) -> int:
+    """0: :func:`linear_wide` does not take a weight of ``n`` rows and inner size ``k``; 1: it does, in several
+    waves of blocks; 2: with at most one block per multiprocessor, which is what it is made for."""
+    return int(library().ms_gemm_wide_supports(_i(n), _i(k)))
+
+
+def linear_wide(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """``out = x @ weight^T`` for up to 8 rows of bfloat16 ``x`` by the library's kernel for weights of many
+    rows (no sum across blocks); ``out`` bfloat16 or float32.
+
+    ``gated``: ``weight [2 I, K]`` holds a gated feed-forward's two projections in blocks of sixteen rows,
+    eight gate rows followed by the up rows of the same features (:func:`interleave_gate_up`), and
+    ``out [M, I]`` bfloat16 receives ``silu(gate) * up``.
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, (n, k))
+    _want(out, "out", torch.bfloat16 if gated else None, (m, n // 2 if gated else n))
+    _check(library().ms_gemm_wide(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(1 if gated else 0), _i(m),
+                                  _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
+
+
+GATE_UP_BLOCK = 8    # rows of the gate projection beside as many of the up projection, for linear_wide(gated=True)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``[2 I, K]``: rows 16 j .. 16 j + 7 are the gate rows 8 j .. 8 j + 7, the next eight the same up rows."""
+    inter, k = gate.shape
+    if inter % GATE_UP_BLOCK != 0 or up.shape != gate.shape:
+        raise KernelError(f"interleave_gate_up: {tuple(gate.shape)} and {tuple(up.shape)}; rows must be a multiple of 8")
+    blocks = inter // GATE_UP_BLOCK
+    return torch.stack((gate.reshape(blocks, GATE_UP_BLOCK, k), up.reshape(blocks, GATE_UP_BLOCK, k)), dim=1).reshape(2 * inter, k)
+
+
+WIDE_GATED_MIN_ROWS = 8192     # of the paired weight: the rule when nothing was measured
+
+
+def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[M, I] = silu(x @ gate^T) * (x @ up^T)`` with ``weight = interleave_gate_up(gate, up)``.
+
+    Few rows of bfloat16 go through :func:`linear_wide`, which applies the activation as it stores, where that
+    is faster than the product (:func:`linear`) followed by :func:`silu_mul`: measured once per weight shape
+    like the choice among the plain products, with the same switch.
+    """
+    m, k = x.shape
+    two_i = weight.shape[0]
+    _want(out, "out", x.dtype, (m, two_i // 2))
+    if x.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and _gated_choice(x, weight) == "wide":
+        linear_wide(x, weight, out, gated=True)
+        return
+    gate_up = torch.empty((m, two_i), dtype=x.dtype, device=x.device)
+    linear(x, weight, gate_up)
+    silu_mul(gate_up, out, paired=True)
+
+
+def _gated_choice(x: torch.Tensor, weight: torch.Tensor) -> str:
+    n, k = weight.shape
+    key = (torch.device(x.device).index or 0, n, k)
+    choice = _gated_choices.get(key)
+    if choice is None:
+        fits = wide_supports(n, k) if k % 8 == 0 and n % (2 * GATE_UP_BLOCK) == 0 else 0
+        if not fits:
+            choice = _gated_choices[key] = "separate"
+        elif not LINEAR_TUNING or torch.cuda.is_current_stream_capturing():
+            return "wide" if fits == 2 and n >= WIDE_GATED_MIN_ROWS else "separate"
+        else:
+            choice = _gated_choices[key] = _measure_gated(weight)
+    return choice
+
+
+def _measure_gated(weight: torch.Tensor) -> str:
+    n, k = weight.shape
+    device = weight.device
+    x = torch.zeros((SKINNY_MAX_ROWS, k), dtype=torch.bfloat16, device=device)
+    gate_up = torch.empty((SKINNY_MAX_ROWS, n), dtype=torch.bfloat16, device=device)
+    out = torch.empty((SKINNY_MAX_ROWS, n // 2), dtype=torch.bfloat16, device=device)
+
+    def separate() -> None:
+        linear(x, weight, gate_up)
+        silu_mul(gate_up, out, paired=True)
+
+    separate()                                              # the plain product's own choice is made outside the timing
+    times = _sample_times({"wide": lambda: linear_wide(x, weight, out, gated=True), "separate": separate}, x)
+    return "wide" if times["wide"] <= times["separate"] else "separate"
+
+
+def gated_choices() -> dict:
+    """What was measured so far: (device index, 2 I, K) -> how the gated product of few rows runs."""
+    return dict(_gated_choices)
 
 
 SKINNY_MAX_ROWS = 8    # above this the weight-streaming kernel re-reads the activations too often

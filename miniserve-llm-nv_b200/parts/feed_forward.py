@@ -1,6 +1,8 @@
 """Feed-forward parts.  ``gated_mlp``: ``down(act(gate(x)) * up(x))`` without biases
 (miniserve/model/layers.py:71-87) with ``silu`` as the activation; gate and up run as one
-matrix product over a row-concatenated weight."""
+matrix product over one weight that holds both.  Where the intermediate size is a multiple of eight
+the rows of the two alternate in blocks of eight (``kernels.interleave_gate_up``), which lets the
+product of a decode step apply the activation as it stores; else the up rows follow the gate rows."""
 
 from __future__ import annotations
 
@@ -24,6 +26,7 @@ class GatedMLP(Part):
         self.names = dict(gate=prefix + gate_name, up=prefix + up_name, down=prefix + down_name)
         self.gate_up_weight: Optional[torch.Tensor] = None
         self.down_weight: Optional[torch.Tensor] = None
+        self.paired = False
 
     def param_specs(self) -> list[ParamSpec]:
         h, i = self.hidden_size, self.intermediate_size
@@ -31,13 +34,23 @@ class GatedMLP(Part):
                 ParamSpec(self.names["down"], (h, i))]
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.gate_up_weight = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]], dim=0).contiguous()
+        gate, up = tensors[self.names["gate"]], tensors[self.names["up"]]
+        self.paired = self.intermediate_size % kernels.GATE_UP_BLOCK == 0
+        if self.paired:
+            self.gate_up_weight = kernels.interleave_gate_up(gate, up).contiguous()
+        else:
+            self.gate_up_weight = torch.cat([gate, up], dim=0).contiguous()
         self.down_weight = tensors[self.names["down"]]
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         n = x.shape[0]
-        gate_up = torch.empty((n, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.linear(x, self.gate_up_weight, gate_up)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
-        kernels.gated_linear(gate_up, self.down_weight, out)
+        if self.paired:
+            hidden = torch.empty((n, self.intermediate_size), dtype=x.dtype, device=x.device)
+            kernels.gated_up(x, self.gate_up_weight, hidden)
+            kernels.linear(hidden, self.down_weight, out)
+        else:
+            gate_up = torch.empty((n, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+            kernels.linear(x, self.gate_up_weight, gate_up)
+            kernels.gated_linear(gate_up, self.down_weight, out)
         return out

@@ -88,10 +88,19 @@ def qk_norm_rope_append(qkv, slots, q_weight, k_weight, eps, cos_sin, rotary_dim
         v_pool[page, :, offset, :] = v[token].to(v_pool.dtype)
 
 
-def silu_mul(gate_up, out):
-    inter = out.shape[1]
-    g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
+def silu_mul(gate_up, out, paired=False):
+    n, inter = out.shape
+    if paired:      # blocks of sixteen columns: eight of the gate, then the same eight of the up projection
+        blocks = gate_up.reshape(n, inter // 8, 2, 8)
+        g, u = blocks[:, :, 0].reshape(n, inter).double(), blocks[:, :, 1].reshape(n, inter).double()
+    else:
+        g, u = gate_up[:, :inter].double(), gate_up[:, inter:].double()
     out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
+
+
+def gated_up(x, weight, out):
+    gate_up = (x.double() @ weight.double().T).to(x.dtype)
+    silu_mul(gate_up, out, paired=True)
 
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
@@ -144,5 +153,5 @@ def install(monkeypatch) -> None:
     from miniserve_b200 import kernels
 
     for name in ("embedding", "add_rmsnorm", "rmsnorm", "rope_table", "qk_norm_rope_append", "silu_mul",
-                 "paged_attention", "linear", "gated_linear", "sample"):
+                 "paged_attention", "linear", "gated_linear", "gated_up", "sample"):
         monkeypatch.setattr(kernels, name, globals()[name])

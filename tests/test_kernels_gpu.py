@@ -135,14 +135,20 @@ def test_qk_norm_rope_append(kernels, dtype, n_q, n_kv, d, page_size, rotary, in
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("inter", [1, 200, 224, 6144])
-def test_silu_mul(kernels, dtype, inter):
+@pytest.mark.parametrize("inter,paired", [(1, False), (200, False), (224, False), (6144, False), (8, True), (200, True), (6144, True)])
+def test_silu_mul(kernels, dtype, inter, paired):
     gate_up = rand((5, 2 * inter), dtype, 11, 3.0)
     out = torch.empty((5, inter), dtype=dtype).cuda()
-    kernels.silu_mul(gate_up, out)
+    kernels.silu_mul(gate_up, out, paired=paired)
     expected = torch.empty((5, inter), dtype=torch.float64).cuda()
-    plain_ops.silu_mul(gate_up, expected)
+    plain_ops.silu_mul(gate_up, expected, paired=paired)
     assert torch.allclose(out.double(), expected, **tol(dtype))
+
+
+def test_silu_mul_refuses_paired_columns_of_a_ragged_size(kernels):
+    gate_up = rand((2, 2 * 12), torch.float32, 11)
+    with pytest.raises(kernels.KernelError, match="multiple of 8"):
+        kernels.silu_mul(gate_up, torch.empty((2, 12)).cuda(), paired=True)
 
 
 def _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, seed):
@@ -318,6 +324,71 @@ def test_linear_stream(kernels, out_dtype, m, n, k):
     alone = torch.empty((1, n), dtype=out_dtype).cuda()
     kernels.linear_stream(x[m // 2:m // 2 + 1].contiguous(), w, alone)
     assert torch.equal(alone[0], outs[0][m // 2])      # a row does not depend on the rows beside it
+
+
+WIDE_SIZES = [(1, 48, 72), (8, 12288, 2048), (5, 1040, 200), (3, 2064, 4096), (8, 20000, 264), (7, 2048, 6144), (2, 16, 8)]
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", WIDE_SIZES)
+def test_linear_wide(kernels, out_dtype, m, n, k):
+    """The product for weights of many rows: one stage and a ring that wraps many times, one to eight 16-row
+    tiles per block, more blocks than multiprocessors, ragged N and K."""
+    assert kernels.wide_supports(n, k)
+    x, w = rand((m, k), torch.bfloat16, 53, 0.5), rand((n, k), torch.bfloat16, 54, 0.1)
+    expected = x.double() @ w.double().T
+    bound = 1e-3 if out_dtype == torch.float32 else 1.5e-2
+    out = torch.full((m, n), 7.0, dtype=out_dtype).cuda()
+    kernels.linear_wide(x, w, out)
+    kernels.check_device_errors(x.device)
+    assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
+    alone = torch.empty((1, n), dtype=out_dtype).cuda()
+    kernels.linear_wide(x[m // 2:m // 2 + 1].contiguous(), w, alone)
+    assert torch.equal(alone[0], out[m // 2])            # a row does not depend on the rows beside it
+
+
+@pytest.mark.parametrize("m,n,k", WIDE_SIZES)
+def test_linear_wide_gated(kernels, m, n, k):
+    """The same kernel storing silu(gate) * up, against the plain product followed by the plain activation."""
+    inter = n // 2 // 8 * 8
+    x = rand((m, k), torch.bfloat16, 55, 0.5)
+    gate, up = rand((inter, k), torch.bfloat16, 56, 0.1), rand((inter, k), torch.bfloat16, 57, 0.1)
+    w = kernels.interleave_gate_up(gate, up)
+    assert torch.equal(w[16:24], gate[8:16]) and torch.equal(w[24:32], up[8:16]) if inter >= 16 else True
+    out = torch.full((m, inter), 7.0, dtype=torch.bfloat16).cuda()
+    kernels.linear_wide(x, w, out, gated=True)
+    kernels.check_device_errors(x.device)
+    g, u = (x.double() @ gate.double().T).bfloat16().double(), (x.double() @ up.double().T).bfloat16().double()
+    expected = g * torch.sigmoid(g) * u
+    # the factors are rounded to bfloat16 on both sides; one that falls the other way moves the product by 2^-8
+    assert torch.allclose(out.double(), expected, atol=1.5e-2 * max(1.0, float(expected.abs().max())), rtol=1.5e-2)
+
+
+def test_linear_wide_refusals(kernels):
+    x, w = rand((9, 64), torch.bfloat16, 58), rand((32, 64), torch.bfloat16, 59)
+    with pytest.raises(kernels.KernelError, match="at most 8"):
+        kernels.linear_wide(x, w, torch.empty((9, 32), dtype=torch.bfloat16).cuda())
+    with pytest.raises(kernels.KernelError, match="multiple of 8"):
+        kernels.linear_wide(rand((2, 60), torch.bfloat16, 58), rand((32, 60), torch.bfloat16, 59),
+                            torch.empty((2, 32), dtype=torch.bfloat16).cuda())
+    with pytest.raises(kernels.KernelError, match="multiple of 16"):
+        kernels.linear_wide(x[:2].contiguous(), w[:24].contiguous(), torch.empty((2, 12), dtype=torch.bfloat16).cuda(), gated=True)
+    assert not kernels.wide_supports(4096, 1 << 20)         # the activations alone would not fit in shared memory
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,inter,k", [(1, 200, 72), (8, 6144, 2048), (20, 224, 96), (3, 8, 64)])
+def test_gated_up(kernels, dtype, m, inter, k):
+    """What the feed-forward part calls: whichever way the kernels choose, the plain result."""
+    x = rand((m, k), dtype, 60, 0.5)
+    w = kernels.interleave_gate_up(rand((inter, k), dtype, 61, 0.1), rand((inter, k), dtype, 62, 0.1))
+    out = torch.empty((m, inter), dtype=dtype).cuda()
+    kernels.gated_up(x, w, out)
+    kernels.check_device_errors(x.device)
+    expected = torch.empty((m, inter), dtype=torch.float64).cuda()
+    plain_ops.gated_up(x, w, expected)
+    bound = 1e-4 if dtype == torch.float32 else 2e-2
+    assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

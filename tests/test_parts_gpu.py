@@ -171,7 +171,7 @@ def test_attention_part_in_portions(dtype, hidden, n_q, n_kv, d, window, qk_norm
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hidden,inter,rows", [(72, 200, 5), (96, 40, 70), (136, 264, 1)])
+@pytest.mark.parametrize("hidden,inter,rows", [(72, 200, 5), (96, 40, 70), (136, 264, 1), (88, 100, 4)])
 def test_feed_forward_part(dtype, hidden, inter, rows):
     from miniserve_b200.parts import FEED_FORWARDS, PartSpec
 
