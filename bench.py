@@ -419,7 +419,11 @@ def main() -> int:
         "clocks": clock_summary,
         # which kernel the measurement at start-up chose for the few-row products of each weight shape
         "few_row_products": {**{f"{n}x{k}": choice for (_, n, k), choice in sorted(kernels.linear_choices().items())},
-                             **{f"gated {n}x{k}": choice for (_, n, k), choice in sorted(kernels.gated_choices().items())}},
+                             **{"gated " + "x".join(str(size) for size in key[1:]): choice
+                                for key, choice in sorted(kernels.gated_choices().items())}},
+        # and what it measured, in microseconds per candidate
+        "few_row_us": {("gated " if len(key) > 3 else "") + f"{key[1]}x{key[2]}": times
+                       for key, times in sorted(kernels.choice_times().items(), key=lambda item: item[0][:3])},
     }
     print(json.dumps(line))
     return 0

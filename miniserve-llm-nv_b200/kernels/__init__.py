@@ -306,6 +306,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
             _check(library().ms_gemm_skinny(_ptr(x), _i(0), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(m),
                                             _i(n), _i(k), _stream()))
             return
+        if choice == "wide":
+            linear_wide(x, weight, out)
+            return
     if USE_TCGEN05_GEMM and m >= 128 and k % 8 == 0:
         linear_tcgen05(x, weight, out)
         return
@@ -344,7 +347,8 @@ def check_device_errors(device: torch.device) -> None:
     code = int(flag.item())
     if code:
         flag.zero_()
-        raise KernelError(f"a kernel gave up a bounded wait (code {code}: 1 producer, 2 MMA issue, 3 epilogue)")
+        raise KernelError(f"a kernel gave up a bounded wait (code {code}: 1 producer, 2 MMA issue, 3 epilogue, "
+                          "4 copies in flight at the end)")
 
 
 def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: bool = False) -> None:
@@ -377,8 +381,9 @@ STREAM_MAX_ROWS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MAX_RO
 STREAM_MIN_UNITS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MIN_UNITS", "32"))
 LINEAR_TUNING = __import__("os").environ.get("MINISERVE_B200_LINEAR_TUNING", "1") == "1"
 _multiprocessors: dict = {}
-_linear_choices: dict = {}           # (device index, N, K) -> "skinny" | "stream" | "library"
+_linear_choices: dict = {}           # (device index, N, K) -> "skinny" | "stream" | "wide" | "library"
 _gated_choices: dict = {}            # (device index, 2 I, K) -> "wide" | "separate"
+_choice_times: dict = {}             # the same keys -> {candidate: microseconds} as measured
 FLUSH_BYTES = 256 << 20              # larger than the L2 cache
 LIBRARY_MARGIN = 0.97                # the vendor library replaces an own kernel if it takes less than this share of its time
 
@@ -459,7 +464,7 @@ def _sample_times(candidates: dict, x: torch.Tensor, rounds: int = 7) -> dict:
 
 
 def _measure_few_rows(weight: torch.Tensor) -> str:
-    """Times the candidates for ``[8, K] @ weight[N, K]^T`` on the device: the faster of this library's two
+    """Times the candidates for ``[8, K] @ weight[N, K]^T`` on the device: the fastest of this library's
     kernels, unless the vendor library is faster than both by more than the measurement can be trusted for."""
     n, k = weight.shape
     device = weight.device
@@ -471,8 +476,11 @@ def _measure_few_rows(weight: torch.Tensor) -> str:
         "stream": lambda: linear_stream(x, weight, out),
         "library": lambda: torch.mm(x, weight.t(), out=out),
     }
+    if wide_supports(n, k):
+        candidates["wide"] = lambda: linear_wide(x, weight, out)
     times = _sample_times(candidates, x)
-    own = "stream" if times["stream"] < times["skinny"] else "skinny"
+    _choice_times[(torch.device(device).index or 0, n, k)] = {name: round(1e3 * t, 2) for name, t in times.items()}
+    own = min((name for name in candidates if name != "library"), key=lambda name: times[name])
     return "library" if times["library"] < LIBRARY_MARGIN * times[own] else own
 
 
@@ -581,7 +589,14 @@ def _measure_gated(weight: torch.Tensor) -> str:
 
     separate()                                              # the plain product's own choice is made outside the timing
     times = _sample_times({"wide": lambda: linear_wide(x, weight, out, gated=True), "separate": separate}, x)
+    _choice_times[(torch.device(device).index or 0, n, k, "gated")] = {name: round(1e3 * t, 2) for name, t in times.items()}
     return "wide" if times["wide"] <= times["separate"] else "separate"
+
+
+def choice_times() -> dict:
+    """The measurements behind :func:`linear_choices` and :func:`gated_choices`: key -> {candidate: microseconds}
+    (gated products have a fourth key element)."""
+    return {key: dict(times) for key, times in _choice_times.items()}
 
 
 def gated_choices() -> dict:
