@@ -380,6 +380,9 @@ _stream_buffers: dict = {}
 STREAM_MAX_ROWS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MAX_ROWS", "16"))
 STREAM_MIN_UNITS = int(__import__("os").environ.get("MINISERVE_B200_STREAM_MIN_UNITS", "32"))
 LINEAR_TUNING = __import__("os").environ.get("MINISERVE_B200_LINEAR_TUNING", "1") == "1"
+FEW_ROWS_KERNEL = __import__("os").environ.get("MINISERVE_B200_FEW_ROWS", "")     # "skinny" | "stream" | "wide" | "library"
+if FEW_ROWS_KERNEL not in ("", "skinny", "stream", "wide", "library"):
+    raise ValueError(f"MINISERVE_B200_FEW_ROWS={FEW_ROWS_KERNEL!r}: expected skinny, stream, wide or library")
 _multiprocessors: dict = {}
 _linear_choices: dict = {}           # (device index, N, K) -> "skinny" | "stream" | "wide" | "library"
 _gated_choices: dict = {}            # (device index, 2 I, K) -> "wide" | "separate"
@@ -396,6 +399,8 @@ def _stream_units_per_block(device: torch.device, n: int, k: int) -> float:
 
 
 def _few_rows_rule(device: torch.device, m: int, n: int, k: int) -> str:
+    if m <= SKINNY_MAX_ROWS and wide_supports(n, k) == 2:
+        return "wide"                # one wave of blocks, each with its whole share of the weight on the way early
     if _stream_units_per_block(device, n, k) >= STREAM_MIN_UNITS:
         return "stream"
     return "skinny" if m <= SKINNY_MAX_ROWS else "library"
@@ -403,6 +408,8 @@ def _few_rows_rule(device: torch.device, m: int, n: int, k: int) -> str:
 
 def _few_rows_choice(x: torch.Tensor, weight: torch.Tensor, m: int) -> str:
     n, k = weight.shape
+    if FEW_ROWS_KERNEL and m <= SKINNY_MAX_ROWS and (FEW_ROWS_KERNEL != "wide" or wide_supports(n, k)):
+        return FEW_ROWS_KERNEL      # pinned (to profile one kernel on every product, or to compare)
     if m > SKINNY_MAX_ROWS:
         return _few_rows_rule(x.device, m, n, k)
     key = (torch.device(x.device).index or 0, n, k)
@@ -505,10 +512,16 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> N
                                     _ptr(buffers[0]), _ptr(buffers[1]), _ptr(device_error_flag(x.device)), _stream()))
 
 
+_wide_supports: dict = {}
+
+
 def wide_supports(n: int, k: int) -> int:
     """0: :func:`linear_wide` does not take a weight of ``n`` rows and inner size ``k``; 1: it does, in several
     waves of blocks; 2: with at most one block per multiprocessor, which is what it is made for."""
-    return int(library().ms_gemm_wide_supports(_i(n), _i(k)))
+    answer = _wide_supports.get((n, k))
+    if answer is None:
+        answer = _wide_supports[(n, k)] = int(library().ms_gemm_wide_supports(_i(n), _i(k)))
+    return answer
 
 
 def linear_wide(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
