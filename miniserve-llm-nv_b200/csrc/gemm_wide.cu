@@ -1,5 +1,5 @@
-// out[M, N] = X[M, K] * W[N, K]^T for up to eight rows M (decode steps) and a weight with many rows, without
-// any sum across thread blocks: a block owns up to 128 rows of W for the whole of K.
+// out[M, N] = X[M, K] * W[N, K]^T for up to eight rows M (decode steps), without any sum across thread blocks:
+// a block owns groups of up to 128 rows of W for the whole of K.
 //
 //   - the grid is one block per multiprocessor where the weight allows it (16 to 128 rows a block); a block
 //     has eight computing warps and one that copies: one thread of it issues TMA loads (cp.async.bulk.tensor,
@@ -20,6 +20,12 @@
 //     projection, and stores silu(gate) * up for the eight features: the activation costs no kernel and no
 //     trip through memory.  (Both factors are rounded to bfloat16 first, as they are where the product and
 //     the activation are separate kernels.)
+//   - larger products: a weight with more rows than one wave of such blocks takes runs as several waves of
+//     blocks of eight tiles, or (on request, see persistent_rows) with one block per multiprocessor that walks
+//     group after group of rows through the one ring, its sums meeting in room of their own while the copies
+//     for the next group are on their way; activations of more than 96 KB pass through two buffers in parts
+//     of K, fetched again for every group of rows (from the L2 cache).  The kernel's second form (MANY) has
+//     those loops; the first, for the products of a small model's layers, has them removed at compile time.
 //
 // Every wait on an mbarrier is bounded: a wait that does not finish within the limit sets the error flag
 // that the host checks, and the block drains and returns.
@@ -33,143 +39,244 @@ namespace wide {
 constexpr int MAX_STAGES = 16;
 constexpr int SMEM_LIMIT = 226 * 1024;       // dynamic shared memory a block may ask for
 constexpr int SLOT_TARGET = 16 * 1024;       // a slot is about this large (and two pieces at least)
+constexpr int X_WHOLE_LIMIT = 96 * 1024;     // activations up to this size stay in shared memory whole
+constexpr int X_PART_TARGET = 48 * 1024;     // larger ones pass through two buffers of about this size
 
 enum : int { MODE_PLAIN = 0, MODE_GATED = 1 };
 
 struct Plan {
   int tiles, pieces, slot_bytes, stages, bulk, smem;
+  int groups, grid;                // groups of `tiles` 16-row tiles; blocks (each takes every grid-th group)
+  int x_pieces, x_parts, x_bufs;   // 64-k pieces of X held at once, how many such parts K has, buffers for them
+  int scratch_bytes;               // room of its own for the partial sums (0: they meet in the ring)
+  int slots_per_group, part_slots; // ring slots that a group of rows takes in all, and in one full part of K
 };
 
-struct Phase {
-  int tiles, pieces, slots, kc;    // 16-row tiles per block, 64-k pieces per slot, slots, pieces in all
+// What one block does, the same arithmetic for the copying thread and the computing warps (the divisions are
+// the host's: a kernel of a few microseconds has no time for them).
+struct Walk {
+  int kc, my_groups, slots_per_group;
+  __device__ __forceinline__ Walk(const Plan& plan, int K, bool many) {
+    kc = (K + BK - 1) / BK;
+    my_groups = many ? (plan.groups - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 1;
+    slots_per_group = plan.slots_per_group;
+  }
+  __device__ __forceinline__ int part_pieces(const Plan& plan, int part) const { return min(plan.x_pieces, kc - part * plan.x_pieces); }
+  __device__ __forceinline__ int part_slots(const Plan& plan, int part) const {
+    return part + 1 < plan.x_parts ? plan.part_slots : plan.slots_per_group - (plan.x_parts - 1) * plan.part_slots;
+  }
 };
 
-// What the computing warps carry through both products.
+// What the computing warps carry along.
 struct Consumer {
-  uint64_t *full_bar, *empty_bar;
+  uint64_t *full_bar, *empty_bar, *x_full, *x_empty;
   int stages, slot_bytes;
-  unsigned ring_u32, a_offset, b_offset;
-  int warp, lane, group;
+  unsigned ring_u32, x_u32, a_offset, b_offset;
+  int warp, lane, half;            // half: the even or the odd pieces of a slot
   int* error_flag;
-  int stage;                       // of the ring's next slot, and the parity of its barrier's phase
-  unsigned parity;
-  bool ok;
 };
 
-// One product's share of a block: TILES tiles of 16 rows of W over the whole inner size, read from the ring
-// slot after slot; the warps' partial sums meet in `scratch`, and the warp that owns a tile (warp < TILES)
-// gets its sums back in `sum`.  Every computing warp waits for every slot and frees it, whether it has a
-// piece in it or not, so all of them see every phase of a slot's barriers.  The number of tiles is a
-// template parameter: with it as a variable every tile's loads and products stay in the code as branches,
-// and a product of one tile per block, which has the most pieces to walk, pays for eight.
-template <int TILES>
-__device__ __forceinline__ void product_tiles(Consumer& c, const Phase& phase, int slots, unsigned x_u32,
-                                              unsigned char* scratch, float4& sum) {
-  float acc[TILES][4];
-#pragma unroll
-  for (int t = 0; t < TILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+// The computing warps' side for blocks of TILES tiles of 16 rows.  For each of the block's groups of rows: the
+// parts of K in turn (X for a part waits in its buffer), the part's slots from the ring, then the eight warps'
+// partial sums meet in `scratch` and the warp that owns a tile (warp < TILES) stores it.  Every computing warp
+// waits for every slot and frees it, whether it has a piece in it or not, so all of them see every phase of a
+// slot's barriers.  The number of tiles is a template parameter: with it as a variable every tile's loads and
+// products stay in the code as branches, and a block of one tile, which has the most pieces to walk, pays for
+// eight.
+template <int TILES, int MODE, typename OutT, bool MANY>
+__device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, const Walk& walk, unsigned char* scratch,
+                                        OutT* __restrict__ out, int M, int N) {
   constexpr int piece_bytes = TILES * 16 * 128;
-  for (int slot = 0; slot < slots && c.ok; ++slot) {
-    c.ok = mbar_wait(&c.full_bar[c.stage], c.parity, c.error_flag, 3);
-    c.ok = __all_sync(0xffffffffu, c.ok);
-    if (!c.ok) break;
-    const int piece0 = slot * phase.pieces, pieces = min(phase.pieces, phase.kc - piece0);
-    const unsigned w_slot = c.ring_u32 + (unsigned)(c.stage * c.slot_bytes) + c.a_offset;
-    const unsigned x_slot = x_u32 + (unsigned)(piece0 * (X_ROWS * 128)) + c.b_offset;
-    for (int j = c.group; j < pieces; j += 2) {
-      unsigned a[TILES][4], b[2];
-      ldmatrix_x2(b, x_slot + j * (X_ROWS * 128));
-#pragma unroll
-      for (int t = 0; t < TILES; ++t) ldmatrix_x4(a[t], w_slot + j * piece_bytes + t * 2048);   // sixteen rows further: the swizzle repeats
-#pragma unroll
-      for (int t = 0; t < TILES; ++t) mma_16816(acc[t], a[t], b);
-    }
-    __syncwarp();
-    if (c.lane == 0) mbar_arrive(&c.empty_bar[c.stage]);
-    if (++c.stage == c.stages) {
-      c.stage = 0;
-      c.parity ^= 1u;
-    }
-  }
-  c.ok = all_compute_warps(c.ok);                          // (also: nobody reads the scratch's old contents any more)
+  int stage = 0, x_seen = 0;                               // the ring's next slot; parts of X waited for so far
+  unsigned parity = 0u;                                    // of the phase of that slot's barriers
+  bool ok = true;
   float4* partial = reinterpret_cast<float4*>(scratch);    // [warp][tile][lane]
-  if (c.ok) {
+  const int my_groups = MANY ? walk.my_groups : 1, x_parts = MANY ? plan.x_parts : 1;   // (compile-time ones shorten the code)
+  for (int gi = 0; gi < my_groups; ++gi) {
+    const int group = (int)blockIdx.x + gi * (int)gridDim.x;
+    float acc[TILES][4];
 #pragma unroll
-    for (int t = 0; t < TILES; ++t) partial[(c.warp * TILES + t) * 32 + c.lane] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
-  }
-  sync_compute_warps();
-  sum = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (c.ok && c.warp < TILES) {
+    for (int t = 0; t < TILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+    for (int part = 0; part < x_parts && ok; ++part) {
+      const bool fresh_x = x_parts > 1 || gi == 0;    // X whole in shared memory is fetched once
+      const int buf = x_parts > 1 ? x_seen % plan.x_bufs : 0;
+      if (fresh_x) {
+        ok = mbar_wait(&c.x_full[buf], (unsigned)(x_seen / plan.x_bufs) & 1u, c.error_flag, 2);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
+      const unsigned x_part = c.x_u32 + (unsigned)(buf * plan.x_pieces * (X_ROWS * 128)) + c.b_offset;
+      const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
+      for (int slot = 0; slot < slots; ++slot) {
+        ok = mbar_wait(&c.full_bar[stage], parity, c.error_flag, 3);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
+        const unsigned w_slot = c.ring_u32 + (unsigned)(stage * c.slot_bytes) + c.a_offset;
+        const unsigned x_slot = x_part + (unsigned)(piece0 * (X_ROWS * 128));
+        for (int j = c.half; j < pieces; j += 2) {
+          unsigned a[TILES][4], b[2];
+          ldmatrix_x2(b, x_slot + j * (X_ROWS * 128));
 #pragma unroll
-    for (int w = 0; w < COMPUTE_WARPS; ++w) {
-      const float4 p = partial[(w * TILES + c.warp) * 32 + c.lane];
-      sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+          for (int t = 0; t < TILES; ++t) ldmatrix_x4(a[t], w_slot + j * piece_bytes + t * 2048);   // sixteen rows further: the swizzle repeats
+#pragma unroll
+          for (int t = 0; t < TILES; ++t) mma_16816(acc[t], a[t], b);
+        }
+        __syncwarp();
+        if (c.lane == 0) mbar_arrive(&c.empty_bar[stage]);
+        if (++stage == c.stages) {
+          stage = 0;
+          parity ^= 1u;
+        }
+      }
+      if (fresh_x) {
+        if (x_parts > 1 && ok) {                    // the buffer may take the part after next
+          __syncwarp();
+          if (c.lane == 0) mbar_arrive(&c.x_empty[buf]);
+        }
+        ++x_seen;
+      }
+    }
+    if (MANY && gi == my_groups - 1) grid_dependency_launch();
+    // the partial sums meet (and nobody reads the scratch's last contents any more)
+    ok = all_compute_warps(ok);
+    if (ok) {
+#pragma unroll
+      for (int t = 0; t < TILES; ++t) partial[(c.warp * TILES + t) * 32 + c.lane] = make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    }
+    sync_compute_warps();
+    if (!ok) return;
+    if (c.warp < TILES) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int w = 0; w < COMPUTE_WARPS; ++w) {
+        const float4 p = partial[(w * TILES + c.warp) * 32 + c.lane];
+        sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+      }
+      // sum.x, sum.y: row (lane / 4) of the warp's tile, tokens 2 (lane % 4) and + 1;  sum.z, sum.w: the row eight further
+      const int r = c.lane >> 2, t0 = 2 * (c.lane & 3);
+      if (MODE == MODE_GATED) {
+        const int feature = (group * TILES + c.warp) * 8 + r, features = N / 2;
+        if (feature < features) {
+          if (t0 < M) out[(size_t)t0 * features + feature] = from_float<OutT>(silu_times(round_bf16(sum.x), round_bf16(sum.z)));
+          if (t0 + 1 < M)
+            out[(size_t)(t0 + 1) * features + feature] = from_float<OutT>(silu_times(round_bf16(sum.y), round_bf16(sum.w)));
+        }
+      } else {
+        const int row = (group * TILES + c.warp) * 16 + r;
+        if (row < N) {
+          if (t0 < M) out[(size_t)t0 * N + row] = from_float<OutT>(sum.x);
+          if (t0 + 1 < M) out[(size_t)(t0 + 1) * N + row] = from_float<OutT>(sum.y);
+        }
+        if (row + 8 < N) {
+          if (t0 < M) out[(size_t)t0 * N + row + 8] = from_float<OutT>(sum.z);
+          if (t0 + 1 < M) out[(size_t)(t0 + 1) * N + row + 8] = from_float<OutT>(sum.w);
+        }
+      }
     }
   }
 }
 
-template <int MODE, typename OutT>
+// MANY: a block may walk several groups of rows, and K in parts; without it (one group per block, X whole in
+// shared memory: the products of a small model's layers) those loops are gone at compile time.
+template <int MODE, typename OutT, bool MANY>
 __global__ void __launch_bounds__(THREADS)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 OutT* __restrict__ out, int M, int N, int K, const Plan plan, int* __restrict__ error_flag) {
+                 OutT* __restrict__ out, int M, int N, int K, const __grid_constant__ Plan plan, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], x_full;
+  __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], x_full[2], x_empty[2];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kc = (K + BK - 1) / BK;
   const int stages = plan.stages, slot_bytes = plan.slot_bytes;
-  const Phase phase{plan.tiles, plan.pieces, (kc + plan.pieces - 1) / plan.pieces, kc};
-  unsigned char* x_s = smem;                       // kc pieces of [8 tokens x 64 k]
-  unsigned char* ring = smem + (size_t)kc * (X_ROWS * 128);
-  const int row0 = blockIdx.x * phase.tiles * 16;
+  const Walk walk(plan, K, MANY);
+  const int x_buf_bytes = plan.x_pieces * (X_ROWS * 128);
+  unsigned char* x_s = smem;                       // x_bufs buffers of x_pieces pieces of [8 tokens x 64 k]
+  unsigned char* own_scratch = x_s + (size_t)plan.x_bufs * x_buf_bytes;
+  unsigned char* ring = own_scratch + plan.scratch_bytes;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], COMPUTE_WARPS);
     }
-    mbar_init(&x_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&x_full[i], 1);
+      mbar_init(&x_empty[i], COMPUTE_WARPS);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  grid_dependency_launch();
+  // The kernel behind this one may start now if this one is short.  Behind a block that walks many groups it
+  // would sit on the multiprocessors for tens of microseconds with its first loads long done, and then run in
+  // two waves (measured: a 23 us product took 44 us behind a 40 us one of this kind); such a block lets it
+  // start when its own last group is nearly done.
+  if (!MANY) grid_dependency_launch();
 
   if (warp == COMPUTE_WARPS) {
     if (lane == 0) {
-      // ---------------- copies
-      const int total = phase.slots, ahead = total < stages ? total : stages;
-      const int piece_bytes = phase.tiles * 16 * 128;
-      bool ok = true;
+      // ---------------- copies: the slots of the block's groups, part of K after part, in one ring
+      const int my_groups = MANY ? walk.my_groups : 1, x_parts = MANY ? plan.x_parts : 1;
+      const int total = my_groups * walk.slots_per_group, ahead = total < stages ? total : stages;
+      const int piece_bytes = plan.tiles * 16 * 128;
+      bool ok = true, waited = false;
       int g = 0, stage = 0;                        // the ring's next slot, and the parity of its barriers' phase
       unsigned parity = 0u;
-      for (; g <= total; ++g) {
-        if (g == ahead) {                          // weights first: nothing on the stream writes them
-          grid_dependency_wait();                  // X comes from the kernel before this one
-          mbar_expect_tx(&x_full, kc * (X_ROWS * 128));
-          for (int i = 0; i < kc; ++i) tma_load_2d(x_s + (size_t)i * (X_ROWS * 128), &map_x, &x_full, i * BK, 0);
+      int x_sent = 0;                              // parts of X requested so far
+      // X comes from the kernel before this one: the first request for it is where this thread waits for that
+      // kernel, and it comes after as many slots of weights as the ring holds (nothing on the stream writes weights)
+      auto send_x = [&](int part) {
+        if (!waited) {
+          grid_dependency_wait();
+          waited = true;
         }
-        if (g == total) break;
-        if (g >= stages && !(ok = mbar_wait(&empty_bar[stage], parity ^ 1u, error_flag, 1))) break;
-        const int piece0 = g * phase.pieces, pieces = min(phase.pieces, kc - piece0);
-        if (plan.bulk) {                           // one copy; pieces past the end arrive as zeros and count
-          mbar_expect_tx(&full_bar[stage], phase.pieces * piece_bytes);
-          tma_load_3d(ring + (size_t)stage * slot_bytes, &map_w, &full_bar[stage], 0, row0, piece0);
-        } else {
-          mbar_expect_tx(&full_bar[stage], pieces * piece_bytes);
-          for (int j = 0; j < pieces; ++j)
-            tma_load_2d(ring + (size_t)stage * slot_bytes + (size_t)j * piece_bytes, &map_w, &full_bar[stage],
-                        (piece0 + j) * BK, row0);
+        const int buf = x_sent % plan.x_bufs;
+        if (x_sent >= plan.x_bufs && !mbar_wait(&x_empty[buf], ((unsigned)(x_sent / plan.x_bufs) & 1u) ^ 1u, error_flag, 1)) {
+          ok = false;
+          return;
         }
-        if (++stage == stages) {
-          stage = 0;
-          parity ^= 1u;
+        const int pieces = walk.part_pieces(plan, part);
+        mbar_expect_tx(&x_full[buf], pieces * (X_ROWS * 128));
+        for (int i = 0; i < pieces; ++i)
+          tma_load_2d(x_s + (size_t)buf * x_buf_bytes + (size_t)i * (X_ROWS * 128), &map_x, &x_full[buf],
+                      (part * plan.x_pieces + i) * BK, 0);
+        ++x_sent;
+      };
+      for (int gi = 0; gi < my_groups && ok; ++gi) {
+        const int row0 = ((int)blockIdx.x + gi * (int)gridDim.x) * plan.tiles * 16;
+        for (int part = 0; part < x_parts && ok; ++part) {
+          const bool fresh_x = x_parts > 1 || gi == 0;
+          if (fresh_x && x_sent > 0) send_x(part);       // (the very first waits until the ring is full, below)
+          const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
+          for (int slot = 0; slot < slots && ok; ++slot, ++g) {
+            if (x_sent == 0 && g == ahead) send_x(0);
+            if (!ok) break;
+            if (g >= stages && !(ok = mbar_wait(&empty_bar[stage], parity ^ 1u, error_flag, 1))) break;
+            const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
+            unsigned char* dst = ring + (size_t)stage * slot_bytes;
+            if (plan.bulk) {                       // one copy; pieces past the end arrive as zeros and count
+              mbar_expect_tx(&full_bar[stage], plan.pieces * piece_bytes);
+              tma_load_3d(dst, &map_w, &full_bar[stage], 0, row0, part * plan.x_pieces + piece0);
+            } else {
+              mbar_expect_tx(&full_bar[stage], pieces * piece_bytes);
+              for (int j = 0; j < pieces; ++j)
+                tma_load_2d(dst + (size_t)j * piece_bytes, &map_w, &full_bar[stage], (part * plan.x_pieces + piece0 + j) * BK, row0);
+            }
+            if (++stage == stages) {
+              stage = 0;
+              parity ^= 1u;
+            }
+          }
+          if (ok && x_parts > 1 && x_sent == 0) send_x(0);   // the parts of X keep their order
         }
       }
+      if (ok && x_sent == 0 && my_groups > 0) send_x(0);     // fewer slots in all than the ring holds
+      if (!waited) grid_dependency_wait();
       if (!ok || *reinterpret_cast<volatile int*>(error_flag) != 0) {
         // something gave up: let the copies still in flight land before the block may exit
         for (int j = g - 1; j >= 0 && j >= g - stages; --j) mbar_wait(&full_bar[j % stages], (j / stages) & 1, error_flag, 4);
-        mbar_wait(&x_full, 0, error_flag, 4);
+        for (int j = x_sent - 1; j >= 0 && j >= x_sent - plan.x_bufs; --j)
+          mbar_wait(&x_full[j % plan.x_bufs], (unsigned)(j / plan.x_bufs) & 1u, error_flag, 4);
       }
     }
     // The other lanes of this warp do nothing, and must not wait for the predecessor here: a warp that
@@ -182,84 +289,108 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   Consumer c;
   c.full_bar = full_bar;
   c.empty_bar = empty_bar;
+  c.x_full = x_full;
+  c.x_empty = x_empty;
   c.stages = stages;
   c.slot_bytes = slot_bytes;
   c.ring_u32 = smem_u32(ring);
+  c.x_u32 = smem_u32(x_s);
   c.warp = warp;
   c.lane = lane;
-  c.group = warp >> 2;                             // the even or the odd pieces of a slot
+  c.half = warp >> 2;
   const int kk = warp & 3;                         // which 16 of a piece's 64 k
   c.a_offset = swizzled((lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4));
   c.b_offset = swizzled(lane & 7, 2 * kk + ((lane >> 3) & 1));
   c.error_flag = error_flag;
-  c.stage = 0;
-  c.parity = 0u;
-  c.ok = mbar_wait(&x_full, 0, error_flag, 2);
-  c.ok = __all_sync(0xffffffffu, c.ok);
-
-  float4 sum;                                      // the ring is free when the sums meet: every slot has been read
-  switch (phase.tiles) {
-    case 1: product_tiles<1>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    case 2: product_tiles<2>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    case 3: product_tiles<3>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    case 4: product_tiles<4>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    case 5: product_tiles<5>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    case 6: product_tiles<6>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    case 7: product_tiles<7>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-    default: product_tiles<8>(c, phase, phase.slots, smem_u32(x_s), ring, sum); break;
-  }
-  if (c.ok && warp < phase.tiles) {
-    // sum.x, sum.y: row (lane / 4) of the warp's tile, tokens 2 (lane % 4) and + 1;  sum.z, sum.w: the row eight further
-    const int r = lane >> 2, t0 = 2 * (lane & 3);
-    if (MODE == MODE_GATED) {
-      const int feature = (blockIdx.x * phase.tiles + warp) * 8 + r, features = N / 2;
-      if (feature < features) {
-        if (t0 < M) out[(size_t)t0 * features + feature] = from_float<OutT>(silu_times(round_bf16(sum.x), round_bf16(sum.z)));
-        if (t0 + 1 < M)
-          out[(size_t)(t0 + 1) * features + feature] = from_float<OutT>(silu_times(round_bf16(sum.y), round_bf16(sum.w)));
-      }
-    } else {
-      const int row = row0 + warp * 16 + r;
-      if (row < N) {
-        if (t0 < M) out[(size_t)t0 * N + row] = from_float<OutT>(sum.x);
-        if (t0 + 1 < M) out[(size_t)(t0 + 1) * N + row] = from_float<OutT>(sum.y);
-      }
-      if (row + 8 < N) {
-        if (t0 < M) out[(size_t)t0 * N + row + 8] = from_float<OutT>(sum.z);
-        if (t0 + 1 < M) out[(size_t)(t0 + 1) * N + row + 8] = from_float<OutT>(sum.w);
-      }
-    }
+  // a block with one group has read every slot when its sums meet, and they meet in the ring; one with more
+  // has copies for the next group on their way by then, and room of its own for the sums
+  unsigned char* scratch = plan.scratch_bytes > 0 ? own_scratch : ring;
+  switch (plan.tiles) {
+    case 1: compute<1, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 2: compute<2, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 3: compute<3, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 4: compute<4, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 5: compute<5, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 6: compute<6, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 7: compute<7, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    default: compute<8, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
   }
 }
 
-// How the product is laid out: 16-row tiles per block, pieces per slot, slots in the ring; false if it does
-// not fit.  `budget` bounds the shared memory: what a block leaves free lets the next kernel's blocks start
-// early, what it takes lets more of the weight be on its way before the predecessor has ended.
-static bool plan_for(int N, int K, int budget, Plan* plan) {
+// How the product is laid out; false if it does not fit.  `budget` bounds the shared memory: what a block
+// leaves free lets the next kernel's blocks start early, what it takes lets more of the weight be on its way
+// before the predecessor has ended.
+//   - rows: groups of `tiles` 16-row tiles, dealt to at most one block per multiprocessor; the tile count is the
+//     one with which the busiest block has the fewest tiles to walk (a group more per block counts as a tenth
+//     of a tile: its sums have to meet once more), the larger count on a draw.  Unless `persistent` is set,
+//     a weight with more rows than that gives every block one group runs as several waves of blocks instead;
+//   - K: X stays in shared memory whole up to 96 KB; beyond that K is walked in parts of about 48 KB of X
+//     through two buffers, for every group again (from the L2 cache);
+//   - the ring: slots of about 16 KB (two pieces at least, so that both halves of the warps work), as many as
+//     the budget holds.
+static bool plan_for(int N, int K, int budget, bool persistent, Plan* plan) {
   if (K <= 0 || N <= 0 || K % 8 != 0) return false;
+  const long long sms = multiprocessors();
   const long long kc = (K + BK - 1) / BK;
   const long long row_tiles = ((long long)N + 15) / 16;
-  long long tiles = (row_tiles + multiprocessors() - 1) / multiprocessors();
-  if (tiles > MAX_TILES) tiles = MAX_TILES;              // (more blocks than multiprocessors then)
+  long long tiles = 1;
+  double best = 0.0;
+  for (long long t = 1; t <= MAX_TILES; ++t) {
+    const long long groups = (row_tiles + t - 1) / t, grid = groups < sms ? groups : sms;
+    const long long per_block = (groups + grid - 1) / grid;
+    const double cost = (double)(per_block * t) + 0.1 * (double)per_block;
+    if (t == 1 || cost <= best) {
+      best = cost;
+      tiles = t;
+    }
+  }
+  long long groups = (row_tiles + tiles - 1) / tiles, grid = groups < sms ? groups : sms;
+  if (groups > grid && !persistent && kc * (X_ROWS * 128) <= X_WHOLE_LIMIT) {
+    // more rows than one wave of blocks takes: several waves of blocks of eight tiles, one group each
+    tiles = MAX_TILES;
+    groups = grid = (row_tiles + tiles - 1) / tiles;
+  }
   const long long piece_bytes = tiles * 16 * 128;
   long long pieces = SLOT_TARGET / piece_bytes;
   if (pieces < 2) pieces = 2;
   if (pieces > kc) pieces = kc;
-  const long long slot = pieces * piece_bytes, slots = (kc + pieces - 1) / pieces;
-  const long long x_bytes = kc * (X_ROWS * 128), partial = (long long)COMPUTE_WARPS * tiles * 512;
-  long long stages = (budget - 1024 - x_bytes) / slot;
+  long long x_pieces = kc, x_parts = 1, x_bufs = 1;
+  if (kc * (X_ROWS * 128) > X_WHOLE_LIMIT) {
+    x_pieces = X_PART_TARGET / (X_ROWS * 128) / pieces * pieces;     // whole slots
+    if (x_pieces < pieces) x_pieces = pieces;
+    x_parts = (kc + x_pieces - 1) / x_pieces;
+    x_bufs = 2;
+  }
+  const long long slot = pieces * piece_bytes;
+  long long slots_per_group = 0;
+  for (long long part = 0; part < x_parts; ++part) {
+    const long long part_pieces = kc - part * x_pieces < x_pieces ? kc - part * x_pieces : x_pieces;
+    slots_per_group += (part_pieces + pieces - 1) / pieces;
+  }
+  const long long total_slots = slots_per_group * ((groups + grid - 1) / grid);
+  const long long x_bytes = x_bufs * x_pieces * (X_ROWS * 128), partial = (long long)COMPUTE_WARPS * tiles * 512;
+  const long long scratch = groups > grid ? partial : 0;             // see the kernel: only a block's last sums may meet in the ring
+  long long stages = (budget - 1024 - x_bytes - scratch) / slot;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
-  if (stages > slots) stages = slots;
-  if (stages < 2 && stages < slots) return false;
+  if (stages > total_slots) stages = total_slots;
+  if (stages < 2 && stages < total_slots) return false;
   long long ring = stages * slot;
-  if (ring < partial) ring = partial;                    // the partial sums meet in the ring at the end
-  if (x_bytes + ring + 1024 > SMEM_LIMIT) return false;
+  if (scratch == 0 && ring < partial) ring = partial;
+  if (x_bytes + scratch + ring + 1024 > SMEM_LIMIT) return false;
   plan->tiles = (int)tiles;
   plan->pieces = (int)pieces;
   plan->slot_bytes = (int)slot;
   plan->stages = (int)stages;
   plan->bulk = K % BK == 0;
-  plan->smem = (int)(x_bytes + ring + 1024);
+  plan->smem = (int)(x_bytes + scratch + ring + 1024);
+  plan->groups = (int)groups;
+  plan->grid = (int)grid;
+  plan->x_pieces = (int)x_pieces;
+  plan->x_parts = (int)x_parts;
+  plan->x_bufs = (int)x_bufs;
+  plan->scratch_bytes = (int)scratch;
+  plan->slots_per_group = (int)slots_per_group;
+  plan->part_slots = (int)((x_pieces + pieces - 1) / pieces);
   return true;
 }
 
@@ -273,22 +404,31 @@ static int smem_budget() {
   return budget;
 }
 
+// Whether blocks walk several groups of rows where the weight has more rows than one wave of blocks takes
+// (MINISERVE_B200_WIDE_MANY=1).  Alone that is the fastest of this library's kernels on several large weights, but
+// the product that followed it in a decode step of the 8B and 32B sizes took up to twice its usual time, for a
+// reason not yet found; several waves of blocks do not have that effect.
+static bool persistent_rows() {
+  const char* text = std::getenv("MINISERVE_B200_WIDE_MANY");     // read at every call: a test turns it on and off
+  return text != nullptr && std::atoi(text) != 0;
+}
+
 template <int MODE, typename OutT>
 int launch(const void* X, const void* W, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
   Plan plan;
-  MS_REQUIRE(plan_for(N, K, smem_budget(), &plan), "gemm_wide: an inner size of %d leaves no room for the weight ring", K);
+  MS_REQUIRE(plan_for(N, K, smem_budget(), persistent_rows(), &plan), "gemm_wide: an inner size of %d leaves no room for the weight ring", K);
   CUtensorMap map_w, map_x;
   const bool maps_ok = cached_map(&map_w, W, N, K, plan.tiles * 16, plan.bulk ? plan.pieces : 0) && cached_map(&map_x, X, M, K, X_ROWS);
   MS_REQUIRE(maps_ok, "gemm_wide: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
-  auto kernel = gemm_wide_kernel<MODE, OutT>;
-  static bool configured = false;
-  if (!configured) {
+  const bool many = plan.groups > plan.grid || plan.x_parts > 1;
+  auto kernel = many ? gemm_wide_kernel<MODE, OutT, true> : gemm_wide_kernel<MODE, OutT, false>;
+  static bool configured[2] = {false, false};
+  if (!configured[many]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
     if (e != cudaSuccess) MS_FAIL("gemm_wide: cannot reserve shared memory: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[many] = true;
   }
-  const int blocks = (int)(((long long)N + plan.tiles * 16 - 1) / (plan.tiles * 16));
-  cudaError_t e = ms::launch(kernel, dim3(blocks), dim3(THREADS), (size_t)plan.smem, stream, map_w, map_x, (OutT*)out, M, N, K,
+  cudaError_t e = ms::launch(kernel, dim3(plan.grid), dim3(THREADS), (size_t)plan.smem, stream, map_w, map_x, (OutT*)out, M, N, K,
                              plan, error_flag);
   if (e != cudaSuccess) MS_FAIL("gemm_wide: launch failed: %s", cudaGetErrorString(e));
   return 0;
@@ -299,13 +439,15 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int* er
 
 using namespace ms;
 
-// Whether ms_gemm_wide takes a product with this inner size (the activations and a ring of weight stages
-// have to fit in shared memory): 0 no; 1 yes, with more blocks than multiprocessors; 2 yes, with at most one
-// block per multiprocessor.
+// Whether ms_gemm_wide is a candidate for a product of these sizes: 2 with at most one block per multiprocessor
+// and the activations whole in shared memory, which is what it was made for first; 1 with more blocks than
+// that, or blocks that walk several groups of rows, or K in parts; 0 not offered (ms_gemm_wide itself takes
+// every inner size that is a multiple of 8).
 MS_EXPORT int ms_gemm_wide_supports(int N, int K) {
   wide::Plan plan;
-  if (!wide::plan_for(N, K, wide::smem_budget(), &plan)) return 0;
-  return ((long long)N + plan.tiles * 16 - 1) / (plan.tiles * 16) <= wide::multiprocessors() ? 2 : 1;
+  if (!wide::plan_for(N, K, wide::smem_budget(), wide::persistent_rows(), &plan)) return 0;
+  if (plan.x_parts > 1) return wide::persistent_rows() ? 1 : 0;      // K in parts is offered with the same switch
+  return plan.groups <= wide::multiprocessors() ? 2 : 1;
 }
 
 // X [M, K], W [N, K] bfloat16 (K a multiple of 8, both 16-byte aligned), M <= 8.

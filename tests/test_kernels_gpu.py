@@ -326,15 +326,16 @@ def test_linear_stream(kernels, out_dtype, m, n, k):
     assert torch.equal(alone[0], outs[0][m // 2])      # a row does not depend on the rows beside it
 
 
-WIDE_SIZES = [(1, 48, 72), (8, 12288, 2048), (5, 1040, 200), (3, 2064, 4096), (8, 20000, 264), (7, 2048, 6144), (2, 16, 8)]
+WIDE_SIZES = [(1, 48, 72), (8, 12288, 2048), (5, 1040, 200), (3, 2064, 4096), (8, 20000, 264), (7, 2048, 6144), (2, 16, 8),
+              (8, 24576, 4096), (4, 2064, 12288), (3, 40000, 6408)]
 
 
 @pytest.mark.parametrize("out_dtype", DTYPES)
 @pytest.mark.parametrize("m,n,k", WIDE_SIZES)
 def test_linear_wide(kernels, out_dtype, m, n, k):
-    """The product for weights of many rows: one stage and a ring that wraps many times, one to eight 16-row
-    tiles per block, more blocks than multiprocessors, ragged N and K."""
-    assert kernels.wide_supports(n, k)
+    """The product for weights of many rows: one slot and a ring that wraps many times, one to eight 16-row
+    tiles per block, blocks that walk several groups of rows, K walked in parts (activations too large for
+    shared memory), ragged N and K."""
     x, w = rand((m, k), torch.bfloat16, 53, 0.5), rand((n, k), torch.bfloat16, 54, 0.1)
     expected = x.double() @ w.double().T
     bound = 1e-3 if out_dtype == torch.float32 else 1.5e-2
@@ -364,6 +365,23 @@ def test_linear_wide_gated(kernels, m, n, k):
     assert torch.allclose(out.double(), expected, atol=1.5e-2 * max(1.0, float(expected.abs().max())), rtol=1.5e-2)
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 24576, 4096), (5, 40000, 264)])
+def test_linear_wide_blocks_that_walk_many_groups(kernels, monkeypatch, m, n, k):
+    """With the switch on, a weight of more rows than one wave of blocks takes is walked by one block per
+    multiprocessor, group after group, through one ring (off, it runs as several waves of blocks)."""
+    x, w = rand((m, k), torch.bfloat16, 74, 0.5), rand((n, k), torch.bfloat16, 75, 0.1)
+    expected = x.double() @ w.double().T
+    outs = {}
+    for switch in ("0", "1"):
+        monkeypatch.setenv("MINISERVE_B200_WIDE_MANY", switch)
+        out = torch.full((m, n), 7.0, dtype=torch.bfloat16).cuda()
+        kernels.linear_wide(x, w, out)
+        kernels.check_device_errors(x.device)
+        assert torch.allclose(out.double(), expected, atol=1.5e-2 * max(1.0, float(expected.abs().max())), rtol=1.5e-2)
+        outs[switch] = out
+    assert torch.equal(outs["0"], outs["1"])        # the same sums in the same order either way
+
+
 def test_linear_wide_refusals(kernels):
     x, w = rand((9, 64), torch.bfloat16, 58), rand((32, 64), torch.bfloat16, 59)
     with pytest.raises(kernels.KernelError, match="at most 8"):
@@ -373,7 +391,10 @@ def test_linear_wide_refusals(kernels):
                             torch.empty((2, 32), dtype=torch.bfloat16).cuda())
     with pytest.raises(kernels.KernelError, match="multiple of 16"):
         kernels.linear_wide(x[:2].contiguous(), w[:24].contiguous(), torch.empty((2, 12), dtype=torch.bfloat16).cuda(), gated=True)
-    assert not kernels.wide_supports(4096, 1 << 20)         # the activations alone would not fit in shared memory
+    assert kernels.wide_supports(64, 12) == 0               # an inner size that is no multiple of 8
+    assert kernels.wide_supports(4096, 2048) == 2           # one group of rows per block, the activations whole in shared memory
+    assert kernels.wide_supports(4096, 12288) in (0, 1)     # K in parts: taken, but offered to the choice only on request
+    assert kernels.wide_supports(151936, 2048) in (0, 1)    # several groups of rows per block: the same
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
