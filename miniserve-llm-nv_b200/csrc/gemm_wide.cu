@@ -195,6 +195,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned char* own_scratch = x_s + (size_t)plan.x_bufs * x_buf_bytes;
   unsigned char* ring = own_scratch + plan.scratch_bytes;
 
+  if (threadIdx.x == 32 * COMPUTE_WARPS) {           // the copying thread's first copies find the maps fetched
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_x)) : "memory");
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -217,14 +221,15 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (lane == 0) {
       // ---------------- copies: the slots of the block's groups, part of K after part, in one ring
       const int my_groups = MANY ? walk.my_groups : 1, x_parts = MANY ? plan.x_parts : 1;
-      const int total = my_groups * walk.slots_per_group, ahead = total < stages ? total : stages;
       const int piece_bytes = plan.tiles * 16 * 128;
       bool ok = true, waited = false;
       int g = 0, stage = 0;                        // the ring's next slot, and the parity of its barriers' phase
       unsigned parity = 0u;
-      int x_sent = 0;                              // parts of X requested so far
-      // X comes from the kernel before this one: the first request for it is where this thread waits for that
-      // kernel, and it comes after as many slots of weights as the ring holds (nothing on the stream writes weights)
+      int x_sent = 1;                              // parts of X requested so far (the first: by the computing side)
+      // X comes from the kernel before this one.  Its first part is requested by the computing side the moment
+      // that kernel has ended (copies are served in the order of their requests, and behind a ring-full of
+      // weights X would arrive last, though it is needed first); later parts are this thread's, which waits
+      // for that kernel before the first of them
       auto send_x = [&](int part) {
         if (!waited) {
           grid_dependency_wait();
@@ -235,22 +240,25 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           ok = false;
           return;
         }
-        const int pieces = walk.part_pieces(plan, part);
-        mbar_expect_tx(&x_full[buf], pieces * (X_ROWS * 128));
-        for (int i = 0; i < pieces; ++i)
-          tma_load_2d(x_s + (size_t)buf * x_buf_bytes + (size_t)i * (X_ROWS * 128), &map_x, &x_full[buf],
-                      (part * plan.x_pieces + i) * BK, 0);
+        if (plan.bulk) {                             // one copy; pieces past the end arrive as zeros and count
+          mbar_expect_tx(&x_full[buf], x_buf_bytes);
+          tma_load_3d(x_s + (size_t)buf * x_buf_bytes, &map_x, &x_full[buf], 0, 0, part * plan.x_pieces);
+        } else {
+          const int pieces = walk.part_pieces(plan, part);
+          mbar_expect_tx(&x_full[buf], pieces * (X_ROWS * 128));
+          for (int i = 0; i < pieces; ++i)
+            tma_load_2d(x_s + (size_t)buf * x_buf_bytes + (size_t)i * (X_ROWS * 128), &map_x, &x_full[buf],
+                        (part * plan.x_pieces + i) * BK, 0);
+        }
         ++x_sent;
       };
       for (int gi = 0; gi < my_groups && ok; ++gi) {
         const int row0 = ((int)blockIdx.x + gi * (int)gridDim.x) * plan.tiles * 16;
         for (int part = 0; part < x_parts && ok; ++part) {
           const bool fresh_x = x_parts > 1 || gi == 0;
-          if (fresh_x && x_sent > 0) send_x(part);       // (the very first waits until the ring is full, below)
+          if (fresh_x && (gi > 0 || part > 0)) send_x(part);
           const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
           for (int slot = 0; slot < slots && ok; ++slot, ++g) {
-            if (x_sent == 0 && g == ahead) send_x(0);
-            if (!ok) break;
             if (g >= stages && !(ok = mbar_wait(&empty_bar[stage], parity ^ 1u, error_flag, 1))) break;
             const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
             unsigned char* dst = ring + (size_t)stage * slot_bytes;
@@ -267,10 +275,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
               parity ^= 1u;
             }
           }
-          if (ok && x_parts > 1 && x_sent == 0) send_x(0);   // the parts of X keep their order
         }
       }
-      if (ok && x_sent == 0 && my_groups > 0) send_x(0);     // fewer slots in all than the ring holds
       if (!waited) grid_dependency_wait();
       if (!ok || *reinterpret_cast<volatile int*>(error_flag) != 0) {
         // something gave up: let the copies still in flight land before the block may exit
@@ -286,6 +292,16 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
   // ---------------- products
   grid_dependency_wait();
+  if (threadIdx.x == 0) {                          // the first part of X (all of it, if it fits): see the copying thread
+    if (plan.bulk) {
+      mbar_expect_tx(&x_full[0], x_buf_bytes);
+      tma_load_3d(x_s, &map_x, &x_full[0], 0, 0, 0);
+    } else {
+      const int pieces = walk.part_pieces(plan, 0);
+      mbar_expect_tx(&x_full[0], pieces * (X_ROWS * 128));
+      for (int i = 0; i < pieces; ++i) tma_load_2d(x_s + (size_t)i * (X_ROWS * 128), &map_x, &x_full[0], i * BK, 0);
+    }
+  }
   Consumer c;
   c.full_bar = full_bar;
   c.empty_bar = empty_bar;
@@ -418,7 +434,7 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int* er
   Plan plan;
   MS_REQUIRE(plan_for(N, K, smem_budget(), persistent_rows(), &plan), "gemm_wide: an inner size of %d leaves no room for the weight ring", K);
   CUtensorMap map_w, map_x;
-  const bool maps_ok = cached_map(&map_w, W, N, K, plan.tiles * 16, plan.bulk ? plan.pieces : 0) && cached_map(&map_x, X, M, K, X_ROWS);
+  const bool maps_ok = cached_map(&map_w, W, N, K, plan.tiles * 16, plan.bulk ? plan.pieces : 0) && cached_map(&map_x, X, M, K, X_ROWS, plan.bulk ? plan.x_pieces : 0);
   MS_REQUIRE(maps_ok, "gemm_wide: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
   const bool many = plan.groups > plan.grid || plan.x_parts > 1;
   auto kernel = many ? gemm_wide_kernel<MODE, OutT, true> : gemm_wide_kernel<MODE, OutT, false>;
