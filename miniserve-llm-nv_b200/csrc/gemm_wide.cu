@@ -7,7 +7,10 @@
 //     64 k (one copy per slot through a three-dimensional map where K is a multiple of 64, else one per
 //     piece).  As many slots as the ring holds are requested BEFORE the kernel waits for its predecessor on
 //     the stream (no kernel writes weights): for a weight of a few MB that is the block's whole share, which
-//     then arrives while the predecessor ends.  The activations (all of X, a few KB) follow after the wait;
+//     then arrives while the predecessor ends.  The activations (all of X, a few KB, one copy) are requested
+//     by the computing side the moment its own wait for the predecessor returns: copies are served in the
+//     order of their requests, and asked for by the copying thread after its ring-full of weights they
+//     arrived last, 2 us late, though nothing can be multiplied without them;
 //   - the computing warps split a piece by k: each reads 16 x 16 parts of W for all of the block's rows and
 //     one 16 x 8 part of X with ldmatrix and multiplies them with mma.sync.m16n8k16 (rows of W on the M
 //     side, tokens on the N side), float32 accumulation, one independent chain per 16 rows; four warps take
