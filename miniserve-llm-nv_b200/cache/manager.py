@@ -128,10 +128,13 @@ class CacheManager:
             return 0
         full = len(prompt) // self.page_size
         pages = [[entry.tables[g][index] for g in range(len(self.paged_needs))] for index in range(full)]
-        added = self.prefix.insert(prompt, pages)
+        added, replaced = self.prefix.insert(prompt, pages, self._held_by_cache_only)
         for new in added:
             for group, page in enumerate(new.pages):
                 self.allocators[group].retain(page)
+        for old in replaced:
+            for group, page in enumerate(old.pages):
+                self.allocators[group].release(page)
         return len(added)
 
     def release(self, request_id: str) -> None:
@@ -154,11 +157,43 @@ class CacheManager:
         ps = self.page_size
         return (end + ps - 1) // ps - (start + ps - 1) // ps
 
+    def _held_by_cache_only(self, entry: PrefixEntry) -> bool:
+        return all(self.allocators[g].refcount(p) == 1 for g, p in enumerate(entry.pages))
+
     def _reclaimable_entries(self) -> list[PrefixEntry]:
+        """Cached pages that evicting leaves first can free: held by the cache only, and so is every entry
+        behind them in their chains.  (An entry that only the cache holds can stand before one that a request
+        holds: the request computed a copy of the earlier pages itself, then cached its later ones behind
+        entries that were there already.)"""
         if self.prefix is None:
             return []
-        return [e for e in self.prefix.entries.values()
-                if all(self.allocators[g].refcount(p) == 1 for g, p in enumerate(e.pages))]
+        entries = self.prefix.entries
+        blocked: set[bytes] = set()
+        for entry in entries.values():
+            if self._held_by_cache_only(entry):
+                continue
+            digest: Optional[bytes] = entry.digest
+            while digest is not None and digest in entries and digest not in blocked:
+                blocked.add(digest)
+                digest = entries[digest].parent
+        return [e for e in entries.values() if e.digest not in blocked]
+
+    def evictable_now(self) -> int:
+        """How many cached pages :meth:`prepare` could free by evicting leaves first (what ``capacity`` reports
+        as reclaimable, counted the slow way: by doing it on a copy)."""
+        if self.prefix is None:
+            return 0
+        children = {digest: entry.children for digest, entry in self.prefix.entries.items()}
+        alive = dict(self.prefix.entries)
+        count = 0
+        while True:
+            leaf = next((e for d, e in alive.items() if children[d] == 0 and self._held_by_cache_only(e)), None)
+            if leaf is None:
+                return count
+            del alive[leaf.digest]
+            if leaf.parent in children:
+                children[leaf.parent] -= 1
+            count += 1
 
     def capacity(self) -> CapacitySnapshot:
         reclaimable = len(self._reclaimable_entries())
@@ -175,8 +210,7 @@ class CacheManager:
             return any(a.free_count < w for a, w in zip(self.allocators, wanted))
 
         while short() and self.prefix is not None:
-            victim = next((e for e in self.prefix.eviction_order()
-                           if all(self.allocators[g].refcount(p) == 1 for g, p in enumerate(e.pages))), None)
+            victim = next((e for e in self.prefix.eviction_order() if self._held_by_cache_only(e)), None)
             if victim is None:
                 break
             for group, page in enumerate(victim.pages):
@@ -280,6 +314,10 @@ class CacheManager:
                 if holders[page] != allocator.refcount(page):
                     raise AssertionError(
                         f"group {group} page {page}: {holders[page]} holders but refcount {allocator.refcount(page)}")
+        if self.evictable_now() != len(self._reclaimable_entries()):
+            raise AssertionError("the reclaimable pages reported are not the pages that evicting leaves first frees")
+        if self.prefix is not None and len(self.prefix.entries) > self.prefix.max_entries:
+            raise AssertionError("the prefix cache holds more entries than its limit")
         self.slots.check_invariants()
         if sorted(e.slot for e in self.requests.values()) != sorted(
                 s for s in range(self.slots.num_slots) if self.slots.owner(s) is not None):

@@ -5,7 +5,10 @@ SHA-256 over (namespace, digest of the page before it, the page's tokens); an en
 page numbers (one per layer group) and the tokens themselves, which are compared again on a
 hit.  The cache holds one reference on every page it names.  Entries whose pages nobody else
 holds are *reclaimable*: when a step needs pages they are evicted, least recently used first,
-leaves of the chain before their parents.
+leaves of the chain before their parents.  The cache holds at most ``max_entries`` entries: an
+insert beyond that replaces reclaimable leaves, least recently used first
+(prefix_cache.py:122-125 drops the oldest entries there), and caches no further page of the
+prompt once nothing can be replaced.
 """
 
 from __future__ import annotations
@@ -13,7 +16,7 @@ from __future__ import annotations
 import hashlib
 import struct
 from dataclasses import dataclass, field
-from typing import Optional, Sequence
+from typing import Callable, Optional, Sequence
 
 
 def page_digest(namespace: bytes, previous: bytes, tokens: Sequence[int]) -> bytes:
@@ -64,16 +67,22 @@ class PrefixCache:
             entry.last_used = now
         return found
 
-    def insert(self, tokens: Sequence[int], pages_per_page_index: Sequence[Sequence[int]]) -> list[PrefixEntry]:
-        """Adds entries for the full pages of ``tokens`` not cached yet; returns the new ones.
+    def insert(self, tokens: Sequence[int], pages_per_page_index: Sequence[Sequence[int]],
+               replaceable: Optional[Callable[[PrefixEntry], bool]] = None) -> tuple[list[PrefixEntry], list[PrefixEntry]]:
+        """Adds entries for the full pages of ``tokens`` not cached yet; returns (new entries, replaced entries).
 
         ``pages_per_page_index[i]`` are the page numbers (one per group) that hold page ``i``.
-        The caller retains the pages of every returned entry.
+        The caller retains the pages of every new entry and releases those of every replaced one.
+        At ``max_entries`` a new entry takes the place of the least recently used leaf for which
+        ``replaceable(entry)`` holds (no ``replaceable``: none is) and which is not part of the
+        chain being inserted; if there is none, the rest of the prompt stays uncached.
         """
         added: list[PrefixEntry] = []
+        replaced: list[PrefixEntry] = []
         previous: bytes = b""
         parent: Optional[PrefixEntry] = None
         now = self._tick()
+        chain: set[bytes] = set()
         full_pages = len(tokens) // self.page_size
         for index in range(full_pages):
             chunk = tuple(tokens[index * self.page_size:(index + 1) * self.page_size])
@@ -81,7 +90,14 @@ class PrefixCache:
             entry = self.entries.get(digest)
             if entry is None:
                 if len(self.entries) >= self.max_entries:
-                    break
+                    victim = None
+                    if replaceable is not None:
+                        victim = next((e for e in self.eviction_order()
+                                       if e.digest not in chain and replaceable(e)), None)
+                    if victim is None:
+                        break
+                    self.remove(victim)
+                    replaced.append(victim)
                 entry = PrefixEntry(digest, parent.digest if parent else None, chunk,
                                     tuple(pages_per_page_index[index]), now)
                 self.entries[digest] = entry
@@ -92,8 +108,9 @@ class PrefixCache:
                 break
             else:
                 entry.last_used = now
+            chain.add(digest)
             parent, previous = entry, digest
-        return added
+        return added, replaced
 
     def eviction_order(self) -> list[PrefixEntry]:
         """Leaves of the chains, least recently used first."""

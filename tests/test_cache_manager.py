@@ -157,12 +157,12 @@ def test_prefix_in_use_is_not_evicted():
     manager.check_invariants()
 
 
-@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("seed", range(10))
 def test_random_orders_lose_no_page(seed):
     rng = random.Random(seed)
     groups = [FULL, window_group(rng.choice((5, 9, 16)))] if seed % 2 else [FULL]
     manager = CacheManager(groups, page_size=rng.choice((1, 4, 16)), num_pages=24, max_seqs=5,
-                           enable_prefix_cache=True)
+                           enable_prefix_cache=True, prefix_cache_max_entries=rng.choice((3, 8, 64)))
     live: dict[str, list[int]] = {}
     shared = [rng.randrange(50) for _ in range(40)]
     counter = 0
@@ -201,3 +201,70 @@ def test_random_orders_lose_no_page(seed):
     snapshot = manager.capacity()
     assert all(f + r == t for f, r, t in zip(snapshot.free_pages, snapshot.reclaimable_pages, snapshot.total_pages))
     assert snapshot.free_slots == 5
+
+
+def _cache_prompt(manager, rid, prompt):
+    manager.admit(rid)
+    matched = manager.attach_prefix(rid, prompt)
+    manager.commit(manager.prepare([(rid, len(prompt) - matched)]))
+    added = manager.cache_prefix(rid, prompt)
+    manager.check_invariants()
+    return matched, added
+
+
+def test_prefix_cache_at_its_limit_replaces_the_least_recently_used():
+    """With ``prefix_cache_max_entries`` reached, a new prompt's pages take the place of the oldest ones that
+    nobody holds (miniserve/kv/prefix_cache.py:122-125), and are then hit."""
+    manager = CacheManager([FULL], page_size=4, num_pages=16, max_seqs=4, enable_prefix_cache=True,
+                           prefix_cache_max_entries=3)
+    first = list(range(100, 112)) + [1]                   # three full pages
+    assert _cache_prompt(manager, "a", first) == (0, 3)
+    manager.release("a")
+    second = list(range(200, 208)) + [2]                  # two full pages: the first prompt's last two make room
+    assert _cache_prompt(manager, "b", second) == (0, 2)
+    manager.release("b")
+    assert len(manager.prefix.entries) == 3
+    manager.admit("c")
+    assert manager.attach_prefix("c", second + [5]) == 8   # the new prompt is hit in full
+    manager.admit("d")
+    assert manager.attach_prefix("d", first) == 4          # of the old one the first page is left
+    manager.check_invariants()
+    manager.release("c"), manager.release("d")
+    assert manager.capacity().free_pages == (13,) and manager.capacity().reclaimable_pages == (3,)
+
+
+def test_prefix_cache_at_its_limit_never_replaces_an_entry_in_use():
+    manager = CacheManager([FULL], page_size=4, num_pages=16, max_seqs=4, enable_prefix_cache=True,
+                           prefix_cache_max_entries=2)
+    first = list(range(100, 108)) + [1]
+    assert _cache_prompt(manager, "a", first) == (0, 2)    # "a" stays live: both entries are in use
+    held = [manager.prefix.entries[d].pages for d in manager.prefix.entries]
+    second = list(range(200, 208)) + [2]
+    assert _cache_prompt(manager, "b", second) == (0, 0)   # nothing can be replaced: the prompt stays uncached
+    assert [manager.prefix.entries[d].pages for d in manager.prefix.entries] == held
+    manager.release("a")
+    third = list(range(300, 312)) + [3]                    # three pages into a cache of two: two are cached, and
+    assert _cache_prompt(manager, "c", third) == (0, 2)    # the chain being inserted never replaces itself
+    manager.admit("e")
+    assert manager.attach_prefix("e", third) == 8
+    manager.check_invariants()
+
+
+def test_reclaimable_counts_only_what_eviction_can_free():
+    """An entry that only the cache holds, standing before one that a request holds, is not reclaimable:
+    eviction takes leaves first and the leaf is in use."""
+    manager = CacheManager([FULL], page_size=4, num_pages=12, max_seqs=4, enable_prefix_cache=True)
+    head = list(range(50, 54))
+    manager.admit("b")                                     # admitted before anything is cached: no hit,
+    assert manager.attach_prefix("b", head + [9, 9, 9, 9, 1]) == 0
+    assert _cache_prompt(manager, "a", head + [3]) == (0, 1)
+    manager.release("a")                                   # the cache alone holds the page of `head`
+    manager.commit(manager.prepare([("b", 9)]))            # "b" computes its own copy of `head`
+    assert manager.cache_prefix("b", head + [9, 9, 9, 9, 1]) == 1   # and caches its second page behind a's entry
+    snapshot = manager.capacity()
+    assert snapshot.reclaimable_pages == (0,) and manager.evictable_now() == 0
+    with pytest.raises(OutOfPagesError):
+        manager.prepare([("b", 4 * snapshot.free_pages[0] + 4)])
+    manager.check_invariants()
+    manager.release("b")
+    assert manager.capacity().reclaimable_pages == (2,) and manager.evictable_now() == 2
