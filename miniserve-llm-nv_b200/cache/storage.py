@@ -4,7 +4,8 @@ the sampling records of the state slots.
 A paged group's pools have the shape ``[runs, pages + 1, kv_heads, page_size, head_dim]`` for
 keys and the same for values (the layout of miniserve/kv/layout.py:65-75 per group); the last
 page is a scratch page that no request ever holds: padding rows of a replayed CUDA graph write
-to it.  Pools are allocated once and never move.
+to it.  State tensors and sampling records likewise have one slot more than there are requests,
+the scratch slot, which padding rows read and write.  Pools are allocated once and never move.
 """
 
 from __future__ import annotations
@@ -43,16 +44,21 @@ class CacheStorage:
             elif isinstance(need, StateNeed):
                 self.key_pools.append(None)
                 self.value_pools.append(None)
-                self.states.append(torch.zeros((group.n_slots, max_seqs) + tuple(need.shape), dtype=need.dtype,
+                self.states.append(torch.zeros((group.n_slots, max_seqs + 1) + tuple(need.shape), dtype=need.dtype,
                                                device=device))
                 self.paged_index.append(None)
             else:
                 raise TypeError(f"unknown cache need {need!r}")
-        self.sampling_records = torch.zeros((max_seqs, SAMPLING_RECORD_WORDS), dtype=torch.int32, device=device)
+        self.sampling_records = torch.zeros((max_seqs + 1, SAMPLING_RECORD_WORDS), dtype=torch.int32, device=device)
 
     @property
     def scratch_page(self) -> int:
         return self.num_pages
+
+    @property
+    def scratch_slot(self) -> int:
+        """The state slot of padding rows: no request ever holds it."""
+        return self.max_seqs
 
     @staticmethod
     def bytes_per_page(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype) -> int:

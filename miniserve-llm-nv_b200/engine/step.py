@@ -60,11 +60,13 @@ class DecodeGraph:
         self.host_np = self.host.numpy()             # same memory, cheaper to fill from Python lists
         self.live_rows = -1
         self.copied: Optional[torch.cuda.Event] = None     # recorded after the last copy of the host mirror
-        self.row_owner: list = [None] * rows         # per row: (request id, pages already written per group)
+        # per row: (the request's cache record, pages of its committed table that the mirror shows, per group)
+        self.row_owner: list = [None] * rows
         self.has_windows = any(need.window is not None for need in manager.paged_needs)
         self.meta = torch.zeros(self.offsets[-1], dtype=torch.int32, device=sf.device)
         self.n_groups = n_groups
         self.scratch = storage.scratch_page
+        self.scratch_slot = storage.scratch_slot
         self._fill_padding(0)
         self.meta.copy_(self.host)
         views = [self.meta[self.offsets[i]:self.offsets[i + 1]] for i in range(len(sizes))]
@@ -98,7 +100,7 @@ class DecodeGraph:
         self.kernel_launches = kernels.launch_count - before
 
     def _fill_padding(self, first_row: int) -> None:
-        """Rows from ``first_row`` on become padding: token 0 at position 0 on the scratch page."""
+        """Rows from ``first_row`` on become padding: token 0 at position 0 on the scratch page, in the scratch slot."""
         import numpy
 
         o, rows, host = self.offsets, self.rows, self.host_np
@@ -108,7 +110,7 @@ class DecodeGraph:
         host[o[2]:o[3]] = numpy.arange(rows, dtype=numpy.int32)
         host[o[3]:o[4]] = numpy.arange(rows + 1, dtype=numpy.int32)
         host[o[4] + first_row:o[5]] = 1
-        host[o[5] + first_row:o[6]] = 0
+        host[o[5] + first_row:o[6]] = self.scratch_slot
         host[o[6]:o[7]] = numpy.arange(rows, dtype=numpy.int32)
         host[o[7] + first_row:o[8]] = 0
         for g in range(self.n_groups):
@@ -293,16 +295,20 @@ class StepFunction:
             tokens.append(token)
             positions.append(item.start)
             lens.append(item.end)
-            slots_state.append(manager.requests[entry.request_id].slot)
+            record = manager.requests[entry.request_id]
+            slots_state.append(record.slot)
             owner = graph.row_owner[row]
-            if feed_back and (owner is None or owner[0] != entry.request_id):
+            if feed_back and (owner is None or owner[0] is not record):
                 raise ValueError(f"row {row} of the step before belonged to another request")
-            same = owner is not None and owner[0] == entry.request_id and not graph.has_windows
+            # The row keeps what it shows only for the very same admission (a request id can come back after a
+            # release, with other pages), and only as far as the pages were committed when they were written:
+            # a page reserved for a step that was aborted may be another one next time.
+            same = owner is not None and owner[0] is record and not graph.has_windows
             for g in range(graph.n_groups):
                 table = item.tables[g]
                 if len(table) > graph.width:
                     raise ValueError("a block table is wider than the model's longest context")
-                # pages that this row already shows (same request as in the last replay) stay; new ones are checked
+                # committed pages that this row already shows stay; the others are checked and written
                 first = owner[1][g] if same and owner[1][g] <= len(table) else 0
                 fresh = table[first:]
                 if any(p != RELEASED and not 0 <= p < limit for p in fresh):
@@ -316,7 +322,7 @@ class StepFunction:
                 if not 0 <= slot < limit * ps:
                     raise ValueError(f"slot {slot} outside the pool")
                 host[o[9 + 2 * g] + row] = slot
-            graph.row_owner[row] = (entry.request_id, [len(item.tables[g]) for g in range(graph.n_groups)])
+            graph.row_owner[row] = (record, [len(item.tables[g]) - len(item.new_pages[g]) for g in range(graph.n_groups)])
         host[o[0]:o[0] + n] = tokens
         host[o[1]:o[1] + n] = positions
         host[o[4]:o[4] + n] = lens

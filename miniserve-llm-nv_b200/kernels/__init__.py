@@ -236,8 +236,10 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
             _f(scale), _i(window if window else 0), _ptr(out), _i(n), _stream()))
         return
 
-    def run(first: int, last: int, longest: int) -> None:
-        """Requests first .. last - 1 (their tokens are found through query_start, which holds absolute rows)."""
+    def run(first: int, last: int, longest: int, rows: int) -> None:
+        """Requests first .. last - 1 (their tokens are found through query_start, which holds absolute rows);
+        ``rows``: one past the last row of the batch that these requests own, which sizes the scratch of the
+        key splits and the merge that follows them."""
         tables, starts, lens = block_tables[first:last], query_start[first:last + 1], context_lens[first:last]
         count = last - first
         group = n_q // n_kv
@@ -253,12 +255,12 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         splits = lib.ms_attention_mma_splits(_i(head_dim), _i(count), _i(n_kv), _i(n_q), _i(longest), _i(max_context_len))
         part_o = part_lse = None
         if splits > 1:
-            part_o = torch.empty((n * n_q * splits, head_dim), dtype=torch.float32, device=q.device)
-            part_lse = torch.empty((n * n_q * splits,), dtype=torch.float32, device=q.device)
+            part_o = torch.empty((rows * n_q * splits, head_dim), dtype=torch.float32, device=q.device)
+            part_lse = torch.empty((rows * n_q * splits,), dtype=torch.float32, device=q.device)
         _check(lib.ms_paged_attention_mma(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(tables), _i(block_tables.shape[1]), _ptr(starts), _ptr(lens),
             _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale), _i(window if window else 0), _ptr(out),
-            _ptr(part_o), _ptr(part_lse), _i(splits), _i(count), _i(longest), _i(n), _stream()))
+            _ptr(part_o), _ptr(part_lse), _i(splits), _i(count), _i(longest), _i(rows), _stream()))
 
     leading_single = 0
     if host_query_start and max_query_len > 1 and len(host_query_start) == n_requests + 1:
@@ -266,10 +268,10 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                and host_query_start[leading_single + 1] - host_query_start[leading_single] == 1):
             leading_single += 1
     if 0 < leading_single < n_requests:
-        run(0, leading_single, 1)
-        run(leading_single, n_requests, max_query_len)
+        run(0, leading_single, 1, leading_single)      # single tokens are the batch's first rows, one each
+        run(leading_single, n_requests, max_query_len, n)
     else:
-        run(0, n_requests, max_query_len)
+        run(0, n_requests, max_query_len, n)
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -26,3 +26,19 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_terminal_summary(terminalreporter):
+    """How close the engine came to its error bounds, worst case per group of tests (so that drift is seen)."""
+    import helpers
+
+    if not helpers.WORST_RATIOS:
+        return
+    groups: dict[str, tuple[float, str]] = {}
+    for case, ratio in helpers.WORST_RATIOS.items():
+        group = case.split("[")[0] + ("/float32" if "float32" in case else "/bfloat16")
+        if ratio >= groups.get(group, (0.0, ""))[0]:
+            groups[group] = (ratio, case)
+    terminalreporter.write_line("worst error / bound per group of tests:")
+    for group, (ratio, case) in sorted(groups.items()):
+        terminalreporter.write_line(f"  {ratio:6.3f}  {group}  ({case})")

@@ -128,6 +128,45 @@ def cut_mixed(requests: dict[str, list[int]], seed: int = 0, max_live: int = 4) 
     return steps
 
 
+def cut_many_live(requests: dict[str, list[int]], prompt_lens: dict[str, int], seed: int = 0, per_step: int = 5) -> list[dict]:
+    """All requests live at once: prompts whole, a few per step (the last position wanted), then every request
+    decoded token by token, teacher-forced, in steps of single tokens whose live set changes: all of them, the
+    first five eighths, every other one in reverse order, a random subset, all again ... until every request
+    has had all its tokens.  A step of single tokens is what a captured decode graph replays, so this walks
+    the graphs through full buckets, padded buckets and rows that change owner between replays."""
+    rng = random.Random(seed)
+    ids = list(requests)
+    steps, step = [], 0
+    for start in range(0, len(ids), per_step):
+        entries = [{"id": rid, "tokens": requests[rid][:prompt_lens[rid]], "want": [prompt_lens[rid] - 1]}
+                   for rid in ids[start:start + per_step]]
+        steps.append({"step": step, "entries": entries, "end": []})
+        step += 1
+    cursor = {rid: prompt_lens[rid] for rid in ids}
+    round_index = 0
+    while any(cursor[rid] < len(requests[rid]) for rid in ids):
+        alive = [rid for rid in ids if cursor[rid] < len(requests[rid])]
+        kind = round_index % 5
+        if kind == 1:
+            chosen = alive[:max(1, (5 * len(alive) + 7) // 8)]
+        elif kind == 2:
+            chosen = alive[::2][::-1]
+        elif kind == 3:
+            chosen = rng.sample(alive, max(1, rng.randrange(len(alive) // 2, len(alive) + 1)))
+        else:
+            chosen = alive
+        entries, ended = [], []
+        for rid in chosen:
+            entries.append({"id": rid, "tokens": [requests[rid][cursor[rid]]], "want": [0]})
+            cursor[rid] += 1
+            if cursor[rid] == len(requests[rid]):
+                ended.append(rid)
+        steps.append({"step": step, "entries": entries, "end": ended})
+        step += 1
+        round_index += 1
+    return steps
+
+
 def max_live_tokens(steps: list[dict], granule: int = 64) -> int:
     """The --max-tokens a trace needs: most tokens live at once, each request rounded up to ``granule``."""
     held: dict[str, int] = {}
@@ -139,6 +178,13 @@ def max_live_tokens(steps: list[dict], granule: int = 64) -> int:
         for rid in record["end"]:
             held.pop(rid, None)
     return peak
+
+
+WORST_RATIOS: dict[str, float] = {}     # test case -> worst error / bound seen; printed at the end of a run
+
+
+def note_ratio(case: str, ratio: float) -> None:
+    WORST_RATIOS[case] = max(WORST_RATIOS.get(case, 0.0), ratio)
 
 
 def collect(steps: list[dict], outputs: dict[int, torch.Tensor]) -> dict[str, dict[int, torch.Tensor]]:
@@ -157,3 +203,48 @@ def collect(steps: list[dict], outputs: dict[int, torch.Tensor]) -> dict[str, di
         for rid in record["end"]:
             cursor.pop(rid, None)
     return result
+
+
+def run_shared_prefix_trace(runtime, vocab: int, page_size: int):
+    """Three requests through the trace session of ``runtime`` (built with prefix reuse on): 'p' computes its
+    prompt and offers its pages; 'q', arriving while 'p' is live, starts with the same 16 tokens and attaches
+    them; 'r' starts with 32 tokens of 'p'.  Checks who holds which pages on the way.  Returns the token
+    lists and {request: {position: logits}} of every position that was computed."""
+    from miniserve_b200.trace import TraceSession
+
+    shared = random_tokens(vocab, 16, seed=40)
+    first = shared + random_tokens(vocab, 21, seed=41)
+    second = shared + random_tokens(vocab, 30, seed=42)
+    third = list(first[:32]) + random_tokens(vocab, 5, seed=43)
+    session, manager = TraceSession(runtime), runtime.manager
+    shared_pages = 16 // page_size
+    steps = [
+        {"step": 0, "entries": [{"id": "p", "tokens": first[:20], "want": list(range(20))}], "cache": ["p"], "end": []},
+        # the second request arrives while the first is live: it names the prefix and runs the rest in two portions
+        {"step": 1, "entries": [{"id": "p", "tokens": first[20:30], "want": list(range(10))},
+                                {"id": "q", "prefix": shared, "tokens": second[16:29], "want": list(range(13))}], "end": []},
+        {"step": 2, "entries": [{"id": "p", "tokens": first[30:], "want": list(range(len(first) - 30))},
+                                {"id": "q", "tokens": second[29:], "want": list(range(len(second) - 29))}],
+         "cache": ["p"], "end": []},
+        # by now 32 tokens of the first request are cached: the third attaches all of them
+        {"step": 3, "entries": [{"id": "r", "prefix": third[:32], "tokens": third[32:], "want": list(range(5))}],
+         "end": ["p", "q", "r"]},
+    ]
+    outputs = {}
+    for record in steps:
+        outputs[record["step"]] = session.run(record).double().cpu()
+        if record["step"] == 1:
+            p, q = manager.requests["p"], manager.requests["q"]
+            assert p.tables[0][:shared_pages] == q.tables[0][:shared_pages]
+            assert all(manager.allocators[0].refcount(page) == 3 for page in q.tables[0][:shared_pages])   # p, q, the cache
+            assert not set(p.tables[0][shared_pages:]) & set(q.tables[0][shared_pages:])
+        manager.check_invariants()
+    got: dict[str, dict[int, torch.Tensor]] = {"p": {}, "q": {}, "r": {}}
+    got["p"].update({i: outputs[0][i] for i in range(20)})
+    got["p"].update({20 + i: outputs[1][i] for i in range(10)})
+    got["q"].update({16 + i: outputs[1][10 + i] for i in range(13)})
+    got["p"].update({30 + i: outputs[2][i] for i in range(len(first) - 30)})
+    got["q"].update({29 + i: outputs[2][len(first) - 30 + i] for i in range(len(second) - 29)})
+    got["r"].update({32 + i: outputs[3][i] for i in range(5)})
+    assert sorted(got["q"]) == list(range(16, len(second))) and sorted(got["p"]) == list(range(len(first)))
+    return {"p": first, "q": second, "r": third}, got

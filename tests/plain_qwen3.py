@@ -135,8 +135,9 @@ def plain_decoder_layer(x, weights, layer, config, positions):
     return x
 
 
-def plain_logits(token_ids, weights: dict[str, torch.Tensor], config: dict) -> torch.Tensor:
-    """Logits ``[T, vocab]`` of one whole sequence starting at position 0.
+def plain_logits(token_ids, weights: dict[str, torch.Tensor], config: dict, rows=None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one whole sequence starting at position 0 (``rows``: of these positions only,
+    where a large vocabulary would make all of them slow).
 
     Embedding without scaling (miniserve/model/qwen3.py:475), the layers in
     order (qwen3.py:482-485), final norm (qwen3.py:486), then the output matrix,
@@ -148,6 +149,8 @@ def plain_logits(token_ids, weights: dict[str, torch.Tensor], config: dict) -> t
     for layer in range(config["num_hidden_layers"]):
         x = plain_decoder_layer(x, weights, layer, config, positions)
     x = plain_rmsnorm(x, weights["model.norm.weight"], config["rms_norm_eps"])
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), dtype=torch.long)]
     if config.get("tie_word_embeddings", False):
         head = weights["model.embed_tokens.weight"]
     else:
