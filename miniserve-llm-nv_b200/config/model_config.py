@@ -100,7 +100,12 @@ class Qwen3Config:
         if self.num_attention_heads % self.num_key_value_heads != 0:
             raise ValueError("num_attention_heads must be divisible by num_key_value_heads")
         if self.head_dim % 2 != 0:
-            raise ValueError("RoPE requires an even head_dim")
+            raise ValueError(f"head_dim {self.head_dim} is odd; the rotation pairs the elements of a head")
+        from ..kernels import MAX_HEAD_DIM      # a number, no device work: the largest head the attention kernels take
+
+        if self.head_dim > MAX_HEAD_DIM:
+            raise ValueError(f"head_dim {self.head_dim} exceeds {MAX_HEAD_DIM}, the largest head size the attention "
+                             "kernels of this engine take")
         for name in ("rms_norm_eps", "rope_theta"):
             value = getattr(self, name)
             if not math.isfinite(value) or value <= 0:

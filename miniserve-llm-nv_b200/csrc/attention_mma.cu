@@ -15,6 +15,7 @@
 // its normalised float32 partial result and log-sum-exp to scratch and a second kernel
 // merges them.
 #include "common.cuh"
+#include "attention_static.h"   // the declaration its users compile against is checked against the definition below
 
 namespace ms {
 

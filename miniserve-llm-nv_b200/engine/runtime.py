@@ -7,7 +7,8 @@ allocate the page pools once, wire the cache manager and the step function.
 
 from __future__ import annotations
 
-from dataclasses import dataclass, replace
+import logging
+from dataclasses import dataclass, field, replace
 from pathlib import Path
 from typing import Optional, Union
 
@@ -24,6 +25,7 @@ from ..weights.random_init import random_tensors_on_device
 from .step import StepFunction
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+log = logging.getLogger("miniserve_b200")
 
 
 @dataclass
@@ -36,6 +38,7 @@ class Runtime:
     step_function: StepFunction
     max_model_len: int
     load_report: object
+    attention_kernels: list = field(default_factory=list)    # per paged cache group: what kernels.attention_kernels says
 
 
 def require_device(device: str) -> torch.device:
@@ -94,4 +97,29 @@ def build_runtime(model_dir: Union[str, Path, None], engine_config: Optional[Eng
     step_function = StepFunction(model, storage, manager, max_model_len,
                                  use_graphs=engine_config.decode_execution == "cuda_graph")
     resolved = replace(engine_config, max_model_len=max_model_len, num_kv_blocks=num_pages)
-    return Runtime(config, resolved, model, storage, manager, step_function, max_model_len, report)
+    chosen = _report_attention_kernels(model, dtype, page_size)
+    return Runtime(config, resolved, model, storage, manager, step_function, max_model_len, report, chosen)
+
+
+def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size: int) -> list:
+    """Says once per build which attention kernel each paged cache group gets, loudly where bfloat16 falls back
+    to the general float32-arithmetic kernel (right, but many times slower than the tensor-core kernels)."""
+    from ..parts.base import PagedKVNeed
+
+    chosen = []
+    for index, run in enumerate(model.spec.order):
+        plan = model.run_caches[index]
+        mixer = model.blocks[run.layer].mixer
+        if plan is None or not plan.writable or plan.slot != 0 or not isinstance(model.cache_groups[plan.group].need, PagedKVNeed):
+            continue
+        need = model.cache_groups[plan.group].need
+        n_q = getattr(mixer, "num_heads", need.num_kv_heads)
+        names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size)
+        chosen.append(dict(group=plan.group, head_dim=need.head_dim, window=need.window, **names))
+        slow = dtype == torch.bfloat16 and "general" in names.values()
+        log.log(logging.WARNING if slow else logging.INFO,
+                "cache group %d (head size %d, %d/%d heads, pages of %d%s): decode steps on the %s kernel, prompt "
+                "portions on the %s kernel%s", plan.group, need.head_dim, n_q, need.num_kv_heads, page_size,
+                f", window {need.window}" if need.window else "", names["decode"], names["prompt"],
+                " (no tensor-core kernel is built for this head size)" if slow else "")
+    return chosen

@@ -194,6 +194,22 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> 
 
 # --------------------------------------------------------------------------- attention
 
+MAX_HEAD_DIM = 512      # of the general attention kernel (attention_generic.cu: 16 output lanes per thread)
+
+
+def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, page_size: int) -> dict:
+    """Which kernel :func:`paged_attention` runs for these sizes: ``{"decode": name, "prompt": name}`` with the
+    names ``tcgen05``, ``mma.sync`` and ``general`` (float32 arithmetic, any size; the only one of the float32
+    path, and what bfloat16 falls back to for head sizes the tensor-core kernels are not built for)."""
+    lib = library()
+    if dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+        return {"decode": "general", "prompt": "general"}
+    prompt = "mma.sync"
+    if USE_TCGEN05_ATTENTION and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(page_size)):
+        prompt = "tcgen05"
+    return {"decode": "mma.sync", "prompt": prompt}
+
+
 
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                     request_of_token: torch.Tensor, positions: torch.Tensor, query_start: torch.Tensor,

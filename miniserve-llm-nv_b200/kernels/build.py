@@ -63,7 +63,7 @@ def source_files() -> list[Path]:
 def _digest() -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for path in sorted(SOURCE_DIR.glob("*.cu*")):
+    for path in sorted(p for pattern in ("*.cu", "*.cuh", "*.h") for p in SOURCE_DIR.glob(pattern)):
         h.update(path.name.encode())
         h.update(path.read_bytes())
     return h.hexdigest()

@@ -33,8 +33,10 @@ class Attention(Part):
                  k_norm_name: str = "k_norm.weight") -> None:
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
-        if head_dim % 16 or not 16 <= head_dim <= 256:
-            raise ValueError(f"head size {head_dim} is not a multiple of 16 in 16..256")
+        if head_dim % 2 or not 2 <= head_dim <= kernels.MAX_HEAD_DIM:
+            # what the general attention kernel and the fused append take; the tensor-core kernels take fewer
+            # sizes, and kernels.attention_kernels() says which of them a given size gets
+            raise ValueError(f"head size {head_dim} is not an even number in 2..{kernels.MAX_HEAD_DIM}")
         self.prefix = prefix
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.qk_norm, self.eps = bool(qk_norm), float(eps)

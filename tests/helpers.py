@@ -28,7 +28,17 @@ TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
               num_hidden_layers=2, num_attention_heads=8, num_key_value_heads=2, head_dim=64, vocab_size=500,
               max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0, attention_dropout=0.0,
               hidden_act="silu", attention_bias=False, tie_word_embeddings=False)
-TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D}
+# Head sizes that the configuration allows (even) but no tensor-core kernel is built for: 24 with as many kv heads as
+# query heads, 40 with an intermediate size that is no multiple of eight (gate and up rows are then not interleaved).
+TINY_E = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=80, intermediate_size=144,
+              num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5, head_dim=24, vocab_size=211,
+              max_position_embeddings=512, rms_norm_eps=1e-6, rope_theta=10000.0, attention_dropout=0.0,
+              hidden_act="silu", attention_bias=False, tie_word_embeddings=True)
+TINY_F = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=56, intermediate_size=100,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=40, vocab_size=300,
+              max_position_embeddings=512, rms_norm_eps=1e-5, rope_theta=500000.0, attention_dropout=0.0,
+              hidden_act="silu", attention_bias=False, tie_word_embeddings=False)
+TINY = {"a": TINY_A, "b": TINY_B, "c": TINY_C, "d": TINY_D, "e": TINY_E, "f": TINY_F}
 
 
 def make_folder(tmp_path: Path, name: str, seed: int = 0, stored_dtype: str = "bfloat16", matrix_std: float = 0.05) -> Path:

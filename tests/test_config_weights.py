@@ -29,7 +29,7 @@ def test_config_reads_every_size_and_never_infers_head_dim():
 @pytest.mark.parametrize("key,value", [
     ("attention_bias", True), ("mlp_bias", True), ("attention_dropout", 0.1), ("hidden_act", "gelu"),
     ("rope_scaling", {"type": "linear", "factor": 2.0}), ("rope_interleaved", True), ("use_sliding_window", True),
-    ("hidden_size", 64.0), ("hidden_size", True), ("vocab_size", 0), ("num_key_value_heads", 3), ("head_dim", 15),
+    ("hidden_size", 64.0), ("hidden_size", True), ("vocab_size", 0), ("num_key_value_heads", 3), ("head_dim", 15), ("head_dim", 514),
     ("rms_norm_eps", float("nan")), ("rms_norm_eps", 0.0), ("rope_theta", -1.0), ("rope_theta", "1e6"),
     ("tie_word_embeddings", "yes")])
 def test_config_rejections(key, value):

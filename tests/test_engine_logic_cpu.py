@@ -41,7 +41,7 @@ def replay(runtime, steps):
     return outputs
 
 
-@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4)])
+@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4), ("f", 8)])
 @pytest.mark.parametrize("cutting", ["whole", "tail", "portions", "mixed"])
 def test_cuttings_match_plain_on_cpu(cpu_runtime, name, page_size, cutting):
     vocab = helpers.TINY[name]["vocab_size"]

@@ -100,8 +100,7 @@ def test_long_decoding_under_few_pages(tmp_path, dtype):
     assert llm.engine.stats.preemptions >= 1
     for prompt, result in zip(prompts, results):
         assert len(result.token_ids) == 200
-        if dtype == "float32":
-            check_against_plain(folder, prompt, result.token_ids, params, dtype)
+        check_against_plain(folder, prompt, result.token_ids, params, dtype)     # bfloat16: under the near-tie rule
     assert llm.runtime.manager.capacity().free_slots == 3
 
 

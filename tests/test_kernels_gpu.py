@@ -261,6 +261,48 @@ def test_paged_attention_window_edge(kernels, dtype, query_len, d):
         assert close == visible, (key, visible)
 
 
+@pytest.mark.parametrize("tcgen05", [True, False])
+@pytest.mark.parametrize("window", [None, 100])
+@pytest.mark.parametrize("d,n_q,n_kv,page_size", [(64, 8, 2, 16), (128, 4, 2, 64), (128, 16, 8, 16)])
+@pytest.mark.parametrize("query_len", [64, 300])
+def test_prompt_attention_finds_single_keys(kernels, monkeypatch, query_len, d, n_q, n_kv, page_size, window, tcgen05):
+    """Prompt portions (the tcgen05 kernel, and the four-warp mma.sync kernel in its place): one key is made to
+    dominate one query row, and the output of that row must be that key's value row when the key is visible
+    and must not be when the causal mask or the window hides it.  Keys at the places where an index can be
+    off by one: key 0, both sides of a 128-key tile edge, a page's last slot, the diagonal, one past the
+    diagonal, and both sides of the window's far edge; for the first and the last row of a portion that
+    starts in the middle of a page."""
+    monkeypatch.setattr(kernels, "USE_TCGEN05_ATTENTION", tcgen05)
+    dtype, length = torch.bfloat16, 707
+    case = _attention_case(dtype, n_q, n_kv, d, page_size, [length, 90], [query_len, 17], 33)
+    q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = case
+    group = n_q // n_kv
+    first_pos = length - query_len
+    assert first_pos % page_size != 0
+    for row in (0, query_len - 1, query_len // 2):
+        pos = first_pos + row
+        lowest = 0 if window is None else pos - window + 1
+        targets = {0, 127, 128, page_size - 1, (pos // page_size) * page_size - 1, pos - 1, pos, pos + 1, 383, 384}
+        if window is not None:
+            targets |= {lowest - 1, lowest, lowest + 1}
+        for target in sorted(t for t in targets if 0 <= t < length):
+            visible = lowest <= target <= pos
+            kp = k_pool.clone()
+            page, offset = int(tables[0, target // page_size]), target % page_size
+            for head in (0, n_q - 1):
+                kp[page, head // group, offset] = (q[row, head].float() * 40).to(dtype)
+            out = torch.empty_like(q)
+            kernels.paged_attention(q, kp, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                                    max_ctx, d ** -0.5, window, out)
+            kernels.check_device_errors(q.device)
+            for head in (0, n_q - 1):
+                found = torch.allclose(out[row, head].float(), v_pool[page, head // group, offset].float(), atol=3e-2)
+                assert found == visible, (row, target, head, visible)
+    # and the whole output, dominant keys and all, against the plain kernel
+    _check_attention(kernels, dtype, (q, kp, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                                      max_ctx), d, window)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 1, 1), (3, 331, 72), (37, 384, 96), (64, 64, 16), (65, 130, 200), (130, 257, 1031)])
 def test_linear_float32(kernels, m, n, k):
     x, w = rand((m, k), torch.float32, 40), rand((n, k), torch.float32, 41)

@@ -81,7 +81,7 @@ def check_against(request, got, expected_of, dtype, wanted=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4), ("d", 16)])
+@pytest.mark.parametrize("name,page_size", [("a", 16), ("b", 8), ("c", 4), ("d", 16), ("e", 16), ("f", 8)])
 @pytest.mark.parametrize("cutting", list(CUTTINGS))
 def test_cuttings_match_plain(request, tmp_path, dtype, name, page_size, cutting):
     vocab = helpers.TINY[name]["vocab_size"]
@@ -90,6 +90,8 @@ def test_cuttings_match_plain(request, tmp_path, dtype, name, page_size, cutting
     folder = helpers.make_folder(tmp_path, name, seed=2)
     pages = (helpers.max_live_tokens(steps, granule=2 * page_size) + page_size - 1) // page_size
     runtime = build(folder, dtype, pages, page_size)
+    expected_kernel = {"a": "general", "b": "mma.sync", "c": "general", "d": "mma.sync", "e": "general", "f": "general"}[name]
+    assert [k["decode"] for k in runtime.attention_kernels] == ["general" if dtype == "float32" else expected_kernel]
     got = helpers.collect(steps, replay(runtime, steps))
     for rid, tokens in requests.items():
         assert sorted(got[rid]) == list(range(len(tokens)))
