@@ -1,10 +1,10 @@
 """The reference arm of ``bench.py``: MiniServe-LLM-NV itself, unmodified, from ``baseline/_ref``.
 
-Install (once, offline):
+Install (once, offline; from a writable copy of the project, because its build writes into the source
+tree, with a wheel directory for the build tools):
 
-    cp -r /path/to/MiniServe-LLM-NV /tmp/ref_copy
-    python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse \
-        --target baseline/_ref /tmp/ref_copy
+    python -m pip install --no-index --no-build-isolation --no-deps --find-links <wheel directory> \
+        --target baseline/_ref <writable copy of MiniServe-LLM-NV>
 
 The engine is wired exactly as MiniServe's own start-up wires it
 (miniserve/api/bootstrap.py:85-163: ModelConfig, EngineConfig, Qwen3ForCausalLM, KVLayout,

@@ -151,6 +151,24 @@ class CacheManager:
     def length(self, request_id: str) -> int:
         return self.requests[request_id].length
 
+    def truncate(self, request_id: str, length: int) -> None:
+        """Forgets the request's tokens from position ``length`` on and gives back the pages that held only them
+        (a request that drops tokens it computed ahead, or a benchmark that decodes the same steps again).  Not
+        for groups with a sliding window: the pages it would have to bring back are gone."""
+        if self._open is not None and any(item.request_id == request_id for item in self._open.items):
+            raise RuntimeError(f"request {request_id!r} is part of the open step; commit or abort first")
+        entry = self.requests[request_id]
+        if not 0 <= length <= entry.length:
+            raise ValueError(f"request {request_id!r} holds {entry.length} tokens; cannot truncate to {length}")
+        if any(need.window is not None for need in self.paged_needs) or self.state_needs:
+            raise RuntimeError("truncate needs every token's keys and no per-request state")
+        keep = (length + self.page_size - 1) // self.page_size
+        for group, table in enumerate(entry.tables):
+            for page in table[keep:]:
+                self.allocators[group].release(page)
+            del table[keep:]
+        entry.length = length
+
     # ------------------------------------------------------------------ capacity
     def pages_for(self, start: int, end: int) -> int:
         """New pages a request of committed length ``start`` needs to reach ``end`` (per group)."""

@@ -268,3 +268,32 @@ def test_reclaimable_counts_only_what_eviction_can_free():
     manager.check_invariants()
     manager.release("b")
     assert manager.capacity().reclaimable_pages == (2,) and manager.evictable_now() == 2
+
+
+def test_truncate_gives_back_the_pages_behind_the_new_end():
+    manager = CacheManager([FULL], page_size=4, num_pages=8, max_seqs=2, enable_prefix_cache=True)
+    prompt = list(range(13))
+    manager.admit("a")
+    manager.commit(manager.prepare([("a", 13)]))            # 4 pages
+    manager.cache_prefix("a", prompt)                       # the cache holds the first 3 too
+    manager.truncate("a", 6)
+    assert manager.length("a") == 6 and manager.requests["a"].tables == [[0, 1]]
+    assert manager.capacity().free_pages == (5,)            # page 3 is free; page 2 is held by the cache alone
+    manager.check_invariants()
+    reservation = manager.prepare([("a", 3)])               # goes on from token 6, in page 1 and a new page
+    assert reservation.items[0].slots[0] == [6, 7, 12] and reservation.items[0].start == 6
+    manager.commit(reservation)
+    with pytest.raises(ValueError):
+        manager.truncate("a", 10)
+    reservation = manager.prepare([("a", 1)])
+    with pytest.raises(RuntimeError):
+        manager.truncate("a", 2)
+    manager.abort(reservation)
+    manager.truncate("a", 0)
+    assert manager.requests["a"].tables == [[]]
+    manager.check_invariants()
+    windowed = CacheManager([window_group(8)], 4, 4, 2)
+    windowed.admit("w")
+    windowed.commit(windowed.prepare([("w", 3)]))
+    with pytest.raises(RuntimeError):
+        windowed.truncate("w", 1)

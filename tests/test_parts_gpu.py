@@ -264,6 +264,12 @@ def register_toy():
 
         def forward(self, x, ctx, cache):
             projected = (x.float() @ self.weight.float().T)
+            if not ctx.host_state_slots:
+                # inside a captured decode step nothing is known on the host: one token per row, slots on the device
+                slots = ctx.state_slots.long()
+                state = cache.states.index_select(0, slots) * self.decay + projected
+                cache.states.index_copy_(0, slots, state)
+                return state.to(x.dtype)
             out = torch.empty_like(projected)
             for r in range(ctx.n_requests):
                 state = cache.states[ctx.host_state_slots[r]]
@@ -369,6 +375,34 @@ def test_toy_architecture_with_stateful_mixer(tmp_path, dtype, cutting):
         bound = (3e-5 if dtype == "float32" else 4e-2) * max(1.0, float(expected.abs().max()))
         for position, row in got[rid].items():
             assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_stateful_mixer_in_a_padded_decode_graph(tmp_path, dtype):
+    """Three requests decode as the captured graph for four rows: the padding row runs the stateful mixer too,
+    and must read and write the scratch state slot, not the slot of a live request."""
+    from test_replay_gpu import build, replay
+
+    register_toy()
+    from miniserve_b200.weights import write_random_model
+
+    folder = write_random_model(tmp_path / "toy", TOY, seed=9, matrix_std=0.08)
+    prompt_lens = {"t0": 5, "t1": 1, "t2": 12}
+    requests = {rid: helpers.random_tokens(TOY["vocab_size"], n + 9, seed=700 + i) for i, (rid, n) in enumerate(prompt_lens.items())}
+    steps = helpers.cut_many_live(requests, prompt_lens, seed=1)
+    runtime = build(folder, dtype, 12, 8, max_seqs=3, execution="cuda_graph", max_model_len=64)
+    got = helpers.collect(steps, replay(runtime, steps))
+    assert runtime.step_function.graph_replays > 0 and set(runtime.step_function.graphs) <= {1, 2, 4}
+    assert 4 in runtime.step_function.graphs
+    _, weights = plain.load_folder(folder, torch.float64)
+    for rid, tokens in requests.items():
+        expected = toy_plain_logits(tokens, weights, TOY)
+        bound = (3e-5 if dtype == "float32" else 4e-2) * max(1.0, float(expected.abs().max()))
+        assert sorted(got[rid]) == list(range(prompt_lens[rid] - 1, len(tokens)))
+        for position, row in got[rid].items():
+            assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
+    # the scratch slot took the padding rows' writes; no request was ever given it
+    assert runtime.storage.scratch_slot == 3 and float(runtime.storage.states[1][:, 3].abs().max()) > 0
 
 
 # --------------------------------------------------------------------------- a second toy: routing and another position encoding

@@ -58,9 +58,10 @@ def error_bounds(dtype, expected):
     return 3e-2 * max(scale, 1.0)
 
 
-# How much of its bound the bfloat16 path may use before a test fails: what was seen on B200 plus a margin,
-# so that a kernel that starts to round worse is noticed long before it reaches the bound itself.
-BF16_RATIO_CEILING = 0.6
+# How much of its bound a path may use before a test fails.  Seen on B200: at most 0.39 in bfloat16 (batch 8 at
+# Qwen3-1.7B's layer sizes) and 0.22 in float32 (64 rows at those sizes), so a kernel that starts to round worse is
+# noticed long before it reaches the bound itself.
+RATIO_CEILING = 0.5
 
 
 def check_against(request, got, expected_of, dtype, wanted=None):
@@ -75,8 +76,7 @@ def check_against(request, got, expected_of, dtype, wanted=None):
             worst = max(worst, error / bound)
             assert error <= bound, (rid, position, error, bound)
     helpers.note_ratio(request.node.name, worst)
-    if dtype == "bfloat16":
-        assert worst <= BF16_RATIO_CEILING, f"bfloat16 error reached {worst:.2f} of its bound (ceiling {BF16_RATIO_CEILING})"
+    assert worst <= RATIO_CEILING, f"{dtype}: the error reached {worst:.2f} of its bound (ceiling {RATIO_CEILING})"
     return worst
 
 
