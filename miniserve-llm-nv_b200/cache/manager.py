@@ -55,11 +55,32 @@ class StepReservation:
 
 @dataclass(frozen=True)
 class CapacitySnapshot:
+    """What the scheduler plans against: per paged group the pages that are free or could be freed by evicting
+    reusable prefixes, and the free state slots.  The page arithmetic is here, with the cache, so that a group
+    with other needs changes this class and not the scheduler; a model without paged groups fits any plan."""
+
     page_size: int
     total_pages: tuple[int, ...]
     free_pages: tuple[int, ...]
     reclaimable_pages: tuple[int, ...]
     free_slots: int
+
+    def available(self) -> list[int]:
+        """Per paged group: pages a step could get (free now, or held by the prefix cache alone)."""
+        return [free + reclaimable for free, reclaimable in zip(self.free_pages, self.reclaimable_pages)]
+
+    def pages_for(self, start: int, end: int) -> tuple[int, ...]:
+        """Per paged group: new pages a request of ``start`` committed tokens needs to reach ``end``.  (A group
+        with a window needs them as well while the step runs; what the window has passed comes back at commit.)"""
+        ps = self.page_size
+        need = (end + ps - 1) // ps - (start + ps - 1) // ps
+        return tuple(need for _ in self.free_pages)
+
+    def room(self, start: int, available: Sequence[int]) -> int:
+        """The most tokens a request of ``start`` committed tokens can add with ``available`` pages per group."""
+        ps = self.page_size
+        held = (start + ps - 1) // ps
+        return min(((pages + held) * ps - start for pages in available), default=1 << 60)
 
 
 class CacheManager:

@@ -11,6 +11,10 @@
 // values.  The four partial results are merged in warp order.  The order of every sum
 // therefore depends only on the token's own position, not on the batch, the portion or
 // the pages it lies in.
+//
+// Two optional changes of a score s between query position p and key position j, applied in this
+// order before the softmax: a soft cap, s = cap * tanh(s / cap); and a bias that grows with the
+// distance, s += slope[head] * (j - p) (one slope per query head; zero at the query's own key).
 #include "common.cuh"
 
 namespace ms {
@@ -60,7 +64,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
                                                const T* __restrict__ v_pool, const int* __restrict__ block_tables,
                                                int table_stride, const int* __restrict__ request_of_token,
                                                const int* __restrict__ positions, int page_size, int n_q, int n_kv,
-                                               int d, float scale, int window, T* __restrict__ out) {
+                                               int d, float scale, int window, float softcap,
+                                               const float* __restrict__ bias_slopes, T* __restrict__ out) {
   grid_dependency_wait();
   grid_dependency_launch();
   extern __shared__ float smem[];
@@ -78,6 +83,7 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
   for (int c = threadIdx.x; c < d; c += blockDim.x) q_s[c] = to_float(q_row[c]) * scale;
   __syncthreads();
 
+  const float slope = bias_slopes ? bias_slopes[head] : 0.f;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int last_key = pos;  // inclusive
   float m = -INFINITY, l = 0.f;
@@ -96,6 +102,8 @@ __global__ void paged_attention_generic_kernel(const T* __restrict__ q, const T*
       const int page = table[key / page_size];
       row_offset = (((size_t)page * n_kv + kv_head) * page_size + key % page_size) * d;
       score = dot_row(q_s, k_pool + row_offset, d);
+      if (softcap > 0.f) score = softcap * tanhf(score / softcap);
+      score += slope * (float)(key - pos);
     }
     const float block_max = warp_max(score);
     const float new_m = fmaxf(m, block_max);       // finite: every block holds at least one valid key
@@ -148,11 +156,13 @@ using namespace ms;
 // q [n_tokens, n_q, d]; pools of one layer [pages, n_kv, page_size, d]; block_tables
 // [requests, table_stride]; request_of_token, positions [n_tokens]; out [n_tokens, n_q, d].
 // The keys of a token are positions max(0, pos - window + 1) .. pos of its own request
-// (window <= 0: no window); they must already be in the pool.
+// (window <= 0: no window); they must already be in the pool.  softcap <= 0: no soft cap; bias_slopes
+// [n_q] float32 or null.
 MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k_pool, const void* v_pool,
                                          const int* block_tables, int table_stride, const int* request_of_token,
                                          const int* positions, int page_size, int n_q, int n_kv, int d, float scale,
-                                         int window, void* out, int n_tokens, cudaStream_t stream) {
+                                         int window, float softcap, const float* bias_slopes, void* out, int n_tokens,
+                                         cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(d > 0 && d <= 32 * kMaxLanesPerThread, "paged_attention: head size %d outside 1..%d", d,
              32 * kMaxLanesPerThread);
@@ -165,11 +175,12 @@ MS_EXPORT int ms_paged_attention_generic(const void* q, int dtype, const void* k
   if (dtype == MS_F32) {
     ms::launch(paged_attention_generic_kernel<float>, grid, kAttnWarps * 32, smem, stream, 
         (const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, table_stride, request_of_token,
-        positions, page_size, n_q, n_kv, d, scale, window, (float*)out);
+        positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes, (float*)out);
   } else if (dtype == MS_BF16) {
     ms::launch(paged_attention_generic_kernel<__nv_bfloat16>, grid, kAttnWarps * 32, smem, stream, 
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_tables,
-        table_stride, request_of_token, positions, page_size, n_q, n_kv, d, scale, window, (__nv_bfloat16*)out);
+        table_stride, request_of_token, positions, page_size, n_q, n_kv, d, scale, window, softcap, bias_slopes,
+        (__nv_bfloat16*)out);
   } else {
     MS_FAIL("paged_attention: unknown element type code %d", dtype);
   }

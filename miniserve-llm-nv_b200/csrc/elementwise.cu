@@ -7,16 +7,28 @@
 namespace ms {
 
 // ---------------------------------------------------------------- embedding
-// out[n, :] = float(table[token[n], :]); the residual stream is float32.
+// out[n, :] = scale * float(table[token[n], :]); the residual stream is float32.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                                 float* __restrict__ out, int hidden) {
+                                 float* __restrict__ out, int hidden, float scale) {
   grid_dependency_wait();
   grid_dependency_launch();
   const size_t row = blockIdx.x;
   const T* src = table + (size_t)tokens[row] * hidden;
   float* dst = out + row * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_float(src[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = scale * to_float(src[c]);
+}
+
+// ---------------------------------------------------------------- logit transform
+// x = scale * x, then (cap > 0) x = cap * tanh(x / cap), in place on float32.
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t total, float scale, float cap) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  float v = scale * x[i];
+  if (cap > 0.f) v = cap * tanhf(v / cap);
+  x[i] = v;
 }
 
 // ---------------------------------------------------------------- residual add + RMSNorm
@@ -204,11 +216,21 @@ using namespace ms;
   else MS_FAIL("unknown element type code %d", (dtype));
 
 MS_EXPORT int ms_embedding(const int* tokens, const void* table, int dtype, float* out, int n_tokens, int hidden,
-                           cudaStream_t stream) {
+                           float scale, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   MS_REQUIRE(hidden > 0, "embedding: hidden size must be positive, got %d", hidden);
-  MS_DISPATCH(dtype, (ms::launch(embedding_kernel<T>, n_tokens, 256, 0, stream, tokens, (const T*)table, out, hidden)));
+  MS_DISPATCH(dtype, (ms::launch(embedding_kernel<T>, n_tokens, 256, 0, stream, tokens, (const T*)table, out, hidden, scale)));
   MS_CHECK_LAUNCH("embedding");
+  return 0;
+}
+
+// x [total] float32 in place: x = scale * x, then, if cap > 0, x = cap * tanh(x / cap).
+MS_EXPORT int ms_scale_softcap(float* x, long long total, float scale, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const long long blocks = (total + 255) / 256;
+  MS_REQUIRE(blocks < 2147483647LL, "scale_softcap: %lld elements in one launch is too many", total);
+  ms::launch(scale_softcap_kernel, (unsigned)blocks, 256, 0, stream, x, (size_t)total, scale, cap);
+  MS_CHECK_LAUNCH("scale_softcap");
   return 0;
 }
 

@@ -114,12 +114,13 @@ def _report_attention_kernels(model: DecoderModel, dtype: torch.dtype, page_size
             continue
         need = model.cache_groups[plan.group].need
         n_q = getattr(mixer, "num_heads", need.num_kv_heads)
-        names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size)
+        modified = bool(getattr(mixer, "score_softcap", None)) or getattr(mixer, "score_bias_slopes", None) is not None
+        names = kernels.attention_kernels(dtype, need.head_dim, n_q, need.num_kv_heads, page_size, modified)
         chosen.append(dict(group=plan.group, head_dim=need.head_dim, window=need.window, **names))
         slow = dtype == torch.bfloat16 and "general" in names.values()
         log.log(logging.WARNING if slow else logging.INFO,
                 "cache group %d (head size %d, %d/%d heads, pages of %d%s): decode steps on the %s kernel, prompt "
                 "portions on the %s kernel%s", plan.group, need.head_dim, n_q, need.num_kv_heads, page_size,
                 f", window {need.window}" if need.window else "", names["decode"], names["prompt"],
-                " (no tensor-core kernel is built for this head size)" if slow else "")
+                " (no tensor-core kernel is built for this head size or for modified scores)" if slow else "")
     return chosen

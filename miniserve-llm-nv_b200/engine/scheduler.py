@@ -63,8 +63,13 @@ class Scheduler:
         return StepPlan(step_id, tuple(PlanItem(r, start, end, True) for r, start, end in rows), len(rows))
 
     @staticmethod
-    def _pages(start: int, end: int, page_size: int) -> int:
-        return (end + page_size - 1) // page_size - (start + page_size - 1) // page_size
+    def _take(available: list[int], need: Seq[int]) -> bool:
+        """Takes ``need`` pages per group out of ``available`` if every group has them."""
+        if any(n > a for n, a in zip(need, available)):
+            return False
+        for group, n in enumerate(need):
+            available[group] -= n
+        return True
 
     def schedule(self, sequences: Seq[Sequence], capacity: CapacitySnapshot) -> StepPlan:
         step_id = self._next_step
@@ -72,8 +77,7 @@ class Scheduler:
         ordered = sorted((s for s in sequences if not s.done), key=lambda s: (s.arrival, s.request_id))
         token_budget = self.max_num_batched_tokens
         seq_budget = self.max_num_seqs
-        page_size = capacity.page_size
-        free_pages = min((f + r for f, r in zip(capacity.free_pages, capacity.reclaimable_pages)), default=1 << 60)
+        available = capacity.available()        # pages per cache group; the cache says what a portion needs of each
         free_slots = capacity.free_slots
         items: list[PlanItem] = []
 
@@ -86,13 +90,11 @@ class Scheduler:
                 continue
             if seq_budget <= reserve or token_budget <= reserve:
                 break
-            extra = self._pages(seq.computed, seq.computed + 1, page_size)
-            if extra > free_pages:
+            if not self._take(available, capacity.pages_for(seq.computed, seq.computed + 1)):
                 continue
             items.append(PlanItem(seq.request_id, seq.computed, seq.computed + 1, True))
             seq_budget -= 1
             token_budget -= 1
-            free_pages -= extra
 
         for seq in prompts:
             if seq_budget == 0 or token_budget == 0:
@@ -105,21 +107,17 @@ class Scheduler:
                 take = min(take, self.prefill_chunk_size)
             if take <= 0 or take > token_budget:
                 continue
-            if self._pages(seq.computed, seq.computed + take, page_size) > free_pages:
+            if not self._take(available, capacity.pages_for(seq.computed, seq.computed + take)):
                 if not self.enable_chunked_prefill:
                     continue
-                # the longest portion the free pages can hold
-                room = (free_pages + (seq.computed + page_size - 1) // page_size) * page_size - seq.computed
-                take = min(take, room)
-                if take <= 0:
+                take = min(take, capacity.room(seq.computed, available))      # the longest portion the pages can hold
+                if take <= 0 or not self._take(available, capacity.pages_for(seq.computed, seq.computed + take)):
                     continue
-            extra = self._pages(seq.computed, seq.computed + take, page_size)
             items.append(PlanItem(seq.request_id, seq.computed, seq.computed + take, False))
             if seq.status is Status.WAITING:
                 free_slots -= 1
             seq_budget -= 1
             token_budget -= take
-            free_pages -= extra
 
         return StepPlan(step_id, tuple(items), self.max_num_batched_tokens - token_budget)
 

@@ -15,7 +15,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 _library: Optional[ctypes.CDLL] = None
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -93,14 +93,20 @@ def _f(value: float) -> ctypes.c_float:
 # --------------------------------------------------------------------------- memory-bound kernels
 
 
-def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[n] = float32(table[tokens[n]])``; tokens int32 ``[N]``, out float32 ``[N, H]``."""
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """``out[n] = scale * float32(table[tokens[n]])``; tokens int32 ``[N]``, out float32 ``[N, H]``."""
     n, hidden = tokens.numel(), table.shape[1]
     _want(tokens, "tokens", torch.int32)
     _want(table, "table")
     _want(out, "out", torch.float32, (n, hidden))
     _check(library().ms_embedding(_ptr(tokens), _ptr(table), _i(_code(table.dtype)), _ptr(out), _i(n), _i(hidden),
-                                  _stream()))
+                                  _f(scale), _stream()))
+
+
+def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: Optional[float] = None) -> None:
+    """In place on float32 ``x``: ``x *= scale``, then with ``cap``: ``x = cap * tanh(x / cap)``."""
+    _want(x, "x", torch.float32)
+    _check(library().ms_scale_softcap(_ptr(x), ctypes.c_longlong(x.numel()), _f(scale), _f(cap if cap else 0.0), _stream()))
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -197,12 +203,14 @@ def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, paired: bool = False) -> 
 MAX_HEAD_DIM = 512      # of the general attention kernel (attention_generic.cu: 16 output lanes per thread)
 
 
-def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, page_size: int) -> dict:
+def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, page_size: int,
+                      modified_scores: bool = False) -> dict:
     """Which kernel :func:`paged_attention` runs for these sizes: ``{"decode": name, "prompt": name}`` with the
     names ``tcgen05``, ``mma.sync`` and ``general`` (float32 arithmetic, any size; the only one of the float32
-    path, and what bfloat16 falls back to for head sizes the tensor-core kernels are not built for)."""
+    path, and what bfloat16 falls back to for head sizes the tensor-core kernels are not built for and for
+    scores with a soft cap or a distance bias)."""
     lib = library()
-    if dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+    if modified_scores or dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         return {"decode": "general", "prompt": "general"}
     prompt = "mma.sync"
     if USE_TCGEN05_ATTENTION and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(page_size)):
@@ -214,7 +222,8 @@ def attention_kernels(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int, pa
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
                     request_of_token: torch.Tensor, positions: torch.Tensor, query_start: torch.Tensor,
                     context_lens: torch.Tensor, max_query_len: int, max_context_len: int, scale: float,
-                    window: Optional[int], out: torch.Tensor, host_query_start: Optional[list] = None) -> None:
+                    window: Optional[int], out: torch.Tensor, host_query_start: Optional[list] = None,
+                    softcap: Optional[float] = None, bias_slopes: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of every token over its request's paged keys and values.
 
     q, out ``[N, n_q, d]``; pools of one layer ``[pages, n_kv, page_size, d]``; block_tables
@@ -222,6 +231,11 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     context_lens ``[R]`` describe the same batch per request (a request's tokens are the last
     ones of its context).  A token at position p sees keys ``max(0, p - window + 1) .. p`` of
     its own request, which must be in the pool already.
+
+    Score modifiers, both off by default: ``softcap`` turns a scaled score ``s`` into ``softcap * tanh(s /
+    softcap)``; ``bias_slopes`` (float32 ``[n_q]``) adds ``slope[head] * (key position - query position)``
+    after it.  The general kernel implements them; the tensor-core kernels do not, so a call with either
+    runs the general kernel whatever the sizes.
 
     bfloat16 with a head size the tensor-core kernels are built for runs there
     (``max_query_len``/``max_context_len`` are upper bounds used to shape their grids); everything
@@ -245,11 +259,15 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     _want(context_lens, "context_lens", torch.int32, (n_requests,))
     lib = library()
     n_kv = k_pool.shape[1]
-    if q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
+    modified = bool(softcap) or bias_slopes is not None
+    if bias_slopes is not None:
+        _want(bias_slopes, "bias_slopes", torch.float32, (n_q,))
+    if modified or q.dtype != torch.bfloat16 or not lib.ms_attention_mma_supports(_i(head_dim)):
         _check(lib.ms_paged_attention_generic(
             _ptr(q), _i(_code(q.dtype)), _ptr(k_pool), _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]),
             _ptr(request_of_token), _ptr(positions), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim),
-            _f(scale), _i(window if window else 0), _ptr(out), _i(n), _stream()))
+            _f(scale), _i(window if window else 0), _f(softcap if softcap else 0.0), _ptr(bias_slopes), _ptr(out),
+            _i(n), _stream()))
         return
 
     def run(first: int, last: int, longest: int, rows: int) -> None:

@@ -10,11 +10,15 @@ append are one kernel.
 
 All sizes are arguments.  ``window`` limits a query to the last ``window`` keys; ``scale``
 overrides the score scale; ``position`` is a :class:`~.spec.PartSpec` of the position family.
+``score_softcap`` c turns a scaled score s into ``c * tanh(s / c)`` and ``score_bias_slopes`` (one
+number per query head) adds ``slope * (key position - query position)`` to it: position
+encodings that act on the scores instead of on queries and keys.  Either of them selects the
+general attention kernel.
 """
 
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -28,7 +32,9 @@ from .spec import PartSpec
 class Attention(Part):
     def __init__(self, *, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm: bool, eps: float, position: PartSpec, window: Optional[int] = None,
-                 scale: Optional[float] = None, q_name: str = "q_proj.weight", k_name: str = "k_proj.weight",
+                 scale: Optional[float] = None, score_softcap: Optional[float] = None,
+                 score_bias_slopes: Optional[Sequence[float]] = None,
+                 q_name: str = "q_proj.weight", k_name: str = "k_proj.weight",
                  v_name: str = "v_proj.weight", o_name: str = "o_proj.weight", q_norm_name: str = "q_norm.weight",
                  k_norm_name: str = "k_norm.weight") -> None:
         if num_heads % num_kv_heads:
@@ -42,6 +48,11 @@ class Attention(Part):
         self.qk_norm, self.eps = bool(qk_norm), float(eps)
         self.window = window
         self.scale = float(scale) if scale is not None else head_dim ** -0.5
+        self.score_softcap = float(score_softcap) if score_softcap else None
+        if score_bias_slopes is not None and len(score_bias_slopes) != num_heads:
+            raise ValueError(f"{len(score_bias_slopes)} score bias slopes for {num_heads} query heads")
+        self.score_bias_slopes = None if score_bias_slopes is None else tuple(float(s) for s in score_bias_slopes)
+        self._slopes_on_device: Optional[torch.Tensor] = None
         self.position = POSITIONS.build(position, head_dim=head_dim) if "head_dim" not in position.args \
             else POSITIONS.build(position)
         self.names = dict(q=prefix + q_name, k=prefix + k_name, v=prefix + v_name, o=prefix + o_name,
@@ -91,10 +102,12 @@ class Attention(Part):
         else:
             self._append_with_external_position(qkv, slots, ctx, cache, q)
         attended = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
+        if self.score_bias_slopes is not None and self._slopes_on_device is None:
+            self._slopes_on_device = torch.tensor(self.score_bias_slopes, dtype=torch.float32, device=x.device)
         kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
                                 ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
                                 ctx.max_context_len, self.scale, self.window, attended,
-                                ctx.host_query_start or None)
+                                ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
         return out

@@ -1,5 +1,6 @@
 """The decoder assembled from a :class:`~.spec.ModelSpec`: embedding, the layer runs in the
-given order, final norm on the wanted rows, output matrix.  It follows the data flow of
+given order, final norm on the wanted rows, output matrix (with the spec's optional scale of the
+embeddings and scale or soft cap of the logits).  It follows the data flow of
 miniserve/model/qwen3.py:454-496 and 565-591 but computes logits only for the rows that are
 asked for, and knows no architecture: layers, their parts and their order are data.
 """
@@ -108,7 +109,7 @@ class DecoderModel:
         """Runs the step's tokens through all layer runs; returns float32 logits ``[len(logit_rows), vocab]``."""
         spec = self.spec
         residual = torch.empty((ctx.n_tokens, spec.hidden_size), dtype=torch.float32, device=self.device)
-        kernels.embedding(ctx.token_ids, self.embedding, residual)
+        kernels.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
         delta = None
         for index, run in enumerate(spec.order):
             plan = self.run_caches[index]
@@ -120,4 +121,6 @@ class DecoderModel:
             final = torch.empty((n_rows, spec.hidden_size), dtype=self.dtype, device=self.device)
             self.final_norm.add_and_norm(residual, delta, final, rows=ctx.logit_rows)
             kernels.linear(final, self.output_weight, logits)
+            if spec.logit_scale != 1.0 or spec.logit_softcap:
+                kernels.scale_softcap(logits, spec.logit_scale, spec.logit_softcap)
         return logits

@@ -59,3 +59,8 @@ class ModelSpec:
     max_positions: int
     # Names that may be present in a checkpoint without being used (a stored copy of a tied matrix).
     optional_names: Sequence[str] = ()
+    # The frame around the layers: embeddings are multiplied by `embedding_scale` as they enter the residual
+    # stream; logits are multiplied by `logit_scale` and then, with `logit_softcap` c, become c * tanh(logit / c).
+    embedding_scale: float = 1.0
+    logit_scale: float = 1.0
+    logit_softcap: Optional[float] = None

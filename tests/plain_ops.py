@@ -17,8 +17,14 @@ import torch
 import plain_qwen3 as plain
 
 
-def embedding(tokens, table, out):
-    out.copy_(table[tokens.long()].to(out.dtype))
+def scale_softcap(x, scale=1.0, cap=None):
+    x.mul_(scale)
+    if cap:
+        x.copy_(cap * torch.tanh(x / cap))
+
+
+def embedding(tokens, table, out, scale=1.0):
+    out.copy_((scale * table[tokens.long()].double()).to(out.dtype))
 
 
 def add_rmsnorm(residual, delta, weight, eps, out, rows=None):
@@ -104,7 +110,8 @@ def gated_up(x, weight, out):
 
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
-                    max_query_len, max_context_len, scale, window, out, host_query_start=None):
+                    max_query_len, max_context_len, scale, window, out, host_query_start=None, softcap=None,
+                    bias_slopes=None):
     n, n_q, d = q.shape
     n_kv, page_size = k_pool.shape[1], k_pool.shape[2]
     group = n_q // n_kv
@@ -119,6 +126,10 @@ def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions
         v = v_pool[pages, :, offsets, :].double()
         for head in range(n_q):
             scores = (k[:, head // group, :] @ q[token, head].double()) * scale
+            if softcap:
+                scores = softcap * torch.tanh(scores / softcap)
+            if bias_slopes is not None:
+                scores = scores + float(bias_slopes[head]) * (keys - pos).double()
             p = torch.softmax(scores, dim=0)
             out[token, head] = (p @ v[:, head // group, :]).to(out.dtype)
 
@@ -153,6 +164,6 @@ def install(monkeypatch) -> None:
     from miniserve_b200 import kernels
 
     for name in ("embedding", "add_rmsnorm", "rmsnorm", "rope_table", "qk_norm_rope_append", "silu_mul",
-                 "paged_attention", "linear", "gated_linear", "gated_up", "sample"):
+                 "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})

@@ -261,6 +261,46 @@ def test_paged_attention_window_edge(kernels, dtype, query_len, d):
         assert close == visible, (key, visible)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,window,softcap,slopes", [
+    (4, 2, 64, 16, None, 5.0, False), (8, 2, 128, 8, None, None, True), (6, 3, 48, 4, 21, 2.5, True), (2, 1, 24, 16, None, 30.0, True)])
+def test_paged_attention_score_modifiers(kernels, dtype, n_q, n_kv, d, page_size, window, softcap, slopes):
+    """A soft cap on the scores and a bias that grows with the distance between query and key (one slope per
+    query head), which only the general kernel implements: sizes that would otherwise run on tensor cores too."""
+    lengths, query_lens = [1, 37, 130, 200], [1, 5, 1, 64]
+    q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = \
+        _attention_case(dtype, n_q, n_kv, d, page_size, lengths, query_lens, 35)
+    bias = torch.tensor([0.5 ** (1 + h) for h in range(n_q)], dtype=torch.float32).cuda() if slopes else None
+    out = torch.empty_like(q)
+    kernels.paged_attention(q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                            max_ctx, d ** -0.5, window, out, None, softcap, bias)
+    expected = torch.empty(q.shape, dtype=torch.float64)
+    plain_ops.paged_attention(q.cpu(), k_pool.cpu(), v_pool.cpu(), tables.cpu(), request_of_token.cpu(), positions.cpu(),
+                              query_start.cpu(), context_lens.cpu(), max_q, max_ctx, d ** -0.5, window, expected,
+                              None, softcap, None if bias is None else bias.cpu())
+    assert torch.allclose(out.double().cpu(), expected, **tol(dtype)), float((out.double().cpu() - expected).abs().max())
+    plain = torch.empty_like(q)
+    kernels.paged_attention(q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q,
+                            max_ctx, d ** -0.5, window, plain)
+    assert not torch.allclose(out.float(), plain.float(), atol=1e-2)      # the modifiers did change something
+
+
+def test_embedding_scale_and_logit_transform(kernels):
+    table = rand((50, 72), torch.bfloat16, 60)
+    tokens = torch.tensor([3, 49, 0, 3], dtype=torch.int32).cuda()
+    out = torch.empty((4, 72), dtype=torch.float32).cuda()
+    kernels.embedding(tokens, table, out, 8.5)
+    assert torch.equal(out, 8.5 * table[tokens.long()].float())
+    logits = rand((3, 331), torch.float32, 61, 20.0)
+    expected = 30.0 * torch.tanh(0.25 * logits.double() / 30.0)
+    kernels.scale_softcap(logits, 0.25, 30.0)
+    assert torch.allclose(logits.double(), expected, atol=1e-5, rtol=1e-5)
+    only_scaled = rand((2, 17), torch.float32, 62)
+    before = only_scaled.clone()
+    kernels.scale_softcap(only_scaled, 3.0)
+    assert torch.equal(only_scaled, 3.0 * before)
+
+
 @pytest.mark.parametrize("tcgen05", [True, False])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("d,n_q,n_kv,page_size", [(64, 8, 2, 16), (128, 4, 2, 64), (128, 16, 8, 16)])

@@ -607,3 +607,109 @@ def test_toy_architecture_with_routing_and_added_positions(tmp_path, dtype, cutt
         for position, row in got[rid].items():
             assert float((row - expected[position]).abs().max()) <= bound, (rid, position)
     runtime.manager.check_invariants()
+
+
+# --------------------------------------------------------------------------- a third toy: the frame around the layers, and scores with a bias
+
+
+BIASED = dict(architectures=["ToyBiasedForCausalLM"], hidden_size=64, vocab_size=113, heads=4, kv_heads=2, head_dim=32,
+              inter=96, eps=1e-6, embedding_scale=8.0, logit_scale=0.5, logit_softcap=6.0, score_softcap=4.0,
+              slopes=[0.25, 0.125, 0.0625, 0.03125])
+
+
+@dataclass(frozen=True)
+class BiasedConfig:
+    hidden_size: int
+    vocab_size: int
+    heads: int
+    kv_heads: int
+    head_dim: int
+    inter: int
+    eps: float
+    embedding_scale: float
+    logit_scale: float
+    logit_softcap: float
+    score_softcap: float
+    slopes: tuple
+
+    @classmethod
+    def from_dict(cls, data):
+        return cls(**{k: (tuple(data[k]) if k == "slopes" else data[k]) for k in cls.__dataclass_fields__})
+
+
+def register_biased_toy():
+    """An architecture made of the package's own parts only, with options that Qwen3 leaves at their defaults:
+    embeddings scaled as they enter the stream, logits scaled and soft-capped, and an attention without any
+    rotation whose scores are soft-capped and biased by the distance between query and key."""
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200.config import register_architecture
+    from miniserve_b200.parts import LayerRun, LayerSpec, ModelSpec, PartSpec
+
+    def build_spec(config: BiasedConfig):
+        rms = lambda name: PartSpec("rms", dict(name=name, size=config.hidden_size, eps=config.eps))
+        attention = PartSpec("attention", dict(
+            hidden_size=config.hidden_size, num_heads=config.heads, num_kv_heads=config.kv_heads, head_dim=config.head_dim,
+            qk_norm=False, eps=config.eps, position=PartSpec("none"), score_softcap=config.score_softcap,
+            score_bias_slopes=config.slopes))
+        layers = [LayerSpec(f"blocks.{i}.", attention,
+                            PartSpec("gated_mlp", dict(hidden_size=config.hidden_size, intermediate_size=config.inter)),
+                            rms("norm_a.weight"), rms("norm_b.weight")) for i in range(2)]
+        return ModelSpec(vocab_size=config.vocab_size, hidden_size=config.hidden_size, embedding_name="embed.weight",
+                         layers=layers, order=[LayerRun(0), LayerRun(1)], final_norm=rms("final_norm.weight"),
+                         output_name=None, max_positions=1024, embedding_scale=config.embedding_scale,
+                         logit_scale=config.logit_scale, logit_softcap=config.logit_softcap)
+
+    register_architecture("ToyBiasedForCausalLM", BiasedConfig, build_spec)
+
+
+def biased_plain_logits(tokens, w, c):
+    n = len(tokens)
+    heads, kv, d = c["heads"], c["kv_heads"], c["head_dim"]
+    positions = torch.arange(n, dtype=torch.float64)
+    distance = positions[None, :] - positions[:, None]                       # key position - query position
+    causal = distance <= 0
+    x = c["embedding_scale"] * w["embed.weight"][torch.tensor(tokens)]
+    for layer in range(2):
+        prefix = f"blocks.{layer}."
+        h = plain.plain_rmsnorm(x, w[prefix + "norm_a.weight"], c["eps"])
+        q = (h @ w[prefix + "q_proj.weight"].T).view(n, heads, d)
+        k = (h @ w[prefix + "k_proj.weight"].T).view(n, kv, d)
+        v = (h @ w[prefix + "v_proj.weight"].T).view(n, kv, d)
+        attended = torch.zeros(n, heads, d, dtype=torch.float64)
+        for head in range(heads):
+            scores = (q[:, head] @ k[:, head // (heads // kv)].T) * d ** -0.5
+            scores = c["score_softcap"] * torch.tanh(scores / c["score_softcap"]) + c["slopes"][head] * distance
+            scores = scores.masked_fill(~causal, float("-inf"))
+            attended[:, head] = scores.softmax(dim=1) @ v[:, head // (heads // kv)]
+        x = x + attended.reshape(n, -1) @ w[prefix + "o_proj.weight"].T
+        h = plain.plain_rmsnorm(x, w[prefix + "norm_b.weight"], c["eps"])
+        x = x + plain.plain_swiglu(h, w[prefix + "gate_proj.weight"], w[prefix + "up_proj.weight"], w[prefix + "down_proj.weight"])
+    logits = c["logit_scale"] * (plain.plain_rmsnorm(x, w["final_norm.weight"], c["eps"]) @ w["embed.weight"].T)
+    return c["logit_softcap"] * torch.tanh(logits / c["logit_softcap"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("cutting", ["whole", "tail", "mixed"])
+def test_toy_architecture_with_scaled_frame_and_biased_scores(tmp_path, dtype, cutting):
+    """Scaled embeddings, scaled and soft-capped logits (fields of the model's spec), and an attention whose
+    position encoding acts on the scores (a soft cap and a per-head bias by distance, options of the attention
+    part): an architecture registered from here, replayed in three cuttings against plain code above."""
+    from test_replay_gpu import CUTTINGS, build, replay
+
+    register_biased_toy()
+    from miniserve_b200.weights import write_random_model
+
+    folder = write_random_model(tmp_path / "biased", BIASED, seed=21, matrix_std=0.08)
+    requests = {f"t{i}": helpers.random_tokens(BIASED["vocab_size"], n, seed=900 + i) for i, n in enumerate((1, 17, 40, 75))}
+    steps = CUTTINGS[cutting](requests)
+    pages = (helpers.max_live_tokens(steps, granule=16) + 7) // 8
+    runtime = build(folder, dtype, pages, 8)
+    assert runtime.attention_kernels[0]["decode"] == "general"           # modified scores: the general kernel, said at build
+    got = helpers.collect(steps, replay(runtime, steps))
+    _, weights = plain.load_folder(folder, torch.float64)
+    for rid, tokens in requests.items():
+        expected = biased_plain_logits(tokens, weights, BIASED)
+        assert float(expected.abs().max()) > 1.0                          # the soft cap of the logits is in play
+        bound = (3e-5 if dtype == "float32" else 4e-2) * max(1.0, float(expected.abs().max()))
+        for position, row in got[rid].items():
+            assert float((row - expected[position]).abs().max()) <= bound, (rid, position)

@@ -313,3 +313,33 @@ def test_failure_of_a_step_started_ahead():
     assert result.token_ids == expected_tokens([1, 2, 3], produced + 1)      # the pending token was still read
     manager.check_invariants()
     assert not manager.requests and manager.capacity().free_pages == (32,)
+
+
+def test_pages_are_planned_per_cache_group():
+    """A model with a group that keeps every key beside one with a window: the group with a window gives pages
+    back as it goes, so the two have different numbers free, and the scheduler plans against each group's own
+    count (the arithmetic is the cache's: ``CapacitySnapshot.pages_for`` / ``room``)."""
+    from miniserve_b200.parts import StateNeed
+
+    full, windowed = CacheGroup(PagedKVNeed(2, 16, None), 1), CacheGroup(PagedKVNeed(2, 16, 6), 1)
+    manager = CacheManager([full, windowed], page_size=4, num_pages=8, max_seqs=3)
+    scheduler = Scheduler(max_num_seqs=3, max_num_batched_tokens=64, enable_chunked_prefill=True)
+    engine = Engine(manager, scheduler, ScriptedExecutor(), vocab_size=97, max_model_len=64)
+    engine.submit("b", list(range(1, 18)), SamplingParams(max_new_tokens=2), arrival=1)   # 17 tokens: five pages
+    manager.admit("hold")
+    manager.commit(manager.prepare([("hold", 20)]))     # five pages in each group, of which
+    capacity = manager.capacity()
+    assert capacity.free_pages == (3, 6)                # the window has given three back already
+    assert capacity.pages_for(0, 17) == (5, 5) and capacity.room(0, capacity.available()) == 12
+    plan = scheduler.schedule(list(engine.sequences.values()), capacity)
+    assert [(i.request_id, i.start, i.end) for i in plan.items] == [("b", 0, 12)]   # what the fuller group can hold
+    manager.release("hold")
+    manager.check_invariants()
+
+    # a model whose only cache is per-request state has no pages to run out of
+    state_only = CacheManager([CacheGroup(StateNeed((8,)), 2)], page_size=4, num_pages=1, max_seqs=2)
+    snapshot = state_only.capacity()
+    assert snapshot.pages_for(0, 1000) == () and snapshot.room(0, snapshot.available()) >= 1 << 60
+    plan = Scheduler(max_num_seqs=2, max_num_batched_tokens=512).schedule(
+        [Sequence("s", tuple(range(300)), SamplingParams(), 0, 0)], snapshot)
+    assert [(i.start, i.end) for i in plan.items] == [(0, 300)]
