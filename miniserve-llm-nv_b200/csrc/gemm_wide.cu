@@ -23,6 +23,14 @@
 //     projection, and stores silu(gate) * up for the eight features: the activation costs no kernel and no
 //     trip through memory.  (Both factors are rounded to bfloat16 first, as they are where the product and
 //     the activation are separate kernels.)
+//   - a norm folded into the products around it (decode steps of a pre-norm block: product, residual add, RMSNorm,
+//     product).  Residual mode does not store its results: it adds them to the float32 residual stream, stores
+//     x' = bfloat16(residual * w) with the weight w of the norm that follows, and leaves the sum of residual^2 over
+//     its own columns, per token, in a row of `out_partials` (one row per block).  The product that follows reads
+//     x' as its activations and is given those rows: it adds them up in block order, and multiplies its own sums by
+//     1 / sqrt(total / size + eps) per token before it stores them (or applies the activation), which is what the
+//     norm would have done to its input: (x w) / rms(x) W^T = (x w W^T) / rms(x).  Two kernels fewer per layer,
+//     and no block normalises anything twice;
 //   - larger products: a weight with more rows than one wave of such blocks takes runs as several waves of
 //     blocks of eight tiles, or (on request, see persistent_rows) with one block per multiprocessor that walks
 //     group after group of rows through the one ring, its sums meeting in room of their own while the copies
@@ -45,7 +53,19 @@ constexpr int SLOT_TARGET = 16 * 1024;       // a slot is about this large (and 
 constexpr int X_WHOLE_LIMIT = 96 * 1024;     // activations up to this size stay in shared memory whole
 constexpr int X_PART_TARGET = 48 * 1024;     // larger ones pass through two buffers of about this size
 
-enum : int { MODE_PLAIN = 0, MODE_GATED = 1 };
+enum : int { MODE_PLAIN = 0, MODE_GATED = 1, MODE_RESIDUAL = 2 };
+
+// A norm folded into the products around it (see the head of this file).
+struct Fold {
+  const float* in_partials;      // [in_count][X_ROWS], or null: the rows of X are as they should be
+  int in_count;
+  float inv_size, eps;           // 1 / (columns of X), the norm's eps
+  float* residual;               // residual mode: [M, N] float32, updated in place
+  const void* norm_weight;       // [N], of the norm that follows
+  int norm_dtype;
+  __nv_bfloat16* x_next;         // [M, N]
+  float* out_partials;           // [blocks][X_ROWS]
+};
 
 struct Plan {
   int tiles, pieces, slot_bytes, stages, bulk, smem;
@@ -77,6 +97,8 @@ struct Consumer {
   unsigned ring_u32, x_u32, a_offset, b_offset;
   int warp, lane, half;            // half: the even or the odd pieces of a slot
   int* error_flag;
+  float* row_scale;                // [X_ROWS] in shared memory: what a token's sums are multiplied by (folded norm)
+  float* tile_squares;             // [MAX_TILES][X_ROWS] in shared memory: residual mode's sums of squares per tile
 };
 
 // The computing warps' side for blocks of TILES tiles of 16 rows.  For each of the block's groups of rows: the
@@ -88,8 +110,34 @@ struct Consumer {
 // eight.
 template <int TILES, int MODE, typename OutT, bool MANY>
 __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, const Walk& walk, unsigned char* scratch,
-                                        OutT* __restrict__ out, int M, int N) {
+                                        OutT* __restrict__ out, int M, int N, const Fold& fold) {
   constexpr int piece_bytes = TILES * 16 * 128;
+  // A folded norm on the input side: the last computing warp adds up the producing blocks' sums of squares, four
+  // lanes per token, each taking every fourth block in order, then the four meet in a fixed order.  Nobody needs
+  // the result before the sums are stored, so it costs the step nothing.
+  if (fold.in_partials != nullptr && c.warp == COMPUTE_WARPS - 1) {
+    const int token = c.lane & 7, part = c.lane >> 3;
+    float squares = 0.f;
+    for (int b = part; b < fold.in_count; b += 4) squares += __ldcg(fold.in_partials + (size_t)b * X_ROWS + token);
+    squares += __shfl_xor_sync(0xffffffffu, squares, 8);
+    squares += __shfl_xor_sync(0xffffffffu, squares, 16);
+    if (c.lane < X_ROWS) c.row_scale[c.lane] = 1.0f / sqrtf(squares * fold.inv_size + fold.eps);
+  }
+  // Residual mode: what the stored sums are added to is fetched now, while the weights stream
+  float held_x = 0.f, held_y = 0.f, held_z = 0.f, held_w = 0.f, norm_lo = 0.f, norm_hi = 0.f;   // as sum.x .. sum.w below
+  if (MODE == MODE_RESIDUAL && c.warp < TILES) {
+    const int col = ((int)blockIdx.x * TILES + c.warp) * 16 + (c.lane >> 2), t0 = 2 * (c.lane & 3);
+    if (col < N) {
+      norm_lo = load_as_float(fold.norm_weight, fold.norm_dtype, col);
+      if (t0 < M) held_x = __ldcg(fold.residual + (size_t)t0 * N + col);
+      if (t0 + 1 < M) held_y = __ldcg(fold.residual + (size_t)(t0 + 1) * N + col);
+    }
+    if (col + 8 < N) {
+      norm_hi = load_as_float(fold.norm_weight, fold.norm_dtype, col + 8);
+      if (t0 < M) held_z = __ldcg(fold.residual + (size_t)t0 * N + col + 8);
+      if (t0 + 1 < M) held_w = __ldcg(fold.residual + (size_t)(t0 + 1) * N + col + 8);
+    }
+  }
   int stage = 0, x_seen = 0;                               // the ring's next slot; parts of X waited for so far
   unsigned parity = 0u;                                    // of the phase of that slot's barriers
   bool ok = true;
@@ -158,7 +206,35 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
       }
       // sum.x, sum.y: row (lane / 4) of the warp's tile, tokens 2 (lane % 4) and + 1;  sum.z, sum.w: the row eight further
       const int r = c.lane >> 2, t0 = 2 * (c.lane & 3);
-      if (MODE == MODE_GATED) {
+      if (fold.in_partials != nullptr) {            // the folded norm of the input: a factor per token
+        const float s0 = c.row_scale[t0], s1 = c.row_scale[t0 + 1];
+        sum.x *= s0; sum.z *= s0; sum.y *= s1; sum.w *= s1;
+      }
+      if (MODE == MODE_RESIDUAL) {
+        const int col = (group * TILES + c.warp) * 16 + r;
+        float sq0 = 0.f, sq1 = 0.f;                 // of tokens t0 and t0 + 1 over this lane's two columns
+        auto settle = [&](bool live, int token, int cc, float before, float add, float w, float& squares) {
+          if (!live) return;
+          const float v = before + add;
+          fold.residual[(size_t)token * N + cc] = v;
+          fold.x_next[(size_t)token * N + cc] = __float2bfloat16_rn(v * w);
+          squares += v * v;
+        };
+        settle(col < N && t0 < M, t0, col, held_x, sum.x, norm_lo, sq0);
+        settle(col < N && t0 + 1 < M, t0 + 1, col, held_y, sum.y, norm_lo, sq1);
+        settle(col + 8 < N && t0 < M, t0, col + 8, held_z, sum.z, norm_hi, sq0);
+        settle(col + 8 < N && t0 + 1 < M, t0 + 1, col + 8, held_w, sum.w, norm_hi, sq1);
+        // over the tile's sixteen columns (the eight lanes that share lane % 4), in a fixed order
+#pragma unroll
+        for (int o = 4; o <= 16; o <<= 1) {
+          sq0 += __shfl_xor_sync(0xffffffffu, sq0, o);
+          sq1 += __shfl_xor_sync(0xffffffffu, sq1, o);
+        }
+        if (c.lane < 4) {
+          c.tile_squares[c.warp * X_ROWS + 2 * c.lane] = sq0;
+          c.tile_squares[c.warp * X_ROWS + 2 * c.lane + 1] = sq1;
+        }
+      } else if (MODE == MODE_GATED) {
         const int feature = (group * TILES + c.warp) * 8 + r, features = N / 2;
         if (feature < features) {
           if (t0 < M) out[(size_t)t0 * features + feature] = from_float<OutT>(silu_times(round_bf16(sum.x), round_bf16(sum.z)));
@@ -177,6 +253,15 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
         }
       }
     }
+    if (MODE == MODE_RESIDUAL) {                     // the tiles' sums of squares meet, in tile order: one row per block
+      sync_compute_warps();
+      if (c.warp == 0 && c.lane < X_ROWS) {
+        float squares = 0.f;
+#pragma unroll
+        for (int t = 0; t < TILES; ++t) squares += c.tile_squares[t * X_ROWS + c.lane];
+        fold.out_partials[(size_t)blockIdx.x * X_ROWS + c.lane] = squares;
+      }
+    }
   }
 }
 
@@ -185,10 +270,12 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
 template <int MODE, typename OutT, bool MANY>
 __global__ void __launch_bounds__(THREADS)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 OutT* __restrict__ out, int M, int N, int K, const __grid_constant__ Plan plan, int* __restrict__ error_flag) {
+                 OutT* __restrict__ out, int M, int N, int K, const __grid_constant__ Plan plan,
+                 const __grid_constant__ Fold fold, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[MAX_STAGES], empty_bar[MAX_STAGES], x_full[2], x_empty[2];
+  __shared__ float row_scale[X_ROWS], tile_squares[MAX_TILES * X_ROWS];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = plan.stages, slot_bytes = plan.slot_bytes;
@@ -321,18 +408,20 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   c.a_offset = swizzled((lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4));
   c.b_offset = swizzled(lane & 7, 2 * kk + ((lane >> 3) & 1));
   c.error_flag = error_flag;
+  c.row_scale = row_scale;
+  c.tile_squares = tile_squares;
   // a block with one group has read every slot when its sums meet, and they meet in the ring; one with more
   // has copies for the next group on their way by then, and room of its own for the sums
   unsigned char* scratch = plan.scratch_bytes > 0 ? own_scratch : ring;
   switch (plan.tiles) {
-    case 1: compute<1, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    case 2: compute<2, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    case 3: compute<3, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    case 4: compute<4, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    case 5: compute<5, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    case 6: compute<6, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    case 7: compute<7, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
-    default: compute<8, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N); break;
+    case 1: compute<1, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    case 2: compute<2, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    case 3: compute<3, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    case 4: compute<4, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    case 5: compute<5, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    case 6: compute<6, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    case 7: compute<7, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
+    default: compute<8, MODE, OutT, MANY>(c, plan, walk, scratch, out, M, N, fold); break;
   }
 }
 
@@ -433,14 +522,16 @@ static bool persistent_rows() {
 }
 
 template <int MODE, typename OutT>
-int launch(const void* X, const void* W, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
+int launch(const void* X, const void* W, void* out, int M, int N, int K, const Fold& fold, int* error_flag, cudaStream_t stream) {
   Plan plan;
   MS_REQUIRE(plan_for(N, K, smem_budget(), persistent_rows(), &plan), "gemm_wide: an inner size of %d leaves no room for the weight ring", K);
+  MS_REQUIRE(MODE != MODE_RESIDUAL || (plan.groups <= plan.grid && plan.x_parts == 1),
+             "gemm_wide: the residual mode takes weights that one wave of blocks covers, not %d x %d", N, K);
   CUtensorMap map_w, map_x;
   const bool maps_ok = cached_map(&map_w, W, N, K, plan.tiles * 16, plan.bulk ? plan.pieces : 0) && cached_map(&map_x, X, M, K, X_ROWS, plan.bulk ? plan.x_pieces : 0);
   MS_REQUIRE(maps_ok, "gemm_wide: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
   const bool many = plan.groups > plan.grid || plan.x_parts > 1;
-  auto kernel = many ? gemm_wide_kernel<MODE, OutT, true> : gemm_wide_kernel<MODE, OutT, false>;
+  auto kernel = (many && MODE != MODE_RESIDUAL) ? gemm_wide_kernel<MODE, OutT, true> : gemm_wide_kernel<MODE, OutT, false>;
   static bool configured[2] = {false, false};
   if (!configured[many]) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT);
@@ -448,7 +539,7 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int* er
     configured[many] = true;
   }
   cudaError_t e = ms::launch(kernel, dim3(plan.grid), dim3(THREADS), (size_t)plan.smem, stream, map_w, map_x, (OutT*)out, M, N, K,
-                             plan, error_flag);
+                             plan, fold, error_flag);
   if (e != cudaSuccess) MS_FAIL("gemm_wide: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -469,6 +560,12 @@ MS_EXPORT int ms_gemm_wide_supports(int N, int K) {
   return plan.groups <= wide::multiprocessors() ? 2 : 1;
 }
 
+// The number of blocks ms_gemm_wide runs for these sizes (the rows of out_partials in its residual mode); 0: not taken.
+MS_EXPORT int ms_gemm_wide_blocks(int N, int K) {
+  wide::Plan plan;
+  return wide::plan_for(N, K, wide::smem_budget(), wide::persistent_rows(), &plan) ? plan.grid : 0;
+}
+
 // X [M, K], W [N, K] bfloat16 (K a multiple of 8, both 16-byte aligned), M <= 8.
 //   mode 0: out [M, N], bfloat16 (out_dtype 1) or float32 (0);
 //   mode 1: W holds a gated feed-forward's gate and up projections in blocks of sixteen rows (eight gate rows,
@@ -476,19 +573,41 @@ MS_EXPORT int ms_gemm_wide_supports(int N, int K) {
 //           silu(gate) * up.
 // error_flag: one int on the device, zero before the first call; a kernel that gave up waiting writes a
 // non-zero code there (1, 4 copies; 2, 3 products), which the caller checks when it synchronises.
+//
+// A folded norm (see the head of this file).  in_partials [in_count][8] float32 or null: every token's sums are
+// multiplied by 1 / sqrt(sum over the rows of in_partials / K + eps) before they are stored.
+//   mode 2: nothing is stored to `out` (null); residual [M, N] float32 += the product, x_next [M, N] bfloat16 =
+//           residual * norm_weight [N] (float32: norm_dtype 0, bfloat16: 1), out_partials [ms_gemm_wide_blocks(N, K)][8]
+//           float32 = sums of residual^2 over each block's columns; only for weights with ms_gemm_wide_supports == 2.
 MS_EXPORT int ms_gemm_wide(const void* X, const void* W, void* out, int out_dtype, int mode, int M, int N, int K,
-                           int* error_flag, cudaStream_t stream) {
+                           const float* in_partials, int in_count, float eps, float* residual, const void* norm_weight,
+                           int norm_dtype, void* x_next, float* out_partials, int* error_flag, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
+  wide::Fold fold = {};
+  fold.in_partials = in_count > 0 ? in_partials : nullptr;
+  fold.in_count = in_count;
+  fold.inv_size = 1.0f / (float)K;
+  fold.eps = eps;
+  fold.residual = residual;
+  fold.norm_weight = norm_weight;
+  fold.norm_dtype = norm_dtype;
+  fold.x_next = (__nv_bfloat16*)x_next;
+  fold.out_partials = out_partials;
   MS_REQUIRE(M <= wide::X_ROWS, "gemm_wide: %d rows; this kernel takes at most %d", M, wide::X_ROWS);
   MS_REQUIRE(K > 0 && K % 8 == 0, "gemm_wide: inner size %d is not a multiple of 8", K);
   MS_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_wide: operands must be 16-byte aligned");
   MS_REQUIRE(error_flag != nullptr, "gemm_wide: an error flag on the device is required");
   if (mode == wide::MODE_GATED) {
     MS_REQUIRE(N % 16 == 0 && out_dtype == MS_BF16, "gemm_wide: gated mode wants a multiple of 16 rows (%d) and bfloat16 results", N);
-    return wide::launch<wide::MODE_GATED, __nv_bfloat16>(X, W, out, M, N, K, error_flag, stream);
+    return wide::launch<wide::MODE_GATED, __nv_bfloat16>(X, W, out, M, N, K, fold, error_flag, stream);
+  }
+  if (mode == wide::MODE_RESIDUAL) {
+    MS_REQUIRE(residual && norm_weight && x_next && out_partials && (norm_dtype == MS_F32 || norm_dtype == MS_BF16),
+               "gemm_wide: the residual mode needs the residual stream, the following norm's weight, x_next and out_partials");
+    return wide::launch<wide::MODE_RESIDUAL, __nv_bfloat16>(X, W, nullptr, M, N, K, fold, error_flag, stream);
   }
   MS_REQUIRE(mode == wide::MODE_PLAIN, "gemm_wide: unknown mode %d", mode);
-  if (out_dtype == MS_BF16) return wide::launch<wide::MODE_PLAIN, __nv_bfloat16>(X, W, out, M, N, K, error_flag, stream);
-  if (out_dtype == MS_F32) return wide::launch<wide::MODE_PLAIN, float>(X, W, out, M, N, K, error_flag, stream);
+  if (out_dtype == MS_BF16) return wide::launch<wide::MODE_PLAIN, __nv_bfloat16>(X, W, out, M, N, K, fold, error_flag, stream);
+  if (out_dtype == MS_F32) return wide::launch<wide::MODE_PLAIN, float>(X, W, out, M, N, K, fold, error_flag, stream);
   MS_FAIL("gemm_wide: unknown output type code %d", out_dtype);
 }

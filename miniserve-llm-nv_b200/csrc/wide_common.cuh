@@ -1,5 +1,5 @@
-// What the few-row products that stream weights through a TMA ring into mma.sync share (gemm_wide.cu,
-// ffn_fused.cu): fragment loads from 128-byte-swizzled tiles, the gated activation, barriers of the computing
+// What the few-row product that streams weights through a TMA ring into mma.sync is made of (gemm_wide.cu):
+// fragment loads from 128-byte-swizzled tiles, the gated activation, barriers of the computing
 // warps, cached tensor maps.
 #pragma once
 

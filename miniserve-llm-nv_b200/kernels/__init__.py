@@ -15,7 +15,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 _library: Optional[ctypes.CDLL] = None
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -311,8 +311,9 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 # --------------------------------------------------------------------------- matrix products
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[M, N] = x[M, K] @ weight[N, K]^T``.
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: Optional["RowStats"] = None) -> None:
+    """``out[M, N] = x[M, K] @ weight[N, K]^T``.  (``row_stats``: see :func:`linear_wide`; the caller has asked
+    :func:`fold_supported` first.)
 
     float32 operands run through the library's own FFMA kernel (true 32-bit, no tensor-core
     mode).  bfloat16 operands go to cuBLAS through ``torch.mm`` with float32 accumulation;
@@ -322,6 +323,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     n = weight.shape[0]
     if weight.shape[1] != k or tuple(out.shape) != (m, n):
         raise KernelError(f"linear: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if row_stats is not None:
+        linear_wide(x, weight, out, row_stats=row_stats)
+        return
     if x.dtype == torch.float32:
         _want(x, "x", torch.float32)
         _want(weight, "weight", torch.float32)
@@ -567,21 +571,102 @@ def wide_supports(n: int, k: int) -> int:
     return answer
 
 
-def linear_wide(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+class RowStats:
+    """What is still missing from activations whose norm is folded into the products around it: ``x`` holds
+    ``residual * norm weight`` and every row has yet to be divided by the root of its mean square.
+    ``partials [count, 8]`` (float32) holds sums of squares of the residual's rows, one row of partial sums per
+    block of the product that wrote ``x``; the product that reads ``x`` adds them up in order and applies
+    ``1 / sqrt(total / size + eps)`` to its own results."""
+
+    __slots__ = ("partials", "count", "eps")
+
+    def __init__(self, partials: torch.Tensor, count: int, eps: float) -> None:
+        self.partials, self.count, self.eps = partials, count, eps
+
+
+def wide_blocks(n: int, k: int) -> int:
+    """Blocks that :func:`linear_wide` runs for a weight ``[n, k]``: the rows of ``partials`` that
+    :func:`linear_wide_residual` writes."""
+    return int(library().ms_gemm_wide_blocks(_i(n), _i(k)))
+
+
+def _wide_call(x, weight, out, out_code: int, mode: int, m: int, n: int, k: int, row_stats: Optional[RowStats],
+               residual=None, norm_weight=None, x_next=None, out_partials=None) -> None:
+    if row_stats is not None:
+        _want(row_stats.partials, "row_stats.partials", torch.float32)
+        if row_stats.partials.dim() != 2 or row_stats.partials.shape[1] != 8 or row_stats.partials.shape[0] < row_stats.count:
+            raise KernelError(f"row statistics of shape {tuple(row_stats.partials.shape)} for {row_stats.count} blocks")
+    _check(library().ms_gemm_wide(
+        _ptr(x), _ptr(weight), _ptr(out), _i(out_code), _i(mode), _i(m), _i(n), _i(k),
+        _ptr(row_stats.partials if row_stats else None), _i(row_stats.count if row_stats else 0),
+        _f(row_stats.eps if row_stats else 0.0), _ptr(residual), _ptr(norm_weight),
+        _i(_code(norm_weight.dtype) if norm_weight is not None else 0), _ptr(x_next), _ptr(out_partials),
+        _ptr(device_error_flag(x.device)), _stream()))
+
+
+def linear_wide(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+                row_stats: Optional[RowStats] = None) -> None:
     """``out = x @ weight^T`` for up to 8 rows of bfloat16 ``x`` by the library's kernel for weights of many
     rows (no sum across blocks); ``out`` bfloat16 or float32.
 
     ``gated``: ``weight [2 I, K]`` holds a gated feed-forward's two projections in blocks of sixteen rows,
     eight gate rows followed by the up rows of the same features (:func:`interleave_gate_up`), and
-    ``out [M, I]`` bfloat16 receives ``silu(gate) * up``.
+    ``out [M, I]`` bfloat16 receives ``silu(gate) * up``.  ``row_stats``: ``x`` comes from
+    :func:`linear_wide_residual`; its rows' norm is completed on the results (before the activation).
     """
     m, k = x.shape
     n = weight.shape[0]
     _want(x, "x", torch.bfloat16)
     _want(weight, "weight", torch.bfloat16, (n, k))
     _want(out, "out", torch.bfloat16 if gated else None, (m, n // 2 if gated else n))
-    _check(library().ms_gemm_wide(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(1 if gated else 0), _i(m),
-                                  _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
+    _wide_call(x, weight, out, _code(out.dtype), 1 if gated else 0, m, n, k, row_stats)
+
+
+def linear_wide_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
+                         eps: float, x_next: torch.Tensor, partials: torch.Tensor) -> RowStats:
+    """``residual += x @ weight^T`` (float32, in place) for up to 8 rows of bfloat16 ``x``, and the input of
+    whatever follows an RMSNorm of the new residual: ``x_next = bfloat16(residual * norm_weight)`` with the rows'
+    sums of squares left in ``partials`` (float32 ``[>= wide_blocks(N, K), 8]``).  The returned statistics go
+    with ``x_next`` into :func:`linear_wide` or :func:`gated_up`.  Only for weights with ``wide_supports == 2``.
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, (n, k))
+    _want(residual, "residual", torch.float32, (m, n))
+    _want(norm_weight, "norm_weight", None, (n,))
+    _want(x_next, "x_next", torch.bfloat16, (m, n))
+    _want(partials, "partials", torch.float32)
+    blocks = wide_blocks(n, k)
+    if wide_supports(n, k) != 2 or partials.dim() != 2 or partials.shape[1] != 8 or partials.shape[0] < blocks:
+        raise KernelError(f"linear_wide_residual: weight {tuple(weight.shape)} (one wave of blocks only), partials "
+                          f"{tuple(partials.shape)} for {blocks} blocks")
+    _wide_call(x, weight, None, 1, 2, m, n, k, None, residual, norm_weight, x_next, partials)
+    return RowStats(partials, blocks, eps)
+
+
+def fold_supported(rows: int, dtype: torch.dtype, producer: torch.Tensor, consumer: torch.Tensor,
+                   consumer_gated: bool = False) -> bool:
+    """Whether, in a step of ``rows`` rows, an RMSNorm between the product with the weight ``producer`` and the
+    one with ``consumer`` can be folded into the two (:func:`linear_wide_residual`, then ``row_stats``): bfloat16,
+    at most 8 rows, and both weights are ones that :func:`linear_wide` is (or would be) chosen for."""
+    if not FOLD_NORMS or dtype != torch.bfloat16 or not 0 < rows <= SKINNY_MAX_ROWS:
+        return False
+    for weight, gated in ((producer, False), (consumer, consumer_gated)):
+        n, k = weight.shape
+        if k % 8 or wide_supports(n, k) != 2:
+            return False
+        key = (torch.device(weight.device).index or 0, n, k)
+        if FEW_ROWS_KERNEL:
+            chosen = FEW_ROWS_KERNEL
+        else:
+            chosen = (_gated_choices if gated else _linear_choices).get(key, "wide")    # not measured yet: the rule says wide
+        if chosen != "wide":
+            return False
+    return True
+
+
+FOLD_NORMS = __import__("os").environ.get("MINISERVE_B200_FOLD_NORMS", "1") == "1"
 
 
 GATE_UP_BLOCK = 8    # rows of the gate projection beside as many of the up projection, for linear_wide(gated=True)
@@ -599,8 +684,9 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 WIDE_GATED_MIN_ROWS = 8192     # of the paired weight: the rule when nothing was measured
 
 
-def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: Optional[RowStats] = None) -> None:
     """``out[M, I] = silu(x @ gate^T) * (x @ up^T)`` with ``weight = interleave_gate_up(gate, up)``.
+    (``row_stats``: see :func:`linear_wide`; the caller has asked :func:`fold_supported` first.)
 
     Few rows of bfloat16 go through :func:`linear_wide`, which applies the activation as it stores, where that
     is faster than the product (:func:`linear`) followed by :func:`silu_mul`: measured once per weight shape
@@ -609,6 +695,9 @@ def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
     m, k = x.shape
     two_i = weight.shape[0]
     _want(out, "out", x.dtype, (m, two_i // 2))
+    if row_stats is not None:
+        linear_wide(x, weight, out, gated=True, row_stats=row_stats)
+        return
     if x.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and _gated_choice(x, weight) == "wide":
         linear_wide(x, weight, out, gated=True)
         return

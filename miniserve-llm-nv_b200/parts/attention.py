@@ -23,7 +23,7 @@ from typing import Optional, Sequence
 import torch
 
 from .. import kernels
-from .base import POSITIONS, PagedKVNeed, ParamSpec, Part, register_mixer
+from .base import POSITIONS, FoldedInput, NormFold, PagedKVNeed, ParamSpec, Part, register_mixer
 from .context import PagedKVView, StepContext
 from .spec import PartSpec
 
@@ -86,12 +86,24 @@ class Attention(Part):
                 self.q_norm_weight = self.q_norm_weight.float()
                 self.k_norm_weight = self.k_norm_weight.float()
 
+    # ------------------------------------------------------------------ norms folded into the projections
+    def fold_input_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        return self.qkv_weight
+
+    def fold_output_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        return self.o_weight
+
     # ------------------------------------------------------------------ work
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: PagedKVView) -> torch.Tensor:
+    def forward(self, x, ctx: StepContext, cache: PagedKVView, fold: Optional[NormFold] = None):
+        """``x``: the normed input, or a :class:`FoldedInput`.  With ``fold`` the output projection adds into the
+        residual stream and a :class:`FoldedInput` for the part behind the following norm is returned."""
+        stats = None
+        if isinstance(x, FoldedInput):
+            x, stats = x.x, x.stats
         n, d = x.shape[0], self.head_dim
         n_q, n_kv = self.num_heads, self.num_kv_heads
         qkv = torch.empty((n, (n_q + 2 * n_kv) * d), dtype=x.dtype, device=x.device)
-        kernels.linear(x, self.qkv_weight, qkv)
+        kernels.linear(x, self.qkv_weight, qkv, row_stats=stats)
         q = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
         slots = cache.slots if cache.writable else torch.full_like(cache.slots, -1)
         fused = self.position.fused_args(ctx)
@@ -109,6 +121,11 @@ class Attention(Part):
                                 ctx.max_context_len, self.scale, self.window, attended,
                                 ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
+        if fold is not None:
+            partials = torch.empty((kernels.wide_blocks(*self.o_weight.shape), 8), dtype=torch.float32, device=x.device)
+            stats = kernels.linear_wide_residual(attended.view(n, n_q * d), self.o_weight, fold.residual, fold.weight,
+                                                 fold.eps, out, partials)
+            return FoldedInput(out, stats)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
         return out
 

@@ -19,6 +19,13 @@ block           ``forward(residual, delta, ctx, cache) -> delta``: arranges the 
 A new part is a class registered under a name with ``register_norm`` / ``register_position``
 / ``register_mixer`` / ``register_feed_forward`` / ``register_block``; an architecture then
 names it in its :class:`~.spec.PartSpec`.
+
+Optional, for speed in steps of few rows: a norm between two matrix products can be *folded* into
+them (:class:`NormFold`, :class:`FoldedInput`).  A norm offers it with ``fold()``, a mixer or
+feed-forward with ``fold_output_weight(ctx)`` (its last product can add into the residual stream
+and prepare the next part's input) and ``fold_input_weight(ctx)`` (its first product can take such
+an input); a block uses the fold only where the norm and both neighbours offer it and
+``kernels.fold_supported`` agrees, and parts that offer none of this are run as before.
 """
 
 from __future__ import annotations
@@ -58,6 +65,26 @@ class StateNeed:
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class NormFold:
+    """Handed to a mixer or feed-forward as ``fold=``: instead of returning its output, its last product adds it
+    into ``residual`` (float32, in place) and prepares the input of the part behind the norm with ``weight`` and
+    ``eps`` (``kernels.linear_wide_residual``).  The part then returns a :class:`FoldedInput`."""
+
+    residual: torch.Tensor
+    weight: torch.Tensor
+    eps: float
+
+
+@dataclass
+class FoldedInput:
+    """What a part receives as ``x`` where the norm before it was folded: ``x = residual * norm weight`` and the
+    statistics that its first product completes the norm with (``kernels.RowStats``)."""
+
+    x: torch.Tensor
+    stats: Any
 
 
 class Part:

@@ -11,7 +11,7 @@ from typing import Optional
 import torch
 
 from .. import kernels
-from .base import ParamSpec, Part, register_feed_forward
+from .base import FoldedInput, NormFold, ParamSpec, Part, register_feed_forward
 from .context import StepContext
 
 
@@ -42,12 +42,32 @@ class GatedMLP(Part):
             self.gate_up_weight = torch.cat([gate, up], dim=0).contiguous()
         self.down_weight = tensors[self.names["down"]]
 
-    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+    # norms folded into the projections (the gate/up weight only in its interleaved form: the product that
+    # completes the norm is the one that applies the activation)
+    fold_input_gated = True
+
+    def fold_input_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        return self.gate_up_weight if self.paired else None
+
+    def fold_output_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        return self.down_weight if self.paired else None
+
+    def forward(self, x, ctx: StepContext, fold: Optional[NormFold] = None):
+        """``x``: the normed input, or a :class:`FoldedInput`.  With ``fold`` the down projection adds into the
+        residual stream and a :class:`FoldedInput` for the part behind the following norm is returned."""
+        stats = None
+        if isinstance(x, FoldedInput):
+            x, stats = x.x, x.stats
         n = x.shape[0]
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
         if self.paired:
             hidden = torch.empty((n, self.intermediate_size), dtype=x.dtype, device=x.device)
-            kernels.gated_up(x, self.gate_up_weight, hidden)
+            kernels.gated_up(x, self.gate_up_weight, hidden, row_stats=stats)
+            if fold is not None:
+                partials = torch.empty((kernels.wide_blocks(*self.down_weight.shape), 8), dtype=torch.float32, device=x.device)
+                stats = kernels.linear_wide_residual(hidden, self.down_weight, fold.residual, fold.weight, fold.eps, out,
+                                                     partials)
+                return FoldedInput(out, stats)
             kernels.linear(hidden, self.down_weight, out)
         else:
             gate_up = torch.empty((n, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)

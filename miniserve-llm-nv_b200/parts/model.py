@@ -110,11 +110,16 @@ class DecoderModel:
         spec = self.spec
         residual = torch.empty((ctx.n_tokens, spec.hidden_size), dtype=torch.float32, device=self.device)
         kernels.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
-        delta = None
+        delta = None            # what a block hands to the next: see parts.block
         for index, run in enumerate(spec.order):
             plan = self.run_caches[index]
             cache = None if plan is None else storage.run_view(plan, ctx)
-            delta = self.blocks[run.layer].forward(residual, delta, ctx, cache)
+            block = self.blocks[run.layer]
+            if getattr(block, "takes_next_block", False):
+                following = self.blocks[spec.order[index + 1].layer] if index + 1 < len(spec.order) else None
+                delta = block.forward(residual, delta, ctx, cache, following)
+            else:
+                delta = block.forward(residual, delta, ctx, cache)
         n_rows = ctx.logit_rows.numel()
         logits = torch.empty((n_rows, spec.vocab_size), dtype=torch.float32, device=self.device)
         if n_rows:

@@ -33,6 +33,10 @@ class RMSNorm(Part):
         kernels.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)
         return out
 
+    def fold(self) -> tuple[torch.Tensor, float]:
+        """(weight, eps): all that the products around this norm need to carry it out between them."""
+        return self.weight, self.eps
+
     def norm(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """Norm over the last dim of ``x`` (any leading shape) without a residual."""
         kernels.rmsnorm(x, self.weight, self.eps, out)

@@ -104,9 +104,32 @@ def silu_mul(gate_up, out, paired=False):
     out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
 
-def gated_up(x, weight, out):
-    gate_up = (x.double() @ weight.double().T).to(x.dtype)
-    silu_mul(gate_up, out, paired=True)
+def _row_factor(row_stats, size):
+    """1 / rms of every row from the partial sums of squares that a folded norm left (kernels.RowStats)."""
+    total = row_stats.partials[:row_stats.count].double().sum(dim=0)
+    return 1.0 / torch.sqrt(total / size + row_stats.eps)
+
+
+def gated_up(x, weight, out, row_stats=None):
+    gate_up = x.double() @ weight.double().T
+    if row_stats is not None:
+        gate_up = gate_up * _row_factor(row_stats, x.shape[1])[:x.shape[0], None]
+    silu_mul(gate_up.to(x.dtype), out, paired=True)
+
+
+FOLD_BLOCKS = 3     # the plain stand-in leaves its sums of squares in this many rows, as a kernel of three blocks would
+
+
+def linear_wide_residual(x, weight, residual, norm_weight, eps, x_next, partials):
+    import miniserve_b200  # noqa: F401
+    from miniserve_b200 import kernels
+
+    residual += (x.double() @ weight.double().T).to(residual.dtype)
+    x_next.copy_((residual.double() * norm_weight.double()).to(x_next.dtype))
+    partials.zero_()
+    for block, columns in enumerate(torch.arange(residual.shape[1]).chunk(FOLD_BLOCKS)):
+        partials[block, :residual.shape[0]] = residual[:, columns].double().pow(2).sum(dim=1).to(partials.dtype)
+    return kernels.RowStats(partials, FOLD_BLOCKS, eps)
 
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
@@ -134,8 +157,11 @@ def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions
             out[token, head] = (p @ v[:, head // group, :]).to(out.dtype)
 
 
-def linear(x, weight, out):
-    out.copy_((x.double() @ weight.double().T).to(out.dtype))
+def linear(x, weight, out, row_stats=None):
+    product = x.double() @ weight.double().T
+    if row_stats is not None:
+        product = product * _row_factor(row_stats, x.shape[1])[:x.shape[0], None]
+    out.copy_(product.to(out.dtype))
 
 
 def gated_linear(gate_up, weight, out):
@@ -167,3 +193,7 @@ def install(monkeypatch) -> None:
                  "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
+    # norms folded into the products around them: offered for steps of up to eight rows, as on the device
+    monkeypatch.setattr(kernels, "linear_wide_residual", linear_wide_residual)
+    monkeypatch.setattr(kernels, "wide_blocks", lambda n, k: FOLD_BLOCKS)
+    monkeypatch.setattr(kernels, "fold_supported", lambda rows, dtype, producer, consumer, gated=False: 0 < rows <= 8)

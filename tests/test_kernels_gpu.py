@@ -464,6 +464,56 @@ def test_linear_wide_blocks_that_walk_many_groups(kernels, monkeypatch, m, n, k)
     assert torch.equal(outs["0"], outs["1"])        # the same sums in the same order either way
 
 
+@pytest.mark.parametrize("norm_dtype", DTYPES)
+@pytest.mark.parametrize("m,hidden,k,n_next,gated", [
+    (8, 2048, 2048, 4096, False), (1, 2048, 6144, 12288, True), (5, 1040, 200, 528, False), (3, 2064, 4096, 4128, True),
+    (8, 72, 64, 48, False), (2, 48, 64, 32, True)])
+def test_norm_folded_into_the_products_around_it(kernels, norm_dtype, m, hidden, k, n_next, gated):
+    """product -> residual add -> RMSNorm -> product as two kernels: the first adds into the float32 stream, writes
+    residual * norm weight and its blocks' sums of squares; the second divides its results by the rows' root mean
+    square (before the activation, in its gated form).  Against the four steps in float64; sizes with one to
+    eight tiles per block, ragged columns, one to eight rows; and a row alone gives the same bits as in a batch."""
+    eps = 1e-5
+    x, w = rand((m, k), torch.bfloat16, 80, 0.5), rand((hidden, k), torch.bfloat16, 81, 0.1)
+    residual0 = rand((m, hidden), torch.float32, 82, 2.0)
+    norm_w = (1 + rand((hidden,), torch.float32, 83, 0.1)).to(norm_dtype)
+    w_next = rand((n_next, hidden), torch.bfloat16, 84, 0.05)
+    if gated:
+        w_next = kernels.interleave_gate_up(w_next[:n_next // 2].contiguous(), w_next[n_next // 2:].contiguous())
+
+    def run(x_rows, residual_rows):
+        rows = x_rows.shape[0]
+        residual = residual_rows.clone()
+        x_next = torch.empty((rows, hidden), dtype=torch.bfloat16).cuda()
+        partials = torch.full((kernels.wide_blocks(hidden, k), 8), float("nan"), dtype=torch.float32).cuda()
+        stats = kernels.linear_wide_residual(x_rows, w, residual, norm_w, eps, x_next, partials)
+        out = torch.empty((rows, n_next // 2 if gated else n_next), dtype=torch.bfloat16).cuda()
+        (kernels.gated_up if gated else kernels.linear)(x_next, w_next, out, row_stats=stats)
+        kernels.check_device_errors(x.device)
+        return residual, x_next, partials, out
+
+    assert kernels.fold_supported(m, torch.bfloat16, w, w_next, gated)
+    assert not kernels.fold_supported(9, torch.bfloat16, w, w_next, gated) and not kernels.fold_supported(m, torch.float32, w, w_next, gated)
+    residual, x_next, partials, out = run(x, residual0)
+    expected_residual = residual0.double() + x.double() @ w.double().T
+    assert torch.allclose(residual.double(), expected_residual, atol=1e-4, rtol=1e-5)
+    assert torch.allclose(x_next.double(), expected_residual * norm_w.double(), atol=1e-2, rtol=1e-2)
+    squares = partials[:kernels.wide_blocks(hidden, k), :m].double().sum(dim=0)
+    assert torch.allclose(squares, expected_residual.pow(2).sum(dim=1), rtol=1e-5)
+    normed = (expected_residual * torch.rsqrt(expected_residual.pow(2).mean(dim=1, keepdim=True) + eps) * norm_w.double())
+    product = normed @ w_next.double().T
+    if gated:
+        product = product.bfloat16().double()
+        inter = n_next // 2
+        paired = product.view(m, inter // 8, 2, 8)
+        g, u = paired[:, :, 0].reshape(m, inter), paired[:, :, 1].reshape(m, inter)
+        product = g * torch.sigmoid(g) * u
+    assert torch.allclose(out.double(), product, atol=2e-2 * max(1.0, float(product.abs().max())), rtol=2e-2)
+    row = m // 2
+    alone = run(x[row:row + 1].contiguous(), residual0[row:row + 1].contiguous())
+    assert torch.equal(alone[0][0], residual[row]) and torch.equal(alone[1][0], x_next[row]) and torch.equal(alone[3][0], out[row])
+
+
 def test_linear_wide_refusals(kernels):
     x, w = rand((9, 64), torch.bfloat16, 58), rand((32, 64), torch.bfloat16, 59)
     with pytest.raises(kernels.KernelError, match="at most 8"):
