@@ -1,0 +1,48 @@
+// What the mma.sync attention kernels share: asynchronous 16-byte copies, ldmatrix and mma.m16n8k16 wrappers,
+// and the swizzled layout of their shared-memory tiles (attention_mma.cu, attention_decode.cu).
+#pragma once
+
+#include "common.cuh"
+
+namespace ms {
+
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // zero-fills the 16 bytes when not valid
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_addr(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Shared-memory tiles are [rows][D] bfloat16 with the 16-byte chunks of a row XOR-swizzled by
+// the row index, so that ldmatrix reads eight rows without bank conflicts.
+// A row of D elements has D / 8 chunks; the XOR mask never leaves the row: rows of 128 bytes or
+// more use the low three row bits, 64-byte rows (D = 32) the row bits 1..2, so that in both cases
+// eight consecutive rows land in eight different 16-byte bank groups.
+template <int D> __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat16* base, int row, int chunk) {
+  static_assert(D % 32 == 0, "head size must be a multiple of 32 for this kernel");
+  constexpr int CHUNKS = D / 8;
+  const int mask = CHUNKS >= 8 ? (row & 7) : ((row >> 1) & (CHUNKS - 1));
+  return base + row * D + ((chunk ^ mask) << 3);
+}
+
+}  // namespace ms

@@ -135,6 +135,34 @@ def test_qk_norm_rope_append(kernels, dtype, n_q, n_kv, d, page_size, rotary, in
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,n", [(16, 8, 128, 64, 600), (8, 2, 64, 16, 1500), (4, 4, 32, 8, 1377), (3, 1, 16, 4, 3300)])
+def test_qk_norm_rope_append_of_many_tokens(kernels, dtype, n_q, n_kv, d, page_size, n):
+    """Prompt portions: thousands of (token, head) pairs, a number of them that is no multiple of what a block
+    takes, tokens without a slot, and every head size with a power-of-two number of lanes."""
+    pages = (n + page_size - 1) // page_size + 2
+    qkv = rand((n, (n_q + 2 * n_kv) * d), dtype, 17)
+    q_w, k_w = (1 + rand((d,), torch.float32, 18, 0.1)).to(dtype), (1 + rand((d,), torch.float32, 19, 0.1)).to(dtype)
+    g = torch.Generator().manual_seed(20)
+    positions = torch.randint(0, 5000, (n,), generator=g).to(torch.int32).cuda()
+    slots = torch.randperm(pages * page_size, generator=g)[:n].to(torch.int32)
+    slots[::97] = -1
+    slots = slots.cuda()
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+    cos_sin = torch.empty((n, d // 2, 2), dtype=torch.float32).cuda()
+    kernels.rope_table(positions, inv_freq, cos_sin)
+    k_pool = torch.zeros((pages, n_kv, page_size, d), dtype=dtype).cuda()
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty((n, n_q, d), dtype=dtype).cuda()
+    kernels.qk_norm_rope_append(qkv, slots, q_w, k_w, 1e-6, cos_sin, d, False, k_pool, v_pool, n_q, n_kv, d, q_out)
+    ek, ev = torch.zeros(k_pool.shape, dtype=torch.float64).cuda(), torch.zeros(k_pool.shape, dtype=torch.float64).cuda()
+    eq = torch.empty(q_out.shape, dtype=torch.float64).cuda()
+    plain_ops.qk_norm_rope_append(qkv, slots, q_w, k_w, 1e-6, cos_sin, d, False, ek, ev, n_q, n_kv, d, eq)
+    assert torch.allclose(q_out.double(), eq, **tol(dtype))
+    assert torch.allclose(k_pool.double(), ek, **tol(dtype))
+    assert torch.equal(v_pool.double(), ev)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("inter,paired", [(1, False), (200, False), (224, False), (6144, False), (8, True), (200, True), (6144, True)])
 def test_silu_mul(kernels, dtype, inter, paired):
     gate_up = rand((5, 2 * inter), dtype, 11, 3.0)
