@@ -9,6 +9,7 @@ built or loaded, raises.
 from __future__ import annotations
 
 import ctypes
+import logging
 from typing import Optional
 
 import torch
@@ -16,6 +17,7 @@ import torch
 from . import build
 
 ABI_VERSION = 4
+log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -458,6 +460,8 @@ def _few_rows_choice(x: torch.Tensor, weight: torch.Tensor, m: int) -> str:
         if not LINEAR_TUNING or torch.cuda.is_current_stream_capturing():
             return _few_rows_rule(x.device, m, n, k)
         choice = _linear_choices[key] = _measure_few_rows(weight)
+        log.info("products of up to %d rows with a %d x %d weight run the %s kernel (measured, us: %s)", SKINNY_MAX_ROWS, n, k,
+                 choice, _choice_times.get(key))
     return choice
 
 
@@ -718,6 +722,9 @@ def _gated_choice(x: torch.Tensor, weight: torch.Tensor) -> str:
             return "wide" if fits == 2 and n >= WIDE_GATED_MIN_ROWS else "separate"
         else:
             choice = _gated_choices[key] = _measure_gated(weight)
+            log.info("gated products of up to %d rows with a %d x %d weight run %s (measured, us: %s)", SKINNY_MAX_ROWS, n, k,
+                     "the kernel that applies the activation" if choice == "wide" else "a plain product and the activation kernel",
+                     _choice_times.get(key + ("gated",)))
     return choice
 
 
