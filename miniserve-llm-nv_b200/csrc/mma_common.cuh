@@ -1,5 +1,6 @@
 // What the mma.sync attention kernels share: asynchronous 16-byte copies, ldmatrix and mma.m16n8k16 wrappers,
-// and the swizzled layout of their shared-memory tiles (attention_mma.cu, attention_decode.cu).
+// the swizzled layout of their shared-memory tiles, and the kernel that merges the splits of the keys
+// (attention_mma.cu, attention_decode.cu).
 #pragma once
 
 #include "common.cuh"
@@ -43,6 +44,57 @@ template <int D> __device__ __forceinline__ __nv_bfloat16* tile_ptr(__nv_bfloat1
   constexpr int CHUNKS = D / 8;
   const int mask = CHUNKS >= 8 ? (row & 7) : ((row >> 1) & (CHUNKS - 1));
   return base + row * D + ((chunk ^ mask) << 3);
+}
+
+// Merges the splits of one (token, head): out = sum_s w_s O_s / sum_s w_s with w_s = 2^(lse_s - max lse).
+// One block of four warps per (token, head).  Warp w takes the splits w, w + 4, ... (at most 64 splits, so
+// at most 16 each) and requests all of their partial results at once, before it reads the splits' weights:
+// the merge then costs one trip to the L2 cache, not one per group of splits.  Lane s of every warp holds the
+// weight of split s and s + 32; the four warps' sums are added in warp order through shared memory.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                         __nv_bfloat16* __restrict__ out, int num_splits, int n_items) {
+  grid_dependency_wait();
+  grid_dependency_launch();
+  __shared__ float warp_acc[4][D];
+  const int item = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float* base = part_o + (size_t)item * num_splits * D;
+  float v[16][D / 32];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int s = warp + 4 * j;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) v[j][i] = s < num_splits ? __ldcg(base + (size_t)s * D + lane + 32 * i) : 0.f;
+  }
+  const float* lse = part_lse + (size_t)item * num_splits;
+  const float lse_a = lane < num_splits ? __ldcg(lse + lane) : -INFINITY;
+  const float lse_b = lane + 32 < num_splits ? __ldcg(lse + lane + 32) : -INFINITY;
+  const float m = warp_max(fmaxf(lse_a, lse_b));
+  const float w_a = lse_a == -INFINITY ? 0.f : exp2f(lse_a - m);
+  const float w_b = lse_b == -INFINITY ? 0.f : exp2f(lse_b - m);
+  const float total = warp_sum(w_a + w_b);
+  float acc[D / 32] = {};
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int s = warp + 4 * j;                      // (a split without keys has weight 0: its buffer is not added)
+    const float w = __shfl_sync(0xffffffffu, s < 32 ? w_a : w_b, s & 31);
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] += (s < num_splits && w != 0.f) ? w * v[j][i] : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) warp_acc[warp][lane + 32 * i] = acc[i];
+  __syncthreads();
+  if (warp == 0) {
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      const int c = lane + 32 * i;
+      const float sum = ((warp_acc[0][c] + warp_acc[1][c]) + warp_acc[2][c]) + warp_acc[3][c];
+      out[(size_t)item * D + c] = __float2bfloat16_rn(sum * inv);
+    }
+  }
 }
 
 }  // namespace ms

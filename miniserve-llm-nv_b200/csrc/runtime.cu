@@ -21,7 +21,7 @@ MS_EXPORT const char* ms_last_error() { return ms::error_buffer(); }
 
 // Bumped whenever an exported signature changes; the bindings refuse a library that
 // reports another number.
-MS_EXPORT int ms_abi_version() { return 4; }
+MS_EXPORT int ms_abi_version() { return 5; }
 
 // 1: kernels are launched as programmatic dependents (default); 0: plain stream order.
 MS_EXPORT void ms_set_dependent_launch(int enabled) { ms::g_dependent_launch = enabled ? 1 : 0; }

@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 log = logging.getLogger("miniserve_b200")
 _library: Optional[ctypes.CDLL] = None
 
@@ -308,6 +308,72 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         run(leading_single, n_requests, max_query_len, n)
     else:
         run(0, n_requests, max_query_len, n)
+
+
+FUSED_DECODE_ATTENTION = __import__("os").environ.get("MINISERVE_B200_FUSED_DECODE_ATTENTION", "1") == "1"
+
+
+# Steps of this many requests run :func:`decode_attention_fused` where it takes the sizes.  Measured at Qwen3-1.7B
+# sizes, context 4,096 (ms per step with / without): 1 request 1.341 / 1.330, 2: 1.370 / 1.366, 4: 1.490 / 1.549,
+# 8: 1.731 / 1.801, 16: 2.807 / 2.789, 64: 6.441 / 6.371.  With one or two requests there are few blocks and each
+# repeats the queries' norm and rotation; with many the kernel's larger register count costs residency.
+FUSED_DECODE_ROWS = (3, 8)
+
+
+def decode_attention_fused_supported(dtype: torch.dtype, head_dim: int, n_q: int, n_kv: int) -> bool:
+    """Whether :func:`decode_attention_fused` takes these sizes (bfloat16, head size 64 or 128, at most 16
+    query heads per key/value head); MINISERVE_B200_FUSED_DECODE_ATTENTION=0 turns it off."""
+    return bool(FUSED_DECODE_ATTENTION and dtype == torch.bfloat16
+                and library().ms_attention_decode_fused_supports(_i(head_dim), _i(n_q), _i(n_kv)))
+
+
+def decode_attention_fused_preferred(rows: int) -> bool:
+    """Whether a step of ``rows`` single tokens is faster with :func:`decode_attention_fused` (see FUSED_DECODE_ROWS)."""
+    return FUSED_DECODE_ROWS[0] <= rows <= FUSED_DECODE_ROWS[1]
+
+
+def decode_attention_fused(qkv: torch.Tensor, slots: torch.Tensor, q_weight: Optional[torch.Tensor],
+                           k_weight: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                           k_pool: torch.Tensor, v_pool: torch.Tensor, block_tables: torch.Tensor,
+                           query_start: torch.Tensor, context_lens: torch.Tensor, max_context_len: int, scale: float,
+                           window: Optional[int], n_q: int, n_kv: int, head_dim: int, out: torch.Tensor) -> None:
+    """A decode step's attention for requests of ONE new token each, from the projection's output: what
+    :func:`qk_norm_rope_append` followed by :func:`paged_attention` computes (per-head RMSNorm of q and k,
+    half-split rotation over the whole head, the append of k and v at ``slots``, attention over the cache with the
+    keys split over many blocks, and the merge of the splits), with the first of the three kernels folded into
+    the second.  Arguments as there; ``cos_sin`` float32 ``[N, d / 2, 2]`` or None; ``max_context_len`` an upper
+    bound that the split count is derived from."""
+    n = qkv.shape[0]
+    _want(qkv, "qkv", torch.bfloat16, (n, (n_q + 2 * n_kv) * head_dim))
+    _want(slots, "slots", torch.int32, (n,))
+    _want(k_pool, "k_pool", torch.bfloat16)
+    _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    if k_pool.dim() != 4 or k_pool.shape[1] != n_kv or k_pool.shape[3] != head_dim:
+        raise KernelError(f"pool shape {tuple(k_pool.shape)} is not [pages, {n_kv}, page_size, {head_dim}]")
+    _want(out, "out", torch.bfloat16, (n, n_q, head_dim))
+    _want(block_tables, "block_tables", torch.int32)
+    _want(query_start, "query_start", torch.int32, (n + 1,))
+    _want(context_lens, "context_lens", torch.int32, (n,))
+    weight_code = 0
+    for name, weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if weight is not None:
+            _want(weight, name, None, (head_dim,))
+            weight_code = _code(weight.dtype)
+    if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+        raise KernelError("q and k norm weights must share one element type")
+    if cos_sin is not None:
+        _want(cos_sin, "cos_sin", torch.float32, (n, head_dim // 2, 2))
+    lib = library()
+    splits = lib.ms_attention_decode_fused_splits(_i(head_dim), _i(n), _i(n_kv), _i(max_context_len))
+    part_o = part_lse = None
+    if splits > 1:
+        part_o = torch.empty((n * n_q * splits, head_dim), dtype=torch.float32, device=qkv.device)
+        part_lse = torch.empty((n * n_q * splits,), dtype=torch.float32, device=qkv.device)
+    _check(lib.ms_attention_decode_fused(
+        _ptr(qkv), _ptr(slots), _ptr(q_weight), _ptr(k_weight), _i(weight_code), _f(eps), _ptr(cos_sin), _ptr(k_pool),
+        _ptr(v_pool), _ptr(block_tables), _i(block_tables.shape[1]), _ptr(query_start), _ptr(context_lens),
+        _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale), _i(window if window else 0), _ptr(out),
+        _ptr(part_o), _ptr(part_lse), _i(splits), _i(n), _stream()))
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -104,22 +104,29 @@ class Attention(Part):
         n_q, n_kv = self.num_heads, self.num_kv_heads
         qkv = torch.empty((n, (n_q + 2 * n_kv) * d), dtype=x.dtype, device=x.device)
         kernels.linear(x, self.qkv_weight, qkv, row_stats=stats)
-        q = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
         slots = cache.slots if cache.writable else torch.full_like(cache.slots, -1)
         fused = self.position.fused_args(ctx)
-        if fused is not None:
-            cos_sin, rotary_dim, interleaved = fused
-            kernels.qk_norm_rope_append(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, cos_sin,
-                                        rotary_dim, interleaved, cache.key_pool, cache.value_pool, n_q, n_kv, d, q)
-        else:
-            self._append_with_external_position(qkv, slots, ctx, cache, q)
         attended = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
-        if self.score_bias_slopes is not None and self._slopes_on_device is None:
-            self._slopes_on_device = torch.tensor(self.score_bias_slopes, dtype=torch.float32, device=x.device)
-        kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
-                                ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
-                                ctx.max_context_len, self.scale, self.window, attended,
-                                ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
+        if self._decode_in_the_attention_kernel(ctx, fused, x.dtype):
+            # a step of single tokens: norm, rotation and append happen inside the split-key attention kernel
+            kernels.decode_attention_fused(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, fused[0],
+                                           cache.key_pool, cache.value_pool, cache.block_tables, ctx.query_start,
+                                           ctx.context_lens, ctx.max_context_len, self.scale, self.window, n_q, n_kv, d,
+                                           attended)
+        else:
+            q = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
+            if fused is not None:
+                cos_sin, rotary_dim, interleaved = fused
+                kernels.qk_norm_rope_append(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, cos_sin,
+                                            rotary_dim, interleaved, cache.key_pool, cache.value_pool, n_q, n_kv, d, q)
+            else:
+                self._append_with_external_position(qkv, slots, ctx, cache, q)
+            if self.score_bias_slopes is not None and self._slopes_on_device is None:
+                self._slopes_on_device = torch.tensor(self.score_bias_slopes, dtype=torch.float32, device=x.device)
+            kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
+                                    ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
+                                    ctx.max_context_len, self.scale, self.window, attended,
+                                    ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
         out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
         if fold is not None:
             partials = torch.empty((kernels.wide_blocks(*self.o_weight.shape), 8), dtype=torch.float32, device=x.device)
@@ -128,6 +135,21 @@ class Attention(Part):
             return FoldedInput(out, stats)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
         return out
+
+    def _decode_in_the_attention_kernel(self, ctx: StepContext, fused, dtype: torch.dtype) -> bool:
+        """Whether this step's norm, rotation and append run inside the attention kernel
+        (``kernels.decode_attention_fused``): one token per request, a position encoding in that kernel's form (none,
+        or half-split rotation over the whole head), no score modifiers, sizes that the kernel takes."""
+        if ctx.max_query_len != 1 or ctx.n_tokens != ctx.n_requests or fused is None:
+            return False
+        if not kernels.decode_attention_fused_preferred(ctx.n_requests):
+            return False
+        cos_sin, rotary_dim, interleaved = fused
+        if cos_sin is not None and (interleaved or rotary_dim != self.head_dim):
+            return False
+        if self.score_softcap or self.score_bias_slopes is not None:
+            return False
+        return kernels.decode_attention_fused_supported(dtype, self.head_dim, self.num_heads, self.num_kv_heads)
 
     def _append_with_external_position(self, qkv, slots, ctx, cache, q_out) -> None:
         """Position parts without a fused form: norm, ``position.apply``, then a plain append."""

@@ -329,6 +329,59 @@ def test_embedding_scale_and_logit_transform(kernels):
     assert torch.equal(only_scaled, 3.0 * before)
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,page_size,window,with_norm,with_rope,weight_dtype", [
+    (16, 8, 128, 64, None, True, True, torch.bfloat16), (8, 2, 64, 16, None, True, True, torch.float32),
+    (6, 1, 128, 8, 300, False, True, torch.bfloat16), (4, 4, 64, 32, 70, True, False, torch.bfloat16),
+    (32, 2, 128, 16, None, True, True, torch.float32)])
+@pytest.mark.parametrize("lengths", [[1, 2, 31, 32, 33, 700, 1500], [2500], [129] * 9, [64, 4000] * 20])
+def test_decode_attention_with_norm_rotation_and_append_inside(kernels, lengths, n_q, n_kv, d, page_size, window, with_norm,
+                                                               with_rope, weight_dtype):
+    """A decode step's norm + rotation + append inside the split-key attention kernel, against the plain versions of
+    the separate steps: the attended heads, and what the cache holds afterwards.  One to many splits, requests of
+    one key, windows, a request whose key is in the cache already (no slot), and a dominant far key."""
+    dtype = torch.bfloat16
+    n = len(lengths)
+    assert kernels.decode_attention_fused_supported(dtype, d, n_q, n_kv)
+    q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, _, max_ctx = \
+        _attention_case(dtype, n_q, n_kv, d, page_size, lengths, [1] * n, 41)
+    qkv = rand((n, (n_q + 2 * n_kv) * d), dtype, 42)
+    q_w = (1 + rand((d,), torch.float32, 43, 0.1)).to(weight_dtype) if with_norm else None
+    k_w = (1 + rand((d,), torch.float32, 44, 0.1)).to(weight_dtype) if with_norm else None
+    cos_sin = None
+    if with_rope:
+        inv_freq = (1.0 / (1e6 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+        cos_sin = torch.empty((n, d // 2, 2), dtype=torch.float32).cuda()
+        kernels.rope_table(positions, inv_freq, cos_sin)
+    slots = torch.tensor([int(tables[r, (length - 1) // page_size]) * page_size + (length - 1) % page_size
+                          for r, length in enumerate(lengths)], dtype=torch.int32)
+    if n > 2:
+        slots[2] = -1                      # this request's newest key and value are in the cache already
+    slots = slots.cuda()
+    # the plain steps, on copies of the cache
+    ek, ev = k_pool.double().clone(), v_pool.double().clone()
+    eq = torch.empty((n, n_q, d), dtype=torch.float64).cuda()
+    plain_ops.qk_norm_rope_append(qkv, slots, q_w, k_w, 1e-6, cos_sin, d if with_rope else 0, False, ek, ev, n_q, n_kv, d, eq)
+    dominated = None
+    if lengths[-1] > 600:                  # one old key of the last request is made to dominate its first query head
+        target = lengths[-1] - 500 if window is None else lengths[-1] - window + 3
+        page, offset = int(tables[n - 1, target // page_size]), target % page_size
+        k_pool[page, 0, offset] = (eq[n - 1, 0] * 40).to(dtype)
+        ek[page, 0, offset] = k_pool[page, 0, offset].double()
+        dominated = (page, offset)
+    expected = torch.empty((n, n_q, d), dtype=torch.float64)
+    plain_ops.paged_attention(eq.to(dtype).cpu(), ek.to(dtype).cpu(), ev.to(dtype).cpu(), tables.cpu(), request_of_token.cpu(),
+                              positions.cpu(), query_start.cpu(), context_lens.cpu(), 1, max_ctx, d ** -0.5, window, expected)
+    out = torch.full((n, n_q, d), 7.0, dtype=dtype).cuda()
+    kernels.decode_attention_fused(qkv, slots, q_w, k_w, 1e-6, cos_sin, k_pool, v_pool, tables, query_start, context_lens,
+                                   max_ctx, d ** -0.5, window, n_q, n_kv, d, out)
+    torch.cuda.synchronize()
+    assert torch.allclose(out.double().cpu(), expected, atol=2e-2, rtol=2e-2), float((out.double().cpu() - expected).abs().max())
+    assert torch.allclose(k_pool.double(), ek, atol=2e-2, rtol=2e-2)
+    assert torch.equal(v_pool.double(), ev)
+    if dominated is not None:
+        assert torch.allclose(out[n - 1, 0].float(), v_pool[dominated[0], 0, dominated[1]].float(), atol=3e-2)
+
+
 @pytest.mark.parametrize("tcgen05", [True, False])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("d,n_q,n_kv,page_size", [(64, 8, 2, 16), (128, 4, 2, 64), (128, 16, 8, 16)])

@@ -298,6 +298,30 @@ def test_many_live_requests_decode_together(request, tmp_path, live, dtype, exec
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
 
 
+@pytest.mark.parametrize("execution", ["eager", "cuda_graph"])
+@pytest.mark.parametrize("fused_rows", [(1, 256), None])
+@pytest.mark.parametrize("live", [1, 2, 5, 20])
+def test_decode_steps_with_and_without_the_fused_attention(request, tmp_path, monkeypatch, live, fused_rows, execution):
+    """Norm, rotation and append inside the attention kernel are used for some numbers of requests only (where they
+    were measured faster); here every number of requests runs both ways, eagerly and as replayed graphs."""
+    from miniserve_b200 import kernels
+
+    if fused_rows is None:
+        monkeypatch.setattr(kernels, "FUSED_DECODE_ATTENTION", False)
+    else:
+        monkeypatch.setattr(kernels, "FUSED_DECODE_ROWS", fused_rows)
+    vocab = helpers.TINY["d"]["vocab_size"]
+    requests, steps, wanted = many_live_case(vocab, live, seed=40 + live, max_prompt=70, new_tokens=6)
+    folder = helpers.make_folder(tmp_path, "d", seed=2)
+    pages = (helpers.max_live_tokens(steps, granule=16) + 15) // 16
+    runtime = build(folder, "bfloat16", pages, 16, max_seqs=live, execution=execution, max_model_len=256)
+    got = helpers.collect(steps, replay(runtime, steps))
+    for rid in requests:
+        assert sorted(got[rid]) == wanted[rid]
+    check_against(request, got, lambda rid: helpers.oracle_logits(folder, requests[rid]), "bfloat16")
+    assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
+
+
 @pytest.fixture(scope="module")
 def real_weights(real_model):
     import plain_qwen3 as plain
