@@ -400,13 +400,15 @@ MS_EXPORT int ms_attention_decode_fused_supports(int head_dim, int n_q, int n_kv
 }
 
 // In how many parts (1..64) the keys of every request should be split: the smallest count whose blocks fill whole
-// waves of the GPU's block slots to at least 90 % (each part keeping 128 keys or more), else the count that fills
+// waves of the GPU's block slots to at least 90 % (each part keeping 64 keys or more), else the count that fills
 // them best.  The count depends on the batch's shape only (requests, longest context allowed), not on its content.
 MS_EXPORT int ms_attention_decode_fused_splits(int head_dim, int n_requests, int n_kv, int max_context_len) {
   const int slots = head_dim == 128 ? fused::block_slots<128, 32, 2>() : fused::block_slots<64, 64, 2>();
   const long long base = (long long)n_requests * n_kv;
   if (slots <= 0 || base <= 0) return 1;
-  int limit = max_context_len / 128;
+  // a part keeps 64 keys (two tiles) or more: with one request the 64 parts of a 4,096-token context made the step 5.6 %
+  // faster than 32 parts of 128 keys (a block's tiles are a chain of memory latencies), with two or more nothing changed
+  int limit = max_context_len / 64;
   if (limit > fused::MAX_SPLITS) limit = fused::MAX_SPLITS;
   if (limit < 1) limit = 1;
   int splits = 1;
