@@ -289,8 +289,10 @@ class Bench:
                 "timed_seconds": sum(times) * steps}
 
     def measure_prefill(self, tokens: int) -> float:
+        import numpy
+
         manager = self.manager
-        prompt = self.prompt(tokens)
+        prompt = numpy.asarray(self.prompt(tokens), dtype=numpy.int64)      # as the engine's sequences hold their prompts
 
         def once() -> None:
             manager.admit("p")

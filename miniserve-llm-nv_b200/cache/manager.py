@@ -43,7 +43,7 @@ class ReservedItem:
     end: int
     new_pages: list[list[int]]      # per paged group
     tables: list[list[int]]         # per paged group: the table this step runs with (old + new pages)
-    slots: list[list[int]]          # per paged group: page * page_size + offset of every new token
+    slots: list                     # per paged group: page * page_size + offset of every new token (a numpy array)
 
 
 @dataclass
@@ -291,7 +291,7 @@ class CacheManager:
                 pages = numpy.asarray(table, dtype=numpy.int64)[positions // self.page_size]
                 if (pages == RELEASED).any():
                     raise RuntimeError("a new token falls into a page that was given back")
-                slots.append((pages * self.page_size + positions % self.page_size).tolist())
+                slots.append(pages * self.page_size + positions % self.page_size)
             reserved.append(ReservedItem(entry.request_id, entry.length, end, new_pages, tables, slots))
         reservation = StepReservation(self._next_step, reserved)
         self._next_step += 1

@@ -14,6 +14,8 @@ import enum
 from dataclasses import dataclass, field
 from typing import Optional
 
+import numpy
+
 from ..sampling.params import SamplingParams
 
 
@@ -37,6 +39,7 @@ class Sequence:
     finish_reason: Optional[str] = None
     preemptions: int = 0
     prompt_cached: bool = False      # its prompt pages were offered for reuse
+    _prompt_array: Optional[numpy.ndarray] = field(default=None, repr=False, compare=False)
 
     @property
     def tokens(self) -> list[int]:
@@ -58,10 +61,15 @@ class Sequence:
     def done(self) -> bool:
         return self.status in (Status.FINISHED, Status.FAILED)
 
-    def token_slice(self, start: int, end: int) -> list[int]:
+    def token_slice(self, start: int, end: int):
+        """Tokens ``start .. end - 1``: a view of the prompt held as an int64 array where the slice lies within the
+        prompt (a portion of thousands of tokens is then handed to the step without being rebuilt number by number),
+        else a list."""
         n_prompt = len(self.prompt)
         if end <= n_prompt:
-            return list(self.prompt[start:end])
+            if self._prompt_array is None:
+                self._prompt_array = numpy.asarray(self.prompt, dtype=numpy.int64)
+            return self._prompt_array[start:end]
         return (list(self.prompt[start:]) if start < n_prompt else []) + self.generated[max(start - n_prompt, 0):end - n_prompt]
 
     def advance(self, end: int) -> None:

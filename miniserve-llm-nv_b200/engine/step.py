@@ -156,7 +156,7 @@ class StepFunction:
                 raise ValueError(f"entry {row} does not match its reservation")
             if item.end > self.max_model_len:
                 raise ValueError(f"request {entry.request_id!r} would reach {item.end} tokens; the limit is {self.max_model_len}")
-            ids = numpy.asarray(entry.tokens, dtype=numpy.int64)
+            ids = numpy.asarray(entry.tokens, dtype=numpy.int64)      # (no copy if the caller holds its tokens as such an array)
             if count and (int(ids.min()) < 0 or int(ids.max()) >= self.vocab_size):
                 raise ValueError(f"a token id of request {entry.request_id!r} lies outside the vocabulary of {self.vocab_size}")
             for index in entry.want:
@@ -318,7 +318,7 @@ class StepFunction:
                     host[base + first:base + len(table)] = [scratch if p == RELEASED else p for p in fresh]
                 if first == 0:
                     host[base + len(table):base + graph.width] = scratch
-                slot = item.slots[g][0]
+                slot = int(item.slots[g][0])
                 if not 0 <= slot < limit * ps:
                     raise ValueError(f"slot {slot} outside the pool")
                 host[o[9 + 2 * g] + row] = slot

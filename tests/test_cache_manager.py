@@ -58,7 +58,7 @@ def test_slots_follow_non_contiguous_tables():
     assert a.tables == [[0, 1, 3]] and b.tables == [[2, 4, 5]]
     for position, slot in zip(range(17, 33), a.slots[0]):
         assert slot == a.tables[0][position // 16] * 16 + position % 16
-    assert b.slots[0][12:15] == [2 * 16 + 15, 4 * 16 + 0, 4 * 16 + 1]       # positions 15, 16, 17
+    assert list(b.slots[0][12:15]) == [2 * 16 + 15, 4 * 16 + 0, 4 * 16 + 1]       # positions 15, 16, 17
     manager.commit(r)
     assert manager.length("a") == 33 and manager.length("b") == 33
     manager.check_invariants()
@@ -281,7 +281,7 @@ def test_truncate_gives_back_the_pages_behind_the_new_end():
     assert manager.capacity().free_pages == (5,)            # page 3 is free; page 2 is held by the cache alone
     manager.check_invariants()
     reservation = manager.prepare([("a", 3)])               # goes on from token 6, in page 1 and a new page
-    assert reservation.items[0].slots[0] == [6, 7, 12] and reservation.items[0].start == 6
+    assert list(reservation.items[0].slots[0]) == [6, 7, 12] and reservation.items[0].start == 6
     manager.commit(reservation)
     with pytest.raises(ValueError):
         manager.truncate("a", 10)
