@@ -525,7 +525,12 @@ def _few_rows_choice(x: torch.Tensor, weight: torch.Tensor, m: int) -> str:
     if choice is None:
         if not LINEAR_TUNING or torch.cuda.is_current_stream_capturing():
             return _few_rows_rule(x.device, m, n, k)
+        choice = _stored_choice("linear", n, k)
+        if choice is not None and (choice != "wide" or wide_supports(n, k)):
+            _linear_choices[key] = choice
+            return choice
         choice = _linear_choices[key] = _measure_few_rows(weight)
+        _store_choice("linear", n, k, choice)
         log.info("products of up to %d rows with a %d x %d weight run the %s kernel (measured, us: %s)", SKINNY_MAX_ROWS, n, k,
                  choice, _choice_times.get(key))
     return choice
@@ -534,6 +539,45 @@ def _few_rows_choice(x: torch.Tensor, weight: torch.Tensor, m: int) -> str:
 def linear_choices() -> dict:
     """What was measured so far: (device index, N, K) -> the kernel chosen for products of few rows."""
     return dict(_linear_choices)
+
+
+# A measured choice can differ between runs where two kernels are level, and with it the order of a product's sums.
+# MINISERVE_B200_CHOICES_FILE names a JSON file that keeps the choices: what it holds is used instead of measuring,
+# and what is measured is added to it, so that later runs (and other processes) repeat the first one's choices.
+CHOICES_FILE = __import__("os").environ.get("MINISERVE_B200_CHOICES_FILE", "")
+
+
+def _stored_choice(kind: str, n: int, k: int) -> Optional[str]:
+    if not CHOICES_FILE:
+        return None
+    import json
+    try:
+        with open(CHOICES_FILE, encoding="utf-8") as handle:
+            value = json.load(handle).get(f"{kind} {n}x{k}")
+    except (OSError, ValueError):
+        return None
+    allowed = ("skinny", "stream", "wide", "library") if kind == "linear" else ("wide", "separate")
+    return value if value in allowed else None
+
+
+def _store_choice(kind: str, n: int, k: int, choice: str) -> None:
+    if not CHOICES_FILE:
+        return
+    import json
+    import os
+    try:
+        try:
+            with open(CHOICES_FILE, encoding="utf-8") as handle:
+                stored = json.load(handle)
+        except (OSError, ValueError):
+            stored = {}
+        stored[f"{kind} {n}x{k}"] = choice
+        temporary = f"{CHOICES_FILE}.{os.getpid()}"
+        with open(temporary, "w", encoding="utf-8") as handle:
+            json.dump(stored, handle, indent=1, sort_keys=True)
+        os.replace(temporary, CHOICES_FILE)
+    except OSError as error:
+        log.warning("cannot keep the kernel choices in %s: %s", CHOICES_FILE, error)
 
 
 TUNING_REPEATS = 8      # a candidate this many times in one captured graph
@@ -787,7 +831,12 @@ def _gated_choice(x: torch.Tensor, weight: torch.Tensor) -> str:
         elif not LINEAR_TUNING or torch.cuda.is_current_stream_capturing():
             return "wide" if fits == 2 and n >= WIDE_GATED_MIN_ROWS else "separate"
         else:
+            choice = _stored_choice("gated", n, k)
+            if choice is not None:
+                _gated_choices[key] = choice
+                return choice
             choice = _gated_choices[key] = _measure_gated(weight)
+            _store_choice("gated", n, k, choice)
             log.info("gated products of up to %d rows with a %d x %d weight run %s (measured, us: %s)", SKINNY_MAX_ROWS, n, k,
                      "the kernel that applies the activation" if choice == "wide" else "a plain product and the activation kernel",
                      _choice_times.get(key + ("gated",)))

@@ -161,3 +161,26 @@ def test_sharded_folder_and_duplicates(tmp_path):
     (folder / "model-00002-of-00002.safetensors").unlink()
     with pytest.raises(FileNotFoundError):
         load_tensors(folder, model.param_specs(), torch.bfloat16, "cpu", spec.optional_names)
+
+
+def test_kernel_choices_can_be_kept_in_a_file(tmp_path, monkeypatch):
+    """MINISERVE_B200_CHOICES_FILE: what was measured once is written down and used by later runs instead of a new
+    measurement, so that the order of a product's sums (and with it bfloat16 results) repeats; entries that name
+    no known kernel are ignored."""
+    import json
+
+    from miniserve_b200 import kernels
+
+    path = tmp_path / "choices.json"
+    monkeypatch.setattr(kernels, "CHOICES_FILE", str(path))
+    assert kernels._stored_choice("linear", 4096, 2048) is None
+    kernels._store_choice("linear", 4096, 2048, "wide")
+    kernels._store_choice("gated", 12288, 2048, "separate")
+    assert kernels._stored_choice("linear", 4096, 2048) == "wide" and kernels._stored_choice("gated", 12288, 2048) == "separate"
+    assert json.loads(path.read_text()) == {"linear 4096x2048": "wide", "gated 12288x2048": "separate"}
+    path.write_text('{"linear 8x8": "no such kernel"}')
+    assert kernels._stored_choice("linear", 8, 8) is None
+    path.write_text("not json")
+    assert kernels._stored_choice("linear", 8, 8) is None
+    kernels._store_choice("linear", 8, 8, "skinny")
+    assert kernels._stored_choice("linear", 8, 8) == "skinny"
