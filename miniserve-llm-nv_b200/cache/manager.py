@@ -184,6 +184,12 @@ class CacheManager:
         if any(need.window is not None for need in self.paged_needs) or self.state_needs:
             raise RuntimeError("truncate needs every token's keys and no per-request state")
         keep = (length + self.page_size - 1) // self.page_size
+        if length % self.page_size:
+            # the request will write its next tokens into the page that holds token `length`: nobody else may hold it
+            for group, table in enumerate(entry.tables):
+                if self.allocators[group].refcount(table[keep - 1]) > 1:
+                    raise RuntimeError(f"request {request_id!r} shares the page that holds token {length} (a reused "
+                                       "prefix); truncate to a multiple of the page size instead")
         for group, table in enumerate(entry.tables):
             for page in table[keep:]:
                 self.allocators[group].release(page)

@@ -276,12 +276,18 @@ def test_truncate_gives_back_the_pages_behind_the_new_end():
     manager.admit("a")
     manager.commit(manager.prepare([("a", 13)]))            # 4 pages
     manager.cache_prefix("a", prompt)                       # the cache holds the first 3 too
+    with pytest.raises(RuntimeError, match="shares the page"):
+        manager.truncate("a", 6)                            # page 1 is the cache's too: new tokens must not land in it
+    manager.prefix.remove(next(e for e in manager.prefix.entries.values() if e.pages == (2,)))
+    manager.allocators[0].release(2)                        # (the cache gives up its last two pages, leaves first)
+    manager.prefix.remove(next(e for e in manager.prefix.entries.values() if e.pages == (1,)))
+    manager.allocators[0].release(1)
     manager.truncate("a", 6)
     assert manager.length("a") == 6 and manager.requests["a"].tables == [[0, 1]]
-    assert manager.capacity().free_pages == (5,)            # page 3 is free; page 2 is held by the cache alone
+    assert manager.capacity().free_pages == (6,)            # pages 2 and 3 are free
     manager.check_invariants()
     reservation = manager.prepare([("a", 3)])               # goes on from token 6, in page 1 and a new page
-    assert list(reservation.items[0].slots[0]) == [6, 7, 12] and reservation.items[0].start == 6
+    assert list(reservation.items[0].slots[0]) == [6, 7, 8] and reservation.items[0].start == 6
     manager.commit(reservation)
     with pytest.raises(ValueError):
         manager.truncate("a", 10)
