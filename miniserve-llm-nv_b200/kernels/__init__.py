@@ -37,6 +37,13 @@ def library() -> ctypes.CDLL:
         lib.ms_abi_version.restype = ctypes.c_int
         if lib.ms_abi_version() != ABI_VERSION:
             raise KernelError(f"{path} reports ABI {lib.ms_abi_version()}, bindings expect {ABI_VERSION}; rebuild it")
+        # argument and result types from the prototypes in the sources: calls then pass plain Python numbers
+        kinds = {"pointer": ctypes.c_void_p, "int": ctypes.c_int, "float": ctypes.c_float, "longlong": ctypes.c_longlong,
+                 "string": ctypes.c_char_p, "void": None}
+        for name, (result, arguments) in build.exported_signatures().items():
+            function = getattr(lib, name)
+            function.restype = kinds[result]
+            function.argtypes = [kinds[a] for a in arguments]
         _library = lib
     return _library
 
@@ -54,16 +61,17 @@ def _check(code: int) -> None:
 _device_index: Optional[int] = None
 
 
-def _stream() -> ctypes.c_void_p:
+def _stream() -> int:
     """torch's current stream on the library's device (the raw handle: this is called for every launch)."""
     global _device_index
     if _device_index is None:
         _device_index = torch.cuda.current_device()
-    return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(_device_index))
+    return torch._C._cuda_getCurrentRawStream(_device_index)
 
 
-def _ptr(tensor: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    """The tensor's address (None: a null pointer); the entry points' argument types are known to ctypes."""
+    return None if tensor is None else tensor.data_ptr()
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -74,6 +82,9 @@ def _code(dtype: torch.dtype) -> int:
 
 
 def _want(tensor: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if (tensor.is_cuda and tensor.is_contiguous() and (dtype is None or tensor.dtype is dtype)
+            and (shape is None or tensor.shape == shape)):
+        return                      # (one test for the usual case; what follows words the refusal)
     if not tensor.is_cuda:
         raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
     if not tensor.is_contiguous():
@@ -84,12 +95,8 @@ def _want(tensor: torch.Tensor, name: str, dtype=None, shape=None) -> None:
         raise KernelError(f"{name} must have shape {tuple(shape)}, got {tuple(tensor.shape)}")
 
 
-def _i(value: int) -> ctypes.c_int:
-    return ctypes.c_int(int(value))
-
-
-def _f(value: float) -> ctypes.c_float:
-    return ctypes.c_float(float(value))
+_i = int        # (arguments are converted by ctypes from the prototypes' types; these only coerce)
+_f = float
 
 
 # --------------------------------------------------------------------------- memory-bound kernels
@@ -108,7 +115,7 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scal
 def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: Optional[float] = None) -> None:
     """In place on float32 ``x``: ``x *= scale``, then with ``cap``: ``x = cap * tanh(x / cap)``."""
     _want(x, "x", torch.float32)
-    _check(library().ms_scale_softcap(_ptr(x), ctypes.c_longlong(x.numel()), _f(scale), _f(cap if cap else 0.0), _stream()))
+    _check(library().ms_scale_softcap(_ptr(x), x.numel(), _f(scale), _f(cap if cap else 0.0), _stream()))
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -665,7 +672,7 @@ def linear_stream(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> N
     buffers = _stream_buffers.get(key)
     if buffers is None or buffers[1].numel() < tiles:
         floats, ints = ctypes.c_longlong(0), ctypes.c_longlong(0)
-        _check(library().ms_gemm_stream_buffers(_i(max(n, 1 << 20)), ctypes.byref(floats), ctypes.byref(ints)))
+        _check(library().ms_gemm_stream_buffers(_i(max(n, 1 << 20)), ctypes.addressof(floats), ctypes.addressof(ints)))
         buffers = (torch.empty(floats.value, dtype=torch.float32, device=x.device),
                    torch.zeros(ints.value, dtype=torch.int32, device=x.device))
         _stream_buffers[key] = buffers

@@ -69,6 +69,38 @@ def _digest() -> str:
     return h.hexdigest()
 
 
+def exported_signatures() -> dict:
+    """``{name: (return kind, [argument kinds])}`` of every ``MS_EXPORT`` function in the sources, read from their
+    prototypes: kinds are ``"pointer"`` (any pointer, and streams), ``"int"``, ``"float"``, ``"longlong"``,
+    ``"string"`` (``const char*`` results) and ``"void"``.  The bindings give these to ctypes, so that calls pass
+    plain Python numbers instead of building a ctypes object per argument."""
+    import re
+
+    def kind(text: str, result: bool = False) -> str:
+        text = " ".join(text.split())
+        if result and text.startswith("const char"):
+            return "string"
+        if "*" in text or "cudaStream_t" in text:
+            return "pointer"
+        if text.startswith("long long") or " long long" in text:
+            return "longlong"
+        if text.startswith("float") or text.startswith("const float"):
+            return "float"
+        if text.startswith("void"):
+            return "void"
+        if text.startswith("int") or text.startswith("const int") or text.startswith("unsigned"):
+            return "int"
+        raise KernelBuildError(f"cannot tell the ctypes kind of {text!r} in an exported prototype")
+
+    found: dict = {}
+    pattern = re.compile(r"MS_EXPORT\s+([\w\s\*]+?)\s*\b(ms_\w+)\s*\(([^)]*)\)", re.DOTALL)
+    for path in source_files():
+        for result, name, arguments in pattern.findall(path.read_text()):
+            arguments = [a for a in (part.strip() for part in arguments.split(",")) if a and a != "void"]
+            found[name] = (kind(result, result=True), [kind(a) for a in arguments])
+    return found
+
+
 def _build_dir() -> Path:
     in_tree = PACKAGE_DIR / "_build"
     try:

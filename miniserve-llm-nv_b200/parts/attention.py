@@ -102,11 +102,11 @@ class Attention(Part):
             x, stats = x.x, x.stats
         n, d = x.shape[0], self.head_dim
         n_q, n_kv = self.num_heads, self.num_kv_heads
-        qkv = torch.empty((n, (n_q + 2 * n_kv) * d), dtype=x.dtype, device=x.device)
+        qkv = ctx.buffer("attention.qkv", (n, (n_q + 2 * n_kv) * d), x.dtype)
         kernels.linear(x, self.qkv_weight, qkv, row_stats=stats)
         slots = cache.slots if cache.writable else torch.full_like(cache.slots, -1)
         fused = self.position.fused_args(ctx)
-        attended = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
+        attended = ctx.buffer("attention.attended", (n, n_q, d), x.dtype)
         if self._decode_in_the_attention_kernel(ctx, fused, x.dtype):
             # a step of single tokens: norm, rotation and append happen inside the split-key attention kernel
             kernels.decode_attention_fused(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, fused[0],
@@ -114,7 +114,7 @@ class Attention(Part):
                                            ctx.context_lens, ctx.max_context_len, self.scale, self.window, n_q, n_kv, d,
                                            attended)
         else:
-            q = torch.empty((n, n_q, d), dtype=x.dtype, device=x.device)
+            q = ctx.buffer("attention.q", (n, n_q, d), x.dtype)
             if fused is not None:
                 cos_sin, rotary_dim, interleaved = fused
                 kernels.qk_norm_rope_append(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, cos_sin,
@@ -127,9 +127,9 @@ class Attention(Part):
                                     ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
                                     ctx.max_context_len, self.scale, self.window, attended,
                                     ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
-        out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
+        out = ctx.buffer("attention.out", (n, self.hidden_size), x.dtype)
         if fold is not None:
-            partials = torch.empty((kernels.wide_blocks(*self.o_weight.shape), 8), dtype=torch.float32, device=x.device)
+            partials = ctx.buffer("attention.partials", (kernels.wide_blocks(*self.o_weight.shape), 8), torch.float32)
             stats = kernels.linear_wide_residual(attended.view(n, n_q * d), self.o_weight, fold.residual, fold.weight,
                                                  fold.eps, out, partials)
             return FoldedInput(out, stats)

@@ -63,14 +63,14 @@ class PreNormBlock:
         if isinstance(pending, FoldedInput):
             normed = pending
         else:
-            normed = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+            normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)
             self.mixer_norm.add_and_norm(residual, pending, normed)
         fold = fold_between(self.mixer, self.feed_forward_norm, self.feed_forward, ctx)
         if fold is not None:
             normed = self.mixer.forward(normed, ctx, cache, fold=NormFold(residual, *fold))
         else:
             delta = self.mixer.forward(normed, ctx, cache)
-            normed = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+            normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)      # (the mixer has read the first)
             self.feed_forward_norm.add_and_norm(residual, delta, normed)
         if next_block is not None and getattr(next_block, "takes_next_block", False):
             fold = fold_between(self.feed_forward, getattr(next_block, "mixer_norm", None), getattr(next_block, "mixer", None), ctx)

@@ -60,3 +60,15 @@ class StepContext:
     host_state_slots: list[int] = field(default_factory=list)
     memo: dict[Any, Any] = field(default_factory=dict)   # per-step scratch shared by parts (rotation tables)
     group_views: list[Any] = field(default_factory=list)  # per cache group: (block_tables, slots)
+
+    def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        """An uninitialised device tensor for a part's intermediate result, the same one for every call of a step
+        with the same name, shape and type.  The layers of a step run one after the other on one stream, so a
+        layer's intermediates can live where the layer before kept its own; a step of 28 layers then allocates
+        nine tensors, not 250 (an allocation costs the host more than some kernels cost the device).  A tensor
+        that outlives the step (the logits) must not come from here."""
+        key = ("buffer", name, shape, dtype)
+        found = self.memo.get(key)
+        if found is None:
+            found = self.memo[key] = torch.empty(shape, dtype=dtype, device=self.device)
+        return found

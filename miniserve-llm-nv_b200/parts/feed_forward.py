@@ -59,18 +59,18 @@ class GatedMLP(Part):
         if isinstance(x, FoldedInput):
             x, stats = x.x, x.stats
         n = x.shape[0]
-        out = torch.empty((n, self.hidden_size), dtype=x.dtype, device=x.device)
+        out = ctx.buffer("gated_mlp.out", (n, self.hidden_size), x.dtype)
         if self.paired:
-            hidden = torch.empty((n, self.intermediate_size), dtype=x.dtype, device=x.device)
+            hidden = ctx.buffer("gated_mlp.hidden", (n, self.intermediate_size), x.dtype)
             kernels.gated_up(x, self.gate_up_weight, hidden, row_stats=stats)
             if fold is not None:
-                partials = torch.empty((kernels.wide_blocks(*self.down_weight.shape), 8), dtype=torch.float32, device=x.device)
+                partials = ctx.buffer("gated_mlp.partials", (kernels.wide_blocks(*self.down_weight.shape), 8), torch.float32)
                 stats = kernels.linear_wide_residual(hidden, self.down_weight, fold.residual, fold.weight, fold.eps, out,
                                                      partials)
                 return FoldedInput(out, stats)
             kernels.linear(hidden, self.down_weight, out)
         else:
-            gate_up = torch.empty((n, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+            gate_up = ctx.buffer("gated_mlp.gate_up", (n, 2 * self.intermediate_size), x.dtype)
             kernels.linear(x, self.gate_up_weight, gate_up)
             kernels.gated_linear(gate_up, self.down_weight, out)
         return out

@@ -181,7 +181,8 @@ def test_feed_forward_part(dtype, hidden, inter, rows):
     assert sorted(s.name for s in part.param_specs()) == sorted(w)
     part.load(w)
     x = rand((rows, hidden), dtype, 33)
-    out = part.forward(x, None)
+    from miniserve_b200.parts import PagedKVNeed
+    out = part.forward(x, Harness([PagedKVNeed(1, 16, None)], dtype, num_pages=32).context({"a": rows}))
     expected = plain.plain_swiglu(x.double(), *(w[k].double() for k in ("m.gate_proj.weight", "m.up_proj.weight", "m.down_proj.weight")))
     assert torch.allclose(out.double(), expected, **tol(dtype, float(expected.abs().max())))
 
