@@ -1,0 +1,387 @@
+// out[M, N] = X[M, K] * W[N, K]^T for the many-row products of prompt portions, with TWO thread blocks (a cluster
+// of two, on neighbouring multiprocessors) working on each 256 x 256 tile of the output: tcgen05.mma with
+// cta_group::2.  bfloat16 operands, float32 accumulation in tensor memory.
+//
+// Each block of a pair loads, for every 64-wide k-block, ITS 128 rows of the X tile and ITS 128 rows of the W tile
+// (32 KB; a block working alone on a 128 x 256 tile loads 48 KB for the same number of MMA cycles), and the MMA,
+// issued by one thread of the pair's even block, reads both halves of both operands from the two blocks' shared
+// memory and accumulates rows 0..127 of the tile in the even block's tensor memory and rows 128..255 in the odd
+// block's.  Nothing is loaded for both blocks at once: every block fetches its own halves.
+//
+// A pair walks over the tiles (pair index, then every (number of pairs)-th; neighbours in this order share their W
+// tile).  In each block:
+//   warp 0      one thread issues the TMA loads of this block's halves into a ring of stages; their arrival is
+//               counted on the EVEN block's "full" barrier of the stage;
+//   warp 1      allocates tensor memory for two accumulators (both blocks, together); in the even block one thread
+//               issues the MMAs and frees each stage with a commit that arrives on the "empty" barrier of BOTH blocks;
+//               a last commit per tile announces the accumulator to both blocks' read-out warps;
+//   warps 2..5  read this block's 128 rows of the accumulator out of tensor memory, apply the epilogue and store,
+//               while the next tile is being accumulated in the other accumulator; then they arrive on the even
+//               block's "accumulator free" barrier.  Each warp puts 32 rows x 128 bytes of results at a time into
+//               one of its two swizzled 4 KB buffers and hands it to a TMA store (or TMA add), which writes whole
+//               lines and clips at the matrix' edges; a thread storing its own row straight from registers
+//               touches 32 lines per instruction, and those requests share the path on which the operand loads
+//               are asked for.  Output widths that TMA does not take (a row pitch that is no multiple of 16
+//               bytes) are stored from registers.
+// Epilogues: store (bfloat16 or float32), add into a float32 matrix in place, or the gated activation
+// silu(gate) * up of a weight whose rows are paired (eight gate rows, then the same eight up rows).
+//
+// Every wait on an mbarrier is bounded: a wait that does not finish within the limit sets the error flag that the
+// host checks, and the kernel drains and returns (tensor memory is freed on every path; both blocks meet before).
+#include "tcgen05.cuh"
+
+namespace ms {
+namespace pair {
+
+using namespace ms::t5;
+
+constexpr int HALF = 128;                    // rows of X, and rows of W, that one block of the pair loads
+constexpr int TILE = 2 * HALF;               // the pair's tile: 256 x 256
+constexpr int BK = 64, UMMA_K = 16;
+constexpr int THREADS = 192;                 // warps 0..5
+constexpr int ACCUMULATORS = 2;
+constexpr int STAGE_BYTES = 2 * HALF * BK * 2;     // this block's halves of X and W for one k-block
+constexpr int OUT_BUFFER = 32 * 128;               // 32 rows x 128 bytes: what one read-out warp stores at a time
+constexpr int OUT_BYTES = 4 * 2 * OUT_BUFFER;      // two such buffers for each of the four read-out warps
+
+enum : int { EPI_STORE = 0, EPI_ADD_F32 = 1, EPI_GATED = 2 };
+
+__device__ __forceinline__ float silu_times(float g, float u) {
+  const float e = __expf(-fabsf(g));
+  const float r = __fdividef(1.0f, 1.0f + e);
+  return g * (g >= 0.f ? r : e * r) * u;
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Returns when at most `Pending` of this thread's bulk groups still read their shared-memory source.
+template <int Pending> __device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(Pending) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// The 16-byte piece `piece` (0..7) of row `row` (0..31) in a 128-byte-swizzled buffer of 32 rows x 128 bytes.
+__device__ __forceinline__ uint4* swizzled_piece(unsigned char* buffer, int row, int piece) {
+  return reinterpret_cast<uint4*>(buffer + row * 128 + ((piece ^ (row & 7)) << 4));
+}
+
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 packed;
+  __nv_bfloat162* two = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) two[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  return packed;
+}
+
+template <int STAGES, int EPILOGUE, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const __grid_constant__ CUtensorMap map_out, int through_tma, OutT* __restrict__ out, int M, int N, int K,
+                 int* __restrict__ error_flag) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACCUMULATORS], acc_empty[ACCUMULATORS];
+  __shared__ unsigned tmem_base_s;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_rank();                 // 0: issues the MMAs
+  const int pair_index = (int)cluster_id_x(), pairs = (int)(gridDim.x / 2);
+  const int tiles_m = (M + TILE - 1) / TILE, tiles_n = (N + TILE - 1) / TILE;
+  const int n_tiles = tiles_m * tiles_n;
+  const int num_k = (K + BK - 1) / BK;
+
+  if (warp == 0 && lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);            // the even block's own announcement; both blocks' bytes are counted on it
+      mbar_init(&empty_bar[s], 1);           // one commit of the even block's MMA thread
+    }
+#pragma unroll
+    for (int b = 0; b < ACCUMULATORS; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);           // four read-out warps in each block
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ACCUMULATORS * TILE) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tmem_fence_before();
+  __syncthreads();
+  cluster_sync_all();                        // the other block's barriers exist before anything arrives on them
+  tmem_fence_after();
+  const unsigned tmem_base = tmem_base_s;
+
+  grid_dependency_wait();          // X (and, for the adding epilogue, out) come from earlier kernels
+  grid_dependency_launch();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---------------- producer: this block's halves, one running count of k-blocks over all tiles of the pair
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair_index; tile < n_tiles && ok; tile += pairs) {
+        const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+        const int x_row = tile_m * TILE + (int)rank * HALF, w_row = tile_n * TILE + (int)rank * HALF;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int stage = it % STAGES;
+          const unsigned phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, error_flag, 1))) break;
+          unsigned char* a_s = smem + (size_t)stage * STAGE_BYTES;
+          unsigned char* b_s = a_s + HALF * BK * 2;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          const unsigned full = address_in_rank(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(a_s, &map_x, full, kb * BK, x_row);
+          tma_load_2d_pair(b_s, &map_w, full, kb * BK, w_row);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---------------- MMA issue for the pair
+      constexpr unsigned idesc = umma_idesc(TILE, TILE);
+      int it = 0, done = 0;
+      bool ok = true;
+      for (int tile = pair_index; tile < n_tiles && ok; tile += pairs, ++done) {
+        const int buf = done % ACCUMULATORS;
+        if (!(ok = mbar_wait(&acc_empty[buf], ((done / ACCUMULATORS) & 1) ^ 1, error_flag, 4))) break;
+        tmem_fence_after();
+        const unsigned accumulator = tmem_base + buf * TILE;
+        for (int kb = 0; kb < num_k; ++kb, ++it) {
+          const int stage = it % STAGES;
+          const unsigned phase = (it / STAGES) & 1;
+          if (!(ok = mbar_wait(&full_bar[stage], phase, error_flag, 2))) break;
+          tmem_fence_after();
+          unsigned char* a_s = smem + (size_t)stage * STAGE_BYTES;
+          unsigned char* b_s = a_s + HALF * BK * 2;
+          const uint64_t a_desc = umma_desc(a_s), b_desc = umma_desc(b_s);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)     // 16 elements (32 bytes) further inside the swizzled row: +2 units
+            umma_bf16_pair(accumulator, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(&empty_bar[stage]);      // both blocks' stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit_pair(&acc_full[buf]);   // the accumulator is complete in both blocks
+      }
+    }
+  } else {
+    // ---------------- read-out: warps 2..5 own the tensor-memory lane quarters 2, 3, 0, 1 of this block
+    const int quarter = warp & 3;
+    unsigned char* out_s = smem + (size_t)STAGES * STAGE_BYTES;
+    int done = 0, stores = 0;
+    bool ok = true;
+    for (int tile = pair_index; tile < n_tiles; tile += pairs, ++done) {
+      const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+      const int buf = done % ACCUMULATORS;
+      const int row = tile_m * TILE + (int)rank * HALF + quarter * 32 + lane;
+      ok = ok && mbar_wait(&acc_full[buf], (done / ACCUMULATORS) & 1, error_flag, 3);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tmem_fence_after();
+      const unsigned lanes = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * TILE);
+      if (through_tma) {
+        // 128 bytes of results per row at a time: 64 bfloat16 (from 64 accumulator columns, or 128 for the gated
+        // form) or 32 float32
+        constexpr int ACC_COLS = EPILOGUE == EPI_GATED ? 128 : sizeof(OutT) == 2 ? 64 : 32;
+        constexpr int OUT_COLS = 128 / (int)sizeof(OutT);
+        const int out_row = tile_m * TILE + (int)rank * HALF + quarter * 32;
+#pragma unroll 1
+        for (int c = 0; c < TILE; c += ACC_COLS, ++stores) {
+          unsigned char* buffer = out_s + (quarter * 2 + (stores & 1)) * OUT_BUFFER;
+          if (lane == 0) bulk_wait_read<1>();          // the store that last read this buffer is through with it
+          __syncwarp();
+#pragma unroll
+          for (int part = 0; part < ACC_COLS / 32; ++part) {
+            float v[32];
+            tmem_load_32(lanes + (unsigned)(c + 32 * part), v);
+            if (EPILOGUE == EPI_GATED) {
+              // columns 16 j .. 16 j + 7 are gate rows, the next eight the same up rows: 32 columns give 16 results
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                float r[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[j] = silu_times(v[16 * h + j], v[16 * h + 8 + j]);
+                *swizzled_piece(buffer, lane, 2 * part + h) = pack8(r);
+              }
+            } else if (sizeof(OutT) == 2) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) *swizzled_piece(buffer, lane, 4 * part + i) = pack8(v + 8 * i);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                *swizzled_piece(buffer, lane, i) = make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]),
+                                                              __float_as_uint(v[4 * i + 2]), __float_as_uint(v[4 * i + 3]));
+            }
+          }
+          fence_async_shared();
+          __syncwarp();
+          if (lane == 0) {
+            const int x = (tile_n * TILE + c) / (EPILOGUE == EPI_GATED ? 2 : 1);
+            if (x < (EPILOGUE == EPI_GATED ? N / 2 : N) && out_row < M) {
+              if (EPILOGUE == EPI_ADD_F32) tma_add_2d(&map_out, buffer, x, out_row);
+              else tma_store_2d(&map_out, buffer, x, out_row);
+            }
+            bulk_commit();
+          }
+          (void)OUT_COLS;
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < TILE; c += 32) {
+          float v[32];
+          tmem_load_32(lanes + (unsigned)c, v);
+          const int col = tile_n * TILE + c;
+          if (row >= M || col >= N) continue;
+          if (EPILOGUE == EPI_GATED) {
+            OutT* dst = out + (size_t)row * (N / 2) + col / 2;
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (col + 16 * (i >> 3) < N) dst[i] = from_float<OutT>(silu_times(v[16 * (i >> 3) + (i & 7)], v[16 * (i >> 3) + 8 + (i & 7)]));
+          } else if (EPILOGUE == EPI_ADD_F32) {
+            float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col + i < N) dst[i] += v[i];
+          } else {
+            OutT* dst = out + (size_t)row * N + col;
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col + i < N) dst[i] = from_float<OutT>(v[i]);
+          }
+        }
+      }
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_in_cluster(address_in_rank(smem_u32(&acc_empty[buf]), 0));   // may be overwritten
+    }
+    if (lane == 0) bulk_wait_all();          // this warp's stores have been written before the block ends
+  }
+
+  // Nobody leaves, and no tensor memory is freed, while the other block may still read this block's shared
+  // memory, write its tensor memory or arrive on its barriers.
+  tmem_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tmem_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ACCUMULATORS * TILE) : "memory");
+  }
+}
+
+// A [rows, K] bfloat16 row-major matrix seen by TMA as boxes of 64 k x 128 rows, 128-byte swizzled.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)HALF};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The output [rows, cols] seen by TMA as boxes of 32 rows x 128 bytes, 128-byte swizzled.
+static bool make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool float32) {
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
+  const int size = float32 ? 4 : 2;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * size};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / size), 32};
+  const cuuint32_t elem[2] = {1, 1};
+  return encode(map, float32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box,
+                elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int STAGES, int EPILOGUE, typename OutT>
+int launch(const void* X, const void* W, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
+  CUtensorMap map_x, map_w, map_out;
+  MS_REQUIRE(make_map(&map_x, X, M, K) && make_map(&map_w, W, N, K),
+             "gemm_pair: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
+  const int out_cols = EPILOGUE == EPI_GATED ? N / 2 : N;
+  const int through_tma = ((size_t)out_cols * sizeof(OutT)) % 16 == 0 && (uintptr_t)out % 16 == 0;
+  if (through_tma)
+    MS_REQUIRE(make_out_map(&map_out, out, M, out_cols, sizeof(OutT) == 4),
+               "gemm_pair: cuTensorMapEncodeTiled failed for the output (M %d N %d)", M, out_cols);
+  else
+    map_out = map_x;               // not used
+  auto kernel = gemm_pair_kernel<STAGES, EPILOGUE, OutT>;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + OUT_BYTES + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) MS_FAIL("gemm_pair: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+    configured = true;
+  }
+  static int sms = 0;
+  if (sms == 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 2;
+  }
+  const long long tiles = (long long)((N + TILE - 1) / TILE) * ((M + TILE - 1) / TILE);
+  MS_REQUIRE(tiles <= 1073741823LL, "gemm_pair: %lld tiles in one launch is too many", tiles);
+  const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+  config.blockDim = dim3(THREADS, 1, 1);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[2];
+  attribute[0].id = cudaLaunchAttributeClusterDimension;
+  attribute[0].val.clusterDim.x = 2;
+  attribute[0].val.clusterDim.y = 1;
+  attribute[0].val.clusterDim.z = 1;
+  attribute[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // as ms::launch gives every kernel
+  attribute[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = dependent_launch_enabled() ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_out, through_tma, (OutT*)out, M, N, K, error_flag);
+  if (e != cudaSuccess) MS_FAIL("gemm_pair: launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+}  // namespace pair
+}  // namespace ms
+
+using namespace ms;
+
+// X [M, K], W [N, K] bfloat16 (K a multiple of 8, both 16-byte aligned):
+//   epilogue 0: out [M, N] stored as bfloat16 (out_dtype 1) or float32 (out_dtype 0);
+//   epilogue 1: added in place into the float32 matrix out [M, N];
+//   epilogue 2: W holds eight gate rows, then the same eight up rows, and so on (N a multiple of 16);
+//               out [M, N / 2] bfloat16 = silu(gate) * up.
+// error_flag: one int on the device, zero before the first call; a kernel that gave up waiting writes a
+// non-zero code there (1 producer, 2 MMA issue, 3 read-out, 4 accumulator), which the caller checks when it
+// synchronises.
+MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtype, int epilogue, int M, int N, int K,
+                           int* error_flag, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  MS_REQUIRE(K > 0 && K % 8 == 0, "gemm_pair: inner size %d is not a multiple of 8", K);
+  MS_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_pair: operands must be 16-byte aligned");
+  MS_REQUIRE(error_flag != nullptr, "gemm_pair: an error flag on the device is required");
+  constexpr int STAGES = 6;
+  if (epilogue == pair::EPI_ADD_F32) {
+    MS_REQUIRE(out_dtype == MS_F32, "gemm_pair: the adding epilogue works on a float32 matrix");
+    return pair::launch<STAGES, pair::EPI_ADD_F32, float>(X, W, out, M, N, K, error_flag, stream);
+  }
+  if (epilogue == pair::EPI_GATED) {
+    MS_REQUIRE(out_dtype == MS_BF16 && N % 16 == 0, "gemm_pair: the gated epilogue stores bfloat16 and wants N %d a multiple of 16", N);
+    return pair::launch<STAGES, pair::EPI_GATED, __nv_bfloat16>(X, W, out, M, N, K, error_flag, stream);
+  }
+  MS_REQUIRE(epilogue == pair::EPI_STORE, "gemm_pair: unknown epilogue %d", epilogue);
+  if (out_dtype == MS_BF16) return pair::launch<STAGES, pair::EPI_STORE, __nv_bfloat16>(X, W, out, M, N, K, error_flag, stream);
+  if (out_dtype == MS_F32) return pair::launch<STAGES, pair::EPI_STORE, float>(X, W, out, M, N, K, error_flag, stream);
+  MS_FAIL("gemm_pair: unknown output type code %d", out_dtype);
+}

@@ -480,6 +480,25 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add
                                      _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
 
 
+def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: bool = False, gated: bool = False) -> None:
+    """``out = x @ weight^T`` by the kernel in which two thread blocks share each 256 x 256 tile (tcgen05 with
+    ``cta_group::2``).  ``add``: ``out += ...`` on a float32 ``out``.  ``gated``: ``weight`` is
+    :func:`interleave_gate_up` of a gate and an up projection and ``out [M, N / 2] = silu(gate) * up``.
+
+    bfloat16 operands with an inner size that is a multiple of 8; meant for 256 rows and more.
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, (n, k))
+    if gated:
+        _want(out, "out", torch.bfloat16, (m, n // 2))
+    else:
+        _want(out, "out", torch.float32 if add else None, (m, n))
+    _check(library().ms_gemm_pair(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(2 if gated else 1 if add else 0),
+                                  _i(m), _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
+
+
 _stream_buffers: dict = {}
 
 # Products of few rows (decode steps) read every weight once; which kernel streams a given weight fastest

@@ -656,6 +656,31 @@ def test_linear_tcgen05(kernels, m, n, k, out_dtype, add):
     assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
 
 
+@pytest.mark.parametrize("m,n,k,out_dtype,mode", [
+    (256, 256, 64, torch.bfloat16, "store"), (130, 264, 72, torch.bfloat16, "store"), (1, 40, 8, torch.float32, "store"),
+    (300, 331, 200, torch.float32, "store"), (2048, 4096, 2048, torch.bfloat16, "store"), (257, 6144, 520, torch.bfloat16, "store"),
+    (5000, 2048, 256, torch.bfloat16, "store"), (512, 2048, 6144, torch.float32, "add"), (150, 96, 224, torch.float32, "add"),
+    (2048, 12288, 2048, torch.bfloat16, "gated"), (300, 656, 136, torch.bfloat16, "gated"), (40, 16, 64, torch.bfloat16, "gated")])
+def test_linear_pair(kernels, m, n, k, out_dtype, mode):
+    """The product in which two thread blocks share a 256 x 256 tile (tcgen05 with cta_group::2): whole and ragged
+    tiles, more tiles than pairs of multiprocessors, every epilogue, no wait given up."""
+    x, w = rand((m, k), torch.bfloat16, 48, 0.5), rand((n, k), torch.bfloat16, 49, 0.1)
+    expected = x.double() @ w.double().T
+    if mode == "add":
+        out = rand((m, n), torch.float32, 50)
+        expected = expected + out.double()
+    elif mode == "gated":
+        out = torch.full((m, n // 2), 7.0, dtype=out_dtype).cuda()
+        blocks = expected.view(m, n // 16, 2, 8)
+        expected = (torch.nn.functional.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(m, n // 2)
+    else:
+        out = torch.full((m, n), 7.0, dtype=out_dtype).cuda()
+    kernels.linear_pair(x, w, out, add=mode == "add", gated=mode == "gated")
+    kernels.check_device_errors(x.device)
+    bound = 1e-3 if out_dtype == torch.float32 else 1.5e-2
+    assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)
+
+
 def records_tensor(rows):
     words = [struct.unpack("<8i", struct.pack("<ffiIIiii", t, p, k, seed & 0xFFFFFFFF, seed >> 32, 0, 0, 0))
              for (t, p, k, seed) in rows]
