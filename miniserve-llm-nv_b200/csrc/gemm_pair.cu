@@ -28,7 +28,7 @@
 //
 // Every wait on an mbarrier is bounded: a wait that does not finish within the limit sets the error flag that the
 // host checks, and the kernel drains and returns (tensor memory is freed on every path; both blocks meet before).
-#include "tcgen05.cuh"
+#include "wide_common.cuh"
 
 namespace ms {
 namespace pair {
@@ -46,11 +46,8 @@ constexpr int OUT_BYTES = 4 * 2 * OUT_BUFFER;      // two such buffers for each 
 
 enum : int { EPI_STORE = 0, EPI_ADD_F32 = 1, EPI_GATED = 2 };
 
-__device__ __forceinline__ float silu_times(float g, float u) {
-  const float e = __expf(-fabsf(g));
-  const float r = __fdividef(1.0f, 1.0f + e);
-  return g * (g >= 0.f ? r : e * r) * u;
-}
+using wide::round_bf16;
+using wide::silu_times;
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -204,11 +201,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             tmem_load_32(lanes + (unsigned)(c + 32 * part), v);
             if (EPILOGUE == EPI_GATED) {
               // columns 16 j .. 16 j + 7 are gate rows, the next eight the same up rows: 32 columns give 16 results
+              // (both rounded to bfloat16 first, as the separate activation kernel finds them)
 #pragma unroll
               for (int h = 0; h < 2; ++h) {
                 float r[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) r[j] = silu_times(v[16 * h + j], v[16 * h + 8 + j]);
+                for (int j = 0; j < 8; ++j) r[j] = silu_times(round_bf16(v[16 * h + j]), round_bf16(v[16 * h + 8 + j]));
                 *swizzled_piece(buffer, lane, 2 * part + h) = pack8(r);
               }
             } else if (sizeof(OutT) == 2) {
@@ -244,7 +242,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             OutT* dst = out + (size_t)row * (N / 2) + col / 2;
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              if (col + 16 * (i >> 3) < N) dst[i] = from_float<OutT>(silu_times(v[16 * (i >> 3) + (i & 7)], v[16 * (i >> 3) + 8 + (i & 7)]));
+              if (col + 16 * (i >> 3) < N) dst[i] = from_float<OutT>(silu_times(round_bf16(v[16 * (i >> 3) + (i & 7)]), round_bf16(v[16 * (i >> 3) + 8 + (i & 7)])));
           } else if (EPILOGUE == EPI_ADD_F32) {
             float* dst = reinterpret_cast<float*>(out) + (size_t)row * N + col;
 #pragma unroll
@@ -276,42 +274,53 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   }
 }
 
-// A [rows, K] bfloat16 row-major matrix seen by TMA as boxes of 64 k x 128 rows, 128-byte swizzled.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int K) {
-  EncodeTiled encode = encode_tiled();
-  if (encode == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)HALF};
-  const cuuint32_t elem[2] = {1, 1};
-  return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-// The output [rows, cols] seen by TMA as boxes of 32 rows x 128 bytes, 128-byte swizzled.
-static bool make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool float32) {
-  EncodeTiled encode = encode_tiled();
-  if (encode == nullptr) return false;
+// The output [rows, cols] seen by TMA as boxes of 32 rows x 128 bytes, 128-byte swizzled.  Kept like the operands'
+// maps (wide::cached_map): a step's buffers come back at the same addresses.
+struct OutKey {
+  const void* base;
+  int rows, cols, size;
+  bool operator==(const OutKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && size == o.size; }
+};
+struct OutKeyHash {
+  size_t operator()(const OutKey& k) const {
+    return std::hash<const void*>()(k.base) ^ ((size_t)k.rows * 1000003u) ^ ((size_t)k.cols * 7919u) ^ (size_t)k.size;
+  }
+};
+static bool out_map(CUtensorMap* map, void* base, int rows, int cols, bool float32) {
+  static std::mutex mutex;
+  static std::unordered_map<OutKey, CUtensorMap, OutKeyHash> cache;
+  std::lock_guard<std::mutex> guard(mutex);
   const int size = float32 ? 4 : 2;
+  const OutKey key{base, rows, cols, size};
+  auto found = cache.find(key);
+  if (found != cache.end()) {
+    *map = found->second;
+    return true;
+  }
+  EncodeTiled encode = encode_tiled();
+  if (encode == nullptr) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)cols * size};
   const cuuint32_t box[2] = {(cuuint32_t)(128 / size), 32};
   const cuuint32_t elem[2] = {1, 1};
-  return encode(map, float32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box,
-                elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (encode(map, float32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box,
+             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *map);
+  return true;
 }
 
 template <int STAGES, int EPILOGUE, typename OutT>
 int launch(const void* X, const void* W, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
   CUtensorMap map_x, map_w, map_out;
-  MS_REQUIRE(make_map(&map_x, X, M, K) && make_map(&map_w, W, N, K),
+  MS_REQUIRE(wide::cached_map(&map_x, X, M, K, HALF) && wide::cached_map(&map_w, W, N, K, HALF),
              "gemm_pair: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
   const int out_cols = EPILOGUE == EPI_GATED ? N / 2 : N;
   const int through_tma = ((size_t)out_cols * sizeof(OutT)) % 16 == 0 && (uintptr_t)out % 16 == 0;
   if (through_tma)
-    MS_REQUIRE(make_out_map(&map_out, out, M, out_cols, sizeof(OutT) == 4),
+    MS_REQUIRE(out_map(&map_out, out, M, out_cols, sizeof(OutT) == 4),
                "gemm_pair: cuTensorMapEncodeTiled failed for the output (M %d N %d)", M, out_cols);
   else
     map_out = map_x;               // not used

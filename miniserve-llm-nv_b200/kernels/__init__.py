@@ -424,6 +424,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: 
         if choice == "wide":
             linear_wide(x, weight, out)
             return
+    if k % 8 == 0 and pair_preferred(x.device, m, n):
+        linear_pair(x, weight, out)
+        return
     if USE_TCGEN05_GEMM and m >= 128 and k % 8 == 0:
         linear_tcgen05(x, weight, out)
         return
@@ -433,9 +436,32 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: 
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
 
 
-# Products of 128 rows and more go to cuBLAS unless this is set (environment MINISERVE_B200_TCGEN05_GEMM=1):
-# the library's own tcgen05 kernel is correct but reaches 60-75 % of cuBLAS' speed so far.
+# Products of many rows (prompt portions).  The kernel in which two thread blocks share a 256 x 256 tile
+# (linear_pair) is level with cuBLAS where its tiles fill the pairs of multiprocessors (measured at 2,048 rows:
+# 29.3 / 17.7 / 76.5 / 39.3 us against 29.7 / 17.8 / 76.2 / 37.8 us for the four products of a Qwen3-1.7B layer), and
+# it can apply the gated activation as it stores, which the library cannot.  With few tiles, or a last round of
+# tiles that leaves most pairs idle, cuBLAS' smaller tiles win, so those shapes stay there
+# (MINISERVE_B200_PAIR_GEMM=0: all of them do).  The one-block tcgen05 kernel (linear_tcgen05) reaches 77-92 % of
+# cuBLAS and runs only on request (MINISERVE_B200_TCGEN05_GEMM=1).
+USE_PAIR_GEMM = __import__("os").environ.get("MINISERVE_B200_PAIR_GEMM", "1") == "1"
 USE_TCGEN05_GEMM = __import__("os").environ.get("MINISERVE_B200_TCGEN05_GEMM", "0") == "1"
+PAIR_MIN_FILL = 0.8            # of the pairs' time in use, by the count of tiles
+
+
+def pair_fill(device: torch.device, m: int, n: int) -> float:
+    """The share of the pairs' time that the 256 x 256 tiles of an ``m x n`` product keep busy: tiles / (rounds x pairs)."""
+    key = torch.device(device).index or 0
+    if key not in _multiprocessors:
+        _multiprocessors[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    pairs = max(_multiprocessors[key] // 2, 1)
+    tiles = ((m + 255) // 256) * ((n + 255) // 256)
+    return tiles / (((tiles + pairs - 1) // pairs) * pairs)
+
+
+def pair_preferred(device: torch.device, m: int, n: int, gated: bool = False) -> bool:
+    """Whether a bfloat16 product of ``m`` rows with an ``n``-row weight goes to :func:`linear_pair`.  The gated form
+    also saves the activation kernel and its traffic, so it is taken at a lower fill."""
+    return USE_PAIR_GEMM and m >= 256 and pair_fill(device, m, n) >= (0.6 if gated else PAIR_MIN_FILL)
 
 # Prompt portions in bfloat16 run the tcgen05 attention kernel where it takes the sizes (head size 64 or 128,
 # group size dividing 128, pages of 8..128 tokens); MINISERVE_B200_TCGEN05_ATTENTION=0 keeps them on the
@@ -840,6 +866,9 @@ def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats
         return
     if x.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and _gated_choice(x, weight) == "wide":
         linear_wide(x, weight, out, gated=True)
+        return
+    if x.dtype == torch.bfloat16 and k % 8 == 0 and pair_preferred(x.device, m, two_i, gated=True):
+        linear_pair(x, weight, out, gated=True)      # many rows: the activation is applied as the tiles are stored
         return
     gate_up = torch.empty((m, two_i), dtype=x.dtype, device=x.device)
     linear(x, weight, gate_up)

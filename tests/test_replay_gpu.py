@@ -142,6 +142,44 @@ def test_layers_of_real_size(real_model, dtype, cutting):
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
 
 
+@pytest.mark.parametrize("cutting", ["whole", "two portions"])
+def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
+    """A prompt of 2,100 tokens at Qwen3-1.7B's layer sizes in bfloat16: at this length every product of a layer
+    goes to the kernel in which two thread blocks share a tile (the gate/up product with the activation applied as
+    it stores), the last row tile is ragged, and the attention walks over 33 pages; against the plain logits at a
+    few positions, among them both sides of the edges of row tiles and portions."""
+    import plain_qwen3 as plain
+    from miniserve_b200 import kernels
+
+    calls = {"plain": 0, "gated": 0}
+    inner = kernels.linear_pair
+
+    def counted(x, weight, out, add=False, gated=False):
+        calls["gated" if gated else "plain"] += 1
+        return inner(x, weight, out, add=add, gated=gated)
+
+    monkeypatch.setattr(kernels, "linear_pair", counted)
+    tokens = helpers.random_tokens(REAL["vocab_size"], 2100, seed=77)
+    wanted = [0, 255, 256, 1099, 1100, 2047, 2048, 2099]
+    config, weights = plain.load_folder(real_model["folder"], torch.float64)
+    expected = plain.plain_logits(tokens, weights, config, rows=wanted)
+    if cutting == "whole":
+        steps = [{"step": 0, "entries": [{"id": "long", "tokens": tokens, "want": wanted}], "end": ["long"]}]
+    else:
+        steps = [{"step": 0, "entries": [{"id": "long", "tokens": tokens[:1100], "want": [w for w in wanted if w < 1100]}], "end": []},
+                 {"step": 1, "entries": [{"id": "long", "tokens": tokens[1100:], "want": [w - 1100 for w in wanted if w >= 1100]}],
+                  "end": ["long"]}]
+    runtime = build(real_model["folder"], "bfloat16", 34, 64, max_model_len=2176)
+    got = helpers.collect(steps, replay(runtime, steps))
+    kernels.check_device_errors(torch.device("cuda"))
+    assert sorted(got["long"]) == wanted
+    check_against(request, got, lambda rid: expected, "bfloat16", wanted={"long": wanted})
+    layers = REAL["num_hidden_layers"]
+    # whole: q/k/v, o, gate/up and down of every layer; two portions: 1,100 rows fill the pairs of multiprocessors
+    # only with the gate/up product's tiles, 1,000 rows with those of q/k/v as well (the rest goes to cuBLAS)
+    assert calls == ({"plain": 3 * layers, "gated": layers} if cutting == "whole" else {"plain": layers, "gated": 2 * layers})
+
+
 def test_generation_at_real_size_graph_against_eager(real_model):
     """Greedy tokens at Qwen3-1.7B's layer sizes: replayed graphs with decoding one step ahead (the path the
     benchmark times) against eager steps, and the first tokens against the plain implementation."""
