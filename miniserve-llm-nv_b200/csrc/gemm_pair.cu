@@ -26,6 +26,16 @@
 // Epilogues: store (bfloat16 or float32), add into a float32 matrix in place, or the gated activation
 // silu(gate) * up of a weight whose rows are paired (eight gate rows, then the same eight up rows).
 //
+// A norm folded into the products around it, as in the few-row kernel (gemm_wide.cu): the residual epilogue adds its
+// results into the float32 stream, stores `stream * norm weight` as bfloat16 and leaves each row's sum of squares
+// over the tile's columns in `out_partials [column tiles, M]`; the product that follows (storing or gated) adds
+// those up in tile order and multiplies its own results by `1 / sqrt(total / K + eps)` before it rounds them:
+// (x w / rms(x)) W^T = (x w) W^T / rms(x).  In that epilogue a read-out warp works on 32 rows x 32 columns at a time:
+// the stream's box arrives by TMA in one of two buffers (asked for two boxes ahead, across tiles, so the first ones
+// come while the tile is still being accumulated), the results go from tensor memory (a row per thread) through a
+// third buffer, and then every instruction handles four whole rows of the box (eight lanes x 16 bytes each), so
+// that the stream and the next input are written in whole lines.
+//
 // Every wait on an mbarrier is bounded: a wait that does not finish within the limit sets the error flag that the
 // host checks, and the kernel drains and returns (tensor memory is freed on every path; both blocks meet before).
 #include "wide_common.cuh"
@@ -42,9 +52,23 @@ constexpr int THREADS = 192;                 // warps 0..5
 constexpr int ACCUMULATORS = 2;
 constexpr int STAGE_BYTES = 2 * HALF * BK * 2;     // this block's halves of X and W for one k-block
 constexpr int OUT_BUFFER = 32 * 128;               // 32 rows x 128 bytes: what one read-out warp stores at a time
-constexpr int OUT_BYTES = 4 * 2 * OUT_BUFFER;      // two such buffers for each of the four read-out warps
+// A read-out warp's buffers: two to store from; in the residual epilogue two boxes of the stream and one of results.
+__host__ __device__ constexpr int warp_bytes(int epilogue) { return (epilogue == 3 ? 3 : 2) * OUT_BUFFER; }
 
-enum : int { EPI_STORE = 0, EPI_ADD_F32 = 1, EPI_GATED = 2 };
+enum : int { EPI_STORE = 0, EPI_ADD_F32 = 1, EPI_GATED = 2, EPI_RESIDUAL = 3 };
+static_assert(warp_bytes(EPI_RESIDUAL) == 3 * OUT_BUFFER, "the residual epilogue has three buffers per warp");
+
+// What a norm folded into the products needs beside the operands.
+struct Fold {
+  const float* in_partials;     // [in_count, M] sums of squares left by the product before (or null)
+  int in_count;
+  float eps;
+  const void* norm_weight;      // [N], residual epilogue
+  int norm_dtype;
+  float* out_partials;          // [column tiles, M], residual epilogue
+  float* residual;              // [M, N], residual epilogue
+};
+
 
 using wide::round_bf16;
 using wide::silu_times;
@@ -70,6 +94,11 @@ __device__ __forceinline__ uint4* swizzled_piece(unsigned char* buffer, int row,
   return reinterpret_cast<uint4*>(buffer + row * 128 + ((piece ^ (row & 7)) << 4));
 }
 
+__device__ __forceinline__ void tma_load_box(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  mbar_expect_tx(bar, OUT_BUFFER);
+  tma_load_2d(smem_dst, map, bar, x, y);
+}
+
 __device__ __forceinline__ uint4 pack8(const float* v) {
   uint4 packed;
   __nv_bfloat162* two = reinterpret_cast<__nv_bfloat162*>(&packed);
@@ -81,11 +110,12 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 template <int STAGES, int EPILOGUE, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 const __grid_constant__ CUtensorMap map_out, int through_tma, OutT* __restrict__ out, int M, int N, int K,
-                 int* __restrict__ error_flag) {
+                 const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_residual,
+                 int through_tma, OutT* __restrict__ out, int M, int N, int K, Fold fold, int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACCUMULATORS], acc_empty[ACCUMULATORS];
+  __shared__ uint64_t residual_bar[4][2];      // residual epilogue: a read-out warp's two boxes of the stream
   __shared__ unsigned tmem_base_s;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,6 +136,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 8);           // four read-out warps in each block
     }
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mbar_init(&residual_bar[w >> 1][w & 1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -175,6 +207,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     unsigned char* out_s = smem + (size_t)STAGES * STAGE_BYTES;
     int done = 0, stores = 0;
     bool ok = true;
+    unsigned boxes = 0;                      // residual epilogue: boxes of the stream taken so far (they alternate between two buffers)
+    if (EPILOGUE == EPI_RESIDUAL && pair_index < n_tiles && lane == 0) {
+      // the stream's first two boxes are on the way while the first tile is being accumulated
+      for (int b = 0; b < 2; ++b)
+        tma_load_box(out_s + quarter * warp_bytes(EPILOGUE) + b * OUT_BUFFER, &map_residual, &residual_bar[quarter][b],
+                     (pair_index / tiles_m) * TILE + 32 * b, (pair_index % tiles_m) * TILE + (int)rank * HALF + quarter * 32);
+    }
     for (int tile = pair_index; tile < n_tiles; tile += pairs, ++done) {
       const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
       const int buf = done % ACCUMULATORS;
@@ -184,15 +223,93 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (!ok) break;
       tmem_fence_after();
       const unsigned lanes = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(buf * TILE);
-      if (through_tma) {
+      const int out_row = tile_m * TILE + (int)rank * HALF + quarter * 32;
+      // a norm folded in before this product: what is left of it is one factor per row
+      float scale = 1.f;
+      if (EPILOGUE != EPI_RESIDUAL && EPILOGUE != EPI_ADD_F32 && fold.in_partials != nullptr && row < M) {
+        float total = 0.f;
+        for (int i = 0; i < fold.in_count; ++i) total += fold.in_partials[(size_t)i * M + row];
+        scale = rsqrtf(total / (float)K + fold.eps);
+      }
+      if (EPILOGUE == EPI_RESIDUAL) {
+        unsigned char* mine = out_s + quarter * warp_bytes(EPILOGUE);
+        unsigned char* results = mine + 2 * OUT_BUFFER;
+        const int group = lane >> 3, piece = lane & 7;       // this lane's row of every four, and its 16 bytes of a row
+        float squares[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) squares[i] = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < TILE; c += 32, ++boxes) {
+          const int b = boxes & 1;
+          unsigned char* stream = mine + b * OUT_BUFFER;
+          float v[32];
+          tmem_load_32(lanes + (unsigned)c, v);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            *reinterpret_cast<float4*>(swizzled_piece(results, lane, i)) = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          ok = mbar_wait(&residual_bar[quarter][b], (boxes >> 1) & 1, error_flag, 5);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          __syncwarp();                                      // every lane's results are in the buffer
+          const int col = tile_n * TILE + c + 4 * piece;
+          float4 w = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (col < N) {
+            if (fold.norm_dtype == MS_F32) {
+              w = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(fold.norm_weight) + col);
+            } else {
+              const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(fold.norm_weight) + col);
+              const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+              const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+              w = make_float4(lo.x, lo.y, hi.x, hi.y);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + group;
+            const float4 a = *reinterpret_cast<const float4*>(swizzled_piece(results, r, piece));
+            float4 t = *reinterpret_cast<const float4*>(swizzled_piece(stream, r, piece));
+            t.x += a.x; t.y += a.y; t.z += a.z; t.w += a.w;
+            squares[i] += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;       // (what lies beyond N or M is zero)
+            const int out_r = out_row + r;
+            if (out_r < M && col < N) {
+              *reinterpret_cast<float4*>(fold.residual + (size_t)out_r * N + col) = t;
+              uint2 next;
+              *reinterpret_cast<__nv_bfloat162*>(&next.x) = __floats2bfloat162_rn(t.x * w.x, t.y * w.y);
+              *reinterpret_cast<__nv_bfloat162*>(&next.y) = __floats2bfloat162_rn(t.z * w.z, t.w * w.w);
+              *reinterpret_cast<uint2*>(out + (size_t)out_r * N + col) = next;
+            }
+          }
+          __syncwarp();                                      // both buffers have been read
+          if (lane == 0) {
+            // the box after the next: of this tile, or of the pair's next tile
+            int next_tile = tile, next_c = c + 64;
+            if (next_c >= TILE) {
+              next_c -= TILE;
+              next_tile += pairs;
+            }
+            if (next_tile < n_tiles)
+              tma_load_box(stream, &map_residual, &residual_bar[quarter][b], (next_tile / tiles_m) * TILE + next_c,
+                           (next_tile % tiles_m) * TILE + (int)rank * HALF + quarter * 32);
+          }
+        }
+        if (!ok) break;
+        // a row's sums lie in the eight lanes of its group
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float total = squares[i];
+          total += __shfl_xor_sync(0xffffffffu, total, 1);
+          total += __shfl_xor_sync(0xffffffffu, total, 2);
+          total += __shfl_xor_sync(0xffffffffu, total, 4);
+          const int out_r = out_row + 4 * i + group;
+          if (piece == 0 && out_r < M) fold.out_partials[(size_t)tile_n * M + out_r] = total;
+        }
+      } else if (through_tma) {
         // 128 bytes of results per row at a time: 64 bfloat16 (from 64 accumulator columns, or 128 for the gated
         // form) or 32 float32
         constexpr int ACC_COLS = EPILOGUE == EPI_GATED ? 128 : sizeof(OutT) == 2 ? 64 : 32;
-        constexpr int OUT_COLS = 128 / (int)sizeof(OutT);
-        const int out_row = tile_m * TILE + (int)rank * HALF + quarter * 32;
 #pragma unroll 1
         for (int c = 0; c < TILE; c += ACC_COLS, ++stores) {
-          unsigned char* buffer = out_s + (quarter * 2 + (stores & 1)) * OUT_BUFFER;
+          unsigned char* buffer = out_s + quarter * warp_bytes(EPILOGUE) + (stores & 1) * OUT_BUFFER;
           if (lane == 0) bulk_wait_read<1>();          // the store that last read this buffer is through with it
           __syncwarp();
 #pragma unroll
@@ -206,17 +323,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               for (int h = 0; h < 2; ++h) {
                 float r[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) r[j] = silu_times(round_bf16(v[16 * h + j]), round_bf16(v[16 * h + 8 + j]));
+                for (int j = 0; j < 8; ++j) r[j] = silu_times(round_bf16(v[16 * h + j] * scale), round_bf16(v[16 * h + 8 + j] * scale));
                 *swizzled_piece(buffer, lane, 2 * part + h) = pack8(r);
               }
             } else if (sizeof(OutT) == 2) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] *= scale;
 #pragma unroll
               for (int i = 0; i < 4; ++i) *swizzled_piece(buffer, lane, 4 * part + i) = pack8(v + 8 * i);
             } else {
 #pragma unroll
               for (int i = 0; i < 8; ++i)
-                *swizzled_piece(buffer, lane, i) = make_uint4(__float_as_uint(v[4 * i]), __float_as_uint(v[4 * i + 1]),
-                                                              __float_as_uint(v[4 * i + 2]), __float_as_uint(v[4 * i + 3]));
+                *swizzled_piece(buffer, lane, i) = make_uint4(__float_as_uint(v[4 * i] * scale), __float_as_uint(v[4 * i + 1] * scale),
+                                                              __float_as_uint(v[4 * i + 2] * scale), __float_as_uint(v[4 * i + 3] * scale));
             }
           }
           fence_async_shared();
@@ -229,7 +348,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             }
             bulk_commit();
           }
-          (void)OUT_COLS;
         }
       } else {
 #pragma unroll 1
@@ -238,6 +356,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           tmem_load_32(lanes + (unsigned)c, v);
           const int col = tile_n * TILE + c;
           if (row >= M || col >= N) continue;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] *= scale;
           if (EPILOGUE == EPI_GATED) {
             OutT* dst = out + (size_t)row * (N / 2) + col / 2;
 #pragma unroll
@@ -313,19 +433,24 @@ static bool out_map(CUtensorMap* map, void* base, int rows, int cols, bool float
 }
 
 template <int STAGES, int EPILOGUE, typename OutT>
-int launch(const void* X, const void* W, void* out, int M, int N, int K, int* error_flag, cudaStream_t stream) {
-  CUtensorMap map_x, map_w, map_out;
+int launch(const void* X, const void* W, void* out, int M, int N, int K, const Fold& fold, float* residual, int* error_flag,
+           cudaStream_t stream) {
+  CUtensorMap map_x, map_w, map_out, map_residual;
   MS_REQUIRE(wide::cached_map(&map_x, X, M, K, HALF) && wide::cached_map(&map_w, W, N, K, HALF),
              "gemm_pair: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
   const int out_cols = EPILOGUE == EPI_GATED ? N / 2 : N;
   const int through_tma = ((size_t)out_cols * sizeof(OutT)) % 16 == 0 && (uintptr_t)out % 16 == 0;
-  if (through_tma)
+  map_out = map_residual = map_x;          // (where they are not used)
+  if (through_tma && EPILOGUE != EPI_RESIDUAL)
     MS_REQUIRE(out_map(&map_out, out, M, out_cols, sizeof(OutT) == 4),
                "gemm_pair: cuTensorMapEncodeTiled failed for the output (M %d N %d)", M, out_cols);
-  else
-    map_out = map_x;               // not used
+  if (EPILOGUE == EPI_RESIDUAL) {
+    MS_REQUIRE(through_tma && (uintptr_t)residual % 16 == 0,
+               "gemm_pair: the residual epilogue wants N %d a multiple of 8 and 16-byte aligned matrices", N);
+    MS_REQUIRE(out_map(&map_residual, residual, M, N, true), "gemm_pair: cuTensorMapEncodeTiled failed for the residual stream");
+  }
   auto kernel = gemm_pair_kernel<STAGES, EPILOGUE, OutT>;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + OUT_BYTES + 1024;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 4 * warp_bytes(EPILOGUE) + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -356,7 +481,7 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, int* er
   attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = dependent_launch_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_out, through_tma, (OutT*)out, M, N, K, error_flag);
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_out, map_residual, through_tma, (OutT*)out, M, N, K, fold, error_flag);
   if (e != cudaSuccess) MS_FAIL("gemm_pair: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -370,27 +495,45 @@ using namespace ms;
 //   epilogue 0: out [M, N] stored as bfloat16 (out_dtype 1) or float32 (out_dtype 0);
 //   epilogue 1: added in place into the float32 matrix out [M, N];
 //   epilogue 2: W holds eight gate rows, then the same eight up rows, and so on (N a multiple of 16);
-//               out [M, N / 2] bfloat16 = silu(gate) * up.
+//               out [M, N / 2] bfloat16 = silu(gate) * up;
+//   epilogue 3: residual [M, N] float32 += the product, in place; out [M, N] bfloat16 = residual * norm_weight
+//               (norm_weight [N] of type norm_dtype); out_partials [ms_gemm_pair_column_tiles(N), M] float32
+//               receives the rows' sums of squares over each tile's columns (N a multiple of 8).
+// in_partials [in_count, M] (epilogues 0 and 2; null: none): sums of squares of X's rows before they were scaled
+// by a norm weight; the results are multiplied by 1 / sqrt(total / K + eps) before they are rounded.
 // error_flag: one int on the device, zero before the first call; a kernel that gave up waiting writes a
-// non-zero code there (1 producer, 2 MMA issue, 3 read-out, 4 accumulator), which the caller checks when it
-// synchronises.
+// non-zero code there (1 producer, 2 MMA issue, 3 read-out, 4 accumulator, 5 residual box), which the caller
+// checks when it synchronises.
 MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtype, int epilogue, int M, int N, int K,
-                           int* error_flag, cudaStream_t stream) {
+                           const float* in_partials, int in_count, float eps, float* residual, const void* norm_weight,
+                           int norm_dtype, float* out_partials, int* error_flag, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
   MS_REQUIRE(K > 0 && K % 8 == 0, "gemm_pair: inner size %d is not a multiple of 8", K);
   MS_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_pair: operands must be 16-byte aligned");
   MS_REQUIRE(error_flag != nullptr, "gemm_pair: an error flag on the device is required");
-  constexpr int STAGES = 6;
+  MS_REQUIRE(in_partials == nullptr || (in_count > 0 && (epilogue == pair::EPI_STORE || epilogue == pair::EPI_GATED)),
+             "gemm_pair: row statistics go with the storing and the gated epilogue (count %d, epilogue %d)", in_count, epilogue);
+  constexpr int STAGES = 6, STAGES_RESIDUAL = 5;      // what fits beside the read-out warps' buffers
+  const pair::Fold fold{in_partials, in_count, eps, norm_weight, norm_dtype, out_partials, residual};
+  if (epilogue == pair::EPI_RESIDUAL) {
+    MS_REQUIRE(out_dtype == MS_BF16 && residual != nullptr && norm_weight != nullptr && out_partials != nullptr &&
+               (norm_dtype == MS_F32 || norm_dtype == MS_BF16),
+               "gemm_pair: the residual epilogue wants a float32 stream, a norm weight, a bfloat16 output and room for the sums");
+    return pair::launch<STAGES_RESIDUAL, pair::EPI_RESIDUAL, __nv_bfloat16>(X, W, out, M, N, K, fold, residual, error_flag, stream);
+  }
   if (epilogue == pair::EPI_ADD_F32) {
     MS_REQUIRE(out_dtype == MS_F32, "gemm_pair: the adding epilogue works on a float32 matrix");
-    return pair::launch<STAGES, pair::EPI_ADD_F32, float>(X, W, out, M, N, K, error_flag, stream);
+    return pair::launch<STAGES, pair::EPI_ADD_F32, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   }
   if (epilogue == pair::EPI_GATED) {
     MS_REQUIRE(out_dtype == MS_BF16 && N % 16 == 0, "gemm_pair: the gated epilogue stores bfloat16 and wants N %d a multiple of 16", N);
-    return pair::launch<STAGES, pair::EPI_GATED, __nv_bfloat16>(X, W, out, M, N, K, error_flag, stream);
+    return pair::launch<STAGES, pair::EPI_GATED, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   }
   MS_REQUIRE(epilogue == pair::EPI_STORE, "gemm_pair: unknown epilogue %d", epilogue);
-  if (out_dtype == MS_BF16) return pair::launch<STAGES, pair::EPI_STORE, __nv_bfloat16>(X, W, out, M, N, K, error_flag, stream);
-  if (out_dtype == MS_F32) return pair::launch<STAGES, pair::EPI_STORE, float>(X, W, out, M, N, K, error_flag, stream);
+  if (out_dtype == MS_BF16) return pair::launch<STAGES, pair::EPI_STORE, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
+  if (out_dtype == MS_F32) return pair::launch<STAGES, pair::EPI_STORE, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   MS_FAIL("gemm_pair: unknown output type code %d", out_dtype);
 }
+
+// Rows of `out_partials` that the residual epilogue writes for a weight of N rows.
+MS_EXPORT int ms_gemm_pair_column_tiles(int N) { return (N + pair::TILE - 1) / pair::TILE; }

@@ -399,7 +399,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: 
     if weight.shape[1] != k or tuple(out.shape) != (m, n):
         raise KernelError(f"linear: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
     if row_stats is not None:
-        linear_wide(x, weight, out, row_stats=row_stats)
+        if row_stats.per_row:
+            linear_pair(x, weight, out, row_stats=row_stats)
+        else:
+            linear_wide(x, weight, out, row_stats=row_stats)
         return
     if x.dtype == torch.float32:
         _want(x, "x", torch.float32)
@@ -458,6 +461,15 @@ def pair_fill(device: torch.device, m: int, n: int) -> float:
     return tiles / (((tiles + pairs - 1) // pairs) * pairs)
 
 
+def pair_rounds(device: torch.device, m: int, n: int) -> int:
+    """Tiles that the busiest pair of multiprocessors works on, one after the other, in an ``m x n`` product."""
+    key = torch.device(device).index or 0
+    if key not in _multiprocessors:
+        _multiprocessors[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    pairs = max(_multiprocessors[key] // 2, 1)
+    return (((m + 255) // 256) * ((n + 255) // 256) + pairs - 1) // pairs
+
+
 def pair_preferred(device: torch.device, m: int, n: int, gated: bool = False) -> bool:
     """Whether a bfloat16 product of ``m`` rows with an ``n``-row weight goes to :func:`linear_pair`.  The gated form
     also saves the activation kernel and its traffic, so it is taken at a lower fill."""
@@ -506,10 +518,13 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add
                                      _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
 
 
-def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: bool = False, gated: bool = False) -> None:
+def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: bool = False, gated: bool = False,
+                row_stats: Optional["RowStats"] = None) -> None:
     """``out = x @ weight^T`` by the kernel in which two thread blocks share each 256 x 256 tile (tcgen05 with
     ``cta_group::2``).  ``add``: ``out += ...`` on a float32 ``out``.  ``gated``: ``weight`` is
     :func:`interleave_gate_up` of a gate and an up projection and ``out [M, N / 2] = silu(gate) * up``.
+    ``row_stats`` (from :func:`linear_pair_residual`): ``x`` still lacks the division by its rows' root mean square,
+    and the results are multiplied by it before they are rounded.
 
     bfloat16 operands with an inner size that is a multiple of 8; meant for 256 rows and more.
     """
@@ -521,8 +536,44 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: b
         _want(out, "out", torch.bfloat16, (m, n // 2))
     else:
         _want(out, "out", torch.float32 if add else None, (m, n))
+    if row_stats is not None:
+        _want(row_stats.partials, "row_stats.partials", torch.float32)
+        if add or not row_stats.per_row or row_stats.partials.dim() != 2 or row_stats.partials.shape[1] != m \
+                or row_stats.partials.shape[0] < row_stats.count:
+            raise KernelError(f"linear_pair: row statistics of shape {tuple(row_stats.partials.shape)} for {m} rows, "
+                              f"{row_stats.count} tiles")
     _check(library().ms_gemm_pair(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(2 if gated else 1 if add else 0),
-                                  _i(m), _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
+                                  _i(m), _i(n), _i(k), _ptr(row_stats.partials if row_stats else None),
+                                  _i(row_stats.count if row_stats else 0), _f(row_stats.eps if row_stats else 0.0), None, None,
+                                  _i(0), None, _ptr(device_error_flag(x.device)), _stream()))
+
+
+def pair_column_tiles(n: int) -> int:
+    """Rows of ``partials`` that :func:`linear_pair_residual` writes for a weight of ``n`` rows."""
+    return (n + 255) // 256
+
+
+def linear_pair_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor,
+                         eps: float, x_next: torch.Tensor, partials: torch.Tensor) -> "RowStats":
+    """:func:`linear_wide_residual` for many rows, by the kernel of :func:`linear_pair`: ``residual += x @ weight^T``
+    (float32, in place), ``x_next = bfloat16(residual * norm_weight)`` and the rows' sums of squares, one row of
+    ``partials [>= pair_column_tiles(N), M]`` per 256 columns.  ``N`` a multiple of 8."""
+    m, k = x.shape
+    n = weight.shape[0]
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, (n, k))
+    _want(residual, "residual", torch.float32, (m, n))
+    _want(norm_weight, "norm_weight", None, (n,))
+    _want(x_next, "x_next", torch.bfloat16, (m, n))
+    _want(partials, "partials", torch.float32)
+    tiles = pair_column_tiles(n)
+    if n % 8 or partials.dim() != 2 or partials.shape[1] != m or partials.shape[0] < tiles:
+        raise KernelError(f"linear_pair_residual: weight {tuple(weight.shape)}, partials {tuple(partials.shape)} for {tiles} "
+                          f"tiles of {m} rows")
+    _check(library().ms_gemm_pair(_ptr(x), _ptr(weight), _ptr(x_next), _i(1), _i(3), _i(m), _i(n), _i(k), None, _i(0),
+                                  _f(0.0), _ptr(residual), _ptr(norm_weight), _i(_code(norm_weight.dtype)), _ptr(partials),
+                                  _ptr(device_error_flag(x.device)), _stream()))
+    return RowStats(partials, tiles, eps, per_row=True)
 
 
 _stream_buffers: dict = {}
@@ -740,14 +791,15 @@ def wide_supports(n: int, k: int) -> int:
 class RowStats:
     """What is still missing from activations whose norm is folded into the products around it: ``x`` holds
     ``residual * norm weight`` and every row has yet to be divided by the root of its mean square.
-    ``partials [count, 8]`` (float32) holds sums of squares of the residual's rows, one row of partial sums per
-    block of the product that wrote ``x``; the product that reads ``x`` adds them up in order and applies
+    ``partials`` (float32) holds sums of squares of the residual's rows, one row of partial sums per block (or
+    column tile) of the product that wrote ``x``: ``[count, 8]`` from the few-row product, ``[count, rows]`` from
+    the many-row one (``per_row``).  The product that reads ``x`` adds them up in order and applies
     ``1 / sqrt(total / size + eps)`` to its own results."""
 
-    __slots__ = ("partials", "count", "eps")
+    __slots__ = ("partials", "count", "eps", "per_row")
 
-    def __init__(self, partials: torch.Tensor, count: int, eps: float) -> None:
-        self.partials, self.count, self.eps = partials, count, eps
+    def __init__(self, partials: torch.Tensor, count: int, eps: float, per_row: bool = False) -> None:
+        self.partials, self.count, self.eps, self.per_row = partials, count, eps, per_row
 
 
 def wide_blocks(n: int, k: int) -> int:
@@ -811,13 +863,38 @@ def linear_wide_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.
     return RowStats(partials, blocks, eps)
 
 
+def residual_partials_shape(rows: int, n: int, k: int) -> tuple:
+    """The shape of the float32 ``partials`` that :func:`linear_residual` wants for ``rows`` rows and a weight ``[n, k]``."""
+    return (wide_blocks(n, k), 8) if rows <= SKINNY_MAX_ROWS else (pair_column_tiles(n), rows)
+
+
+def linear_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                    x_next: torch.Tensor, partials: torch.Tensor) -> RowStats:
+    """A product whose results join the residual stream, with the norm that follows folded in (where
+    :func:`fold_supported` said so): :func:`linear_wide_residual` for up to 8 rows, :func:`linear_pair_residual`
+    for many."""
+    if x.shape[0] <= SKINNY_MAX_ROWS:
+        return linear_wide_residual(x, weight, residual, norm_weight, eps, x_next, partials)
+    return linear_pair_residual(x, weight, residual, norm_weight, eps, x_next, partials)
+
+
 def fold_supported(rows: int, dtype: torch.dtype, producer: torch.Tensor, consumer: torch.Tensor,
                    consumer_gated: bool = False) -> bool:
     """Whether, in a step of ``rows`` rows, an RMSNorm between the product with the weight ``producer`` and the
-    one with ``consumer`` can be folded into the two (:func:`linear_wide_residual`, then ``row_stats``): bfloat16,
-    at most 8 rows, and both weights are ones that :func:`linear_wide` is (or would be) chosen for."""
-    if not FOLD_NORMS or dtype != torch.bfloat16 or not 0 < rows <= SKINNY_MAX_ROWS:
+    one with ``consumer`` can be folded into the two (:func:`linear_residual`, then ``row_stats``): bfloat16, and
+    either at most 8 rows and both weights ones that :func:`linear_wide` is (or would be) chosen for, or so many
+    rows that both products go to :func:`linear_pair`."""
+    if not FOLD_NORMS or dtype != torch.bfloat16 or rows <= 0:
         return False
+    if rows > SKINNY_MAX_ROWS:
+        if not FOLD_NORMS_MANY_ROWS or producer.shape[0] % 8 or producer.shape[1] % 8 or consumer.shape[1] % 8:
+            return False
+        # The folded epilogue moves 10 bytes per element against 2; it pays where a pair has a next tile to
+        # accumulate meanwhile (measured at Qwen3-1.7B sizes: 4,096 rows 39.3 against 46.1 us for the o projection and
+        # the norm kernel, 8,192 rows 71.9 against 89.4 us; 2,048 rows, one tile per pair, 25.8 against 26.1 us)
+        return (pair_preferred(producer.device, rows, producer.shape[0])
+                and pair_rounds(producer.device, rows, producer.shape[0]) >= 2
+                and pair_preferred(consumer.device, rows, consumer.shape[0], gated=consumer_gated))
     for weight, gated in ((producer, False), (consumer, consumer_gated)):
         n, k = weight.shape
         if k % 8 or wide_supports(n, k) != 2:
@@ -833,6 +910,7 @@ def fold_supported(rows: int, dtype: torch.dtype, producer: torch.Tensor, consum
 
 
 FOLD_NORMS = __import__("os").environ.get("MINISERVE_B200_FOLD_NORMS", "1") == "1"
+FOLD_NORMS_MANY_ROWS = __import__("os").environ.get("MINISERVE_B200_FOLD_NORMS_MANY_ROWS", "1") == "1"
 
 
 GATE_UP_BLOCK = 8    # rows of the gate projection beside as many of the up projection, for linear_wide(gated=True)
@@ -862,7 +940,10 @@ def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats
     two_i = weight.shape[0]
     _want(out, "out", x.dtype, (m, two_i // 2))
     if row_stats is not None:
-        linear_wide(x, weight, out, gated=True, row_stats=row_stats)
+        if row_stats.per_row:
+            linear_pair(x, weight, out, gated=True, row_stats=row_stats)
+        else:
+            linear_wide(x, weight, out, gated=True, row_stats=row_stats)
         return
     if x.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and _gated_choice(x, weight) == "wide":
         linear_wide(x, weight, out, gated=True)

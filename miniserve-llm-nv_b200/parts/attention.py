@@ -129,8 +129,8 @@ class Attention(Part):
                                     ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
         out = ctx.buffer("attention.out", (n, self.hidden_size), x.dtype)
         if fold is not None:
-            partials = ctx.buffer("attention.partials", (kernels.wide_blocks(*self.o_weight.shape), 8), torch.float32)
-            stats = kernels.linear_wide_residual(attended.view(n, n_q * d), self.o_weight, fold.residual, fold.weight,
+            partials = ctx.buffer("attention.partials", kernels.residual_partials_shape(n, *self.o_weight.shape), torch.float32)
+            stats = kernels.linear_residual(attended.view(n, n_q * d), self.o_weight, fold.residual, fold.weight,
                                                  fold.eps, out, partials)
             return FoldedInput(out, stats)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)

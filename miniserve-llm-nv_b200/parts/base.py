@@ -71,7 +71,7 @@ class StateNeed:
 class NormFold:
     """Handed to a mixer or feed-forward as ``fold=``: instead of returning its output, its last product adds it
     into ``residual`` (float32, in place) and prepares the input of the part behind the norm with ``weight`` and
-    ``eps`` (``kernels.linear_wide_residual``).  The part then returns a :class:`FoldedInput`."""
+    ``eps`` (``kernels.linear_residual``).  The part then returns a :class:`FoldedInput`."""
 
     residual: torch.Tensor
     weight: torch.Tensor

@@ -64,8 +64,8 @@ class GatedMLP(Part):
             hidden = ctx.buffer("gated_mlp.hidden", (n, self.intermediate_size), x.dtype)
             kernels.gated_up(x, self.gate_up_weight, hidden, row_stats=stats)
             if fold is not None:
-                partials = ctx.buffer("gated_mlp.partials", (kernels.wide_blocks(*self.down_weight.shape), 8), torch.float32)
-                stats = kernels.linear_wide_residual(hidden, self.down_weight, fold.residual, fold.weight, fold.eps, out,
+                partials = ctx.buffer("gated_mlp.partials", kernels.residual_partials_shape(n, *self.down_weight.shape), torch.float32)
+                stats = kernels.linear_residual(hidden, self.down_weight, fold.residual, fold.weight, fold.eps, out,
                                                      partials)
                 return FoldedInput(out, stats)
             kernels.linear(hidden, self.down_weight, out)

@@ -120,7 +120,7 @@ def gated_up(x, weight, out, row_stats=None):
 FOLD_BLOCKS = 3     # the plain stand-in leaves its sums of squares in this many rows, as a kernel of three blocks would
 
 
-def linear_wide_residual(x, weight, residual, norm_weight, eps, x_next, partials):
+def linear_residual(x, weight, residual, norm_weight, eps, x_next, partials):
     import miniserve_b200  # noqa: F401
     from miniserve_b200 import kernels
 
@@ -129,7 +129,7 @@ def linear_wide_residual(x, weight, residual, norm_weight, eps, x_next, partials
     partials.zero_()
     for block, columns in enumerate(torch.arange(residual.shape[1]).chunk(FOLD_BLOCKS)):
         partials[block, :residual.shape[0]] = residual[:, columns].double().pow(2).sum(dim=1).to(partials.dtype)
-    return kernels.RowStats(partials, FOLD_BLOCKS, eps)
+    return kernels.RowStats(partials, FOLD_BLOCKS, eps, per_row=partials.shape[1] != 8)
 
 
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
@@ -193,7 +193,8 @@ def install(monkeypatch) -> None:
                  "paged_attention", "linear", "gated_linear", "gated_up", "sample", "scale_softcap"):
         monkeypatch.setattr(kernels, name, globals()[name])
     monkeypatch.setattr(kernels, "attention_kernels", lambda *sizes: {"decode": "plain", "prompt": "plain"})
-    # norms folded into the products around them: offered for steps of up to eight rows, as on the device
-    monkeypatch.setattr(kernels, "linear_wide_residual", linear_wide_residual)
-    monkeypatch.setattr(kernels, "wide_blocks", lambda n, k: FOLD_BLOCKS)
-    monkeypatch.setattr(kernels, "fold_supported", lambda rows, dtype, producer, consumer, gated=False: 0 < rows <= 8)
+    # norms folded into the products around them: offered for steps of up to eight rows and for steps of many
+    # (here: 24 and more), as on the device, with the two layouts of the sums of squares
+    monkeypatch.setattr(kernels, "linear_residual", linear_residual)
+    monkeypatch.setattr(kernels, "residual_partials_shape", lambda rows, n, k: (FOLD_BLOCKS, 8 if rows <= 8 else rows))
+    monkeypatch.setattr(kernels, "fold_supported", lambda rows, dtype, producer, consumer, gated=False: 0 < rows <= 8 or rows >= 24)

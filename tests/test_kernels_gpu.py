@@ -595,6 +595,68 @@ def test_norm_folded_into_the_products_around_it(kernels, norm_dtype, m, hidden,
     assert torch.equal(alone[0][0], residual[row]) and torch.equal(alone[1][0], x_next[row]) and torch.equal(alone[3][0], out[row])
 
 
+@pytest.mark.parametrize("norm_dtype", DTYPES)
+@pytest.mark.parametrize("m,hidden,k,n_next,gated", [
+    (2048, 2048, 2048, 4096, False), (2100, 2048, 6144, 12288, True), (300, 1040, 200, 528, False), (257, 520, 136, 544, True),
+    (5000, 264, 64, 256, False)])
+def test_norm_folded_into_many_row_products(kernels, norm_dtype, m, hidden, k, n_next, gated):
+    """The same fold for many rows, in the kernel in which two thread blocks share a tile: the first product adds into
+    the float32 stream through shared memory (boxes fetched and stored by TMA), writes residual * norm weight and
+    one sum of squares per row and column tile; the second multiplies its results by the rows' factors.  Against
+    the four steps in float64; ragged rows and columns, more tiles than pairs of multiprocessors; and a row tile
+    alone gives the same bits as among others."""
+    eps = 1e-5
+    x, w = rand((m, k), torch.bfloat16, 80, 0.5), rand((hidden, k), torch.bfloat16, 81, 0.1)
+    residual0 = rand((m, hidden), torch.float32, 82, 2.0)
+    norm_w = (1 + rand((hidden,), torch.float32, 83, 0.1)).to(norm_dtype)
+    w_next = rand((n_next, hidden), torch.bfloat16, 84, 0.05)
+    if gated:
+        w_next = kernels.interleave_gate_up(w_next[:n_next // 2].contiguous(), w_next[n_next // 2:].contiguous())
+
+    def run(x_rows, residual_rows):
+        rows = x_rows.shape[0]
+        residual = residual_rows.clone()
+        x_next = torch.full((rows, hidden), 7.0, dtype=torch.bfloat16).cuda()
+        partials = torch.full(kernels.residual_partials_shape(rows, hidden, k), float("nan"), dtype=torch.float32).cuda()
+        stats = kernels.linear_residual(x_rows, w, residual, norm_w, eps, x_next, partials)
+        assert stats.per_row and stats.count == kernels.pair_column_tiles(hidden)
+        out = torch.full((rows, n_next // 2 if gated else n_next), 7.0, dtype=torch.bfloat16).cuda()
+        (kernels.gated_up if gated else kernels.linear)(x_next, w_next, out, row_stats=stats)
+        kernels.check_device_errors(x.device)
+        return residual, x_next, partials, out
+
+    residual, x_next, partials, out = run(x, residual0)
+    expected_residual = residual0.double() + x.double() @ w.double().T
+    assert torch.allclose(residual.double(), expected_residual, atol=1e-4, rtol=1e-5)
+    assert torch.allclose(x_next.double(), expected_residual * norm_w.double(), atol=1e-2, rtol=1e-2)
+    # (the sums are those of the stream as the kernel holds it, in float32)
+    squares = partials.double().sum(dim=0)
+    assert torch.allclose(squares, residual.double().pow(2).sum(dim=1), rtol=1e-5)
+    normed = (expected_residual * torch.rsqrt(expected_residual.pow(2).mean(dim=1, keepdim=True) + eps) * norm_w.double())
+    product = normed @ w_next.double().T
+    if gated:
+        product = product.bfloat16().double()
+        inter = n_next // 2
+        paired = product.view(m, inter // 8, 2, 8)
+        g, u = paired[:, :, 0].reshape(m, inter), paired[:, :, 1].reshape(m, inter)
+        product = g * torch.sigmoid(g) * u
+    assert torch.allclose(out.double(), product, atol=2e-2 * max(1.0, float(product.abs().max())), rtol=2e-2)
+    first = min(256, m) - 9
+    alone = run(x[first:first + 9].contiguous(), residual0[first:first + 9].contiguous())
+    assert torch.equal(alone[0], residual[first:first + 9]) and torch.equal(alone[1], x_next[first:first + 9])
+    assert torch.equal(alone[3], out[first:first + 9])
+
+
+def test_many_row_fold_is_offered_where_it_pays(kernels):
+    hidden, inter = 2048, 6144
+    o, gate_up = rand((hidden, hidden), torch.bfloat16, 1), rand((2 * inter, hidden), torch.bfloat16, 2)
+    assert kernels.fold_supported(4096, torch.bfloat16, o, gate_up, True)
+    assert not kernels.fold_supported(2048, torch.bfloat16, o, gate_up, True)      # one tile per pair: nothing to overlap with
+    assert not kernels.fold_supported(3072, torch.bfloat16, o, gate_up, True)      # 96 tiles of o on 74 pairs
+    assert not kernels.fold_supported(4096, torch.float32, o, gate_up, True)
+    assert not kernels.fold_supported(64, torch.bfloat16, o, gate_up, True)
+
+
 def test_linear_wide_refusals(kernels):
     x, w = rand((9, 64), torch.bfloat16, 58), rand((32, 64), torch.bfloat16, 59)
     with pytest.raises(kernels.KernelError, match="at most 8"):

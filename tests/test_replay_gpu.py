@@ -142,7 +142,7 @@ def test_layers_of_real_size(real_model, dtype, cutting):
     assert all(a.free_count == a.num_pages for a in runtime.manager.allocators)
 
 
-@pytest.mark.parametrize("cutting", ["whole", "two portions"])
+@pytest.mark.parametrize("cutting", ["whole", "whole, norms folded", "two portions"])
 def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     """A prompt of 2,100 tokens at Qwen3-1.7B's layer sizes in bfloat16: at this length every product of a layer
     goes to the kernel in which two thread blocks share a tile (the gate/up product with the activation applied as
@@ -151,19 +151,28 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     import plain_qwen3 as plain
     from miniserve_b200 import kernels
 
-    calls = {"plain": 0, "gated": 0}
-    inner = kernels.linear_pair
+    calls = {"plain": 0, "gated": 0, "residual": 0}
+    inner, inner_residual = kernels.linear_pair, kernels.linear_pair_residual
 
-    def counted(x, weight, out, add=False, gated=False):
+    def counted(x, weight, out, add=False, gated=False, row_stats=None):
         calls["gated" if gated else "plain"] += 1
-        return inner(x, weight, out, add=add, gated=gated)
+        return inner(x, weight, out, add=add, gated=gated, row_stats=row_stats)
+
+    def counted_residual(*args):
+        calls["residual"] += 1
+        return inner_residual(*args)
 
     monkeypatch.setattr(kernels, "linear_pair", counted)
+    monkeypatch.setattr(kernels, "linear_pair_residual", counted_residual)
+    if cutting == "whole, norms folded":
+        # as for prompts of 4,096 tokens and more, where a pair of multiprocessors has a next tile to accumulate
+        # while the longer epilogue of a folded norm runs
+        monkeypatch.setattr(kernels, "pair_rounds", lambda device, m, n: 2)
     tokens = helpers.random_tokens(REAL["vocab_size"], 2100, seed=77)
     wanted = [0, 255, 256, 1099, 1100, 2047, 2048, 2099]
     config, weights = plain.load_folder(real_model["folder"], torch.float64)
     expected = plain.plain_logits(tokens, weights, config, rows=wanted)
-    if cutting == "whole":
+    if cutting.startswith("whole"):
         steps = [{"step": 0, "entries": [{"id": "long", "tokens": tokens, "want": wanted}], "end": ["long"]}]
     else:
         steps = [{"step": 0, "entries": [{"id": "long", "tokens": tokens[:1100], "want": [w for w in wanted if w < 1100]}], "end": []},
@@ -175,9 +184,16 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     assert sorted(got["long"]) == wanted
     check_against(request, got, lambda rid: expected, "bfloat16", wanted={"long": wanted})
     layers = REAL["num_hidden_layers"]
-    # whole: q/k/v, o, gate/up and down of every layer; two portions: 1,100 rows fill the pairs of multiprocessors
-    # only with the gate/up product's tiles, 1,000 rows with those of q/k/v as well (the rest goes to cuBLAS)
-    assert calls == ({"plain": 3 * layers, "gated": layers} if cutting == "whole" else {"plain": layers, "gated": 2 * layers})
+    # whole: every product of a layer.  Two portions: 1,100 rows fill the pairs of multiprocessors only with the
+    # gate/up product's tiles, 1,000 rows with those of q/k/v as well (the rest goes to cuBLAS).  No norm is folded:
+    # at these lengths a pair has one tile of the o and down products, and nothing to overlap the longer epilogue with
+    if cutting == "whole":
+        assert calls == {"plain": 3 * layers, "gated": layers, "residual": 0}
+    elif cutting == "whole, norms folded":
+        # o and down (but for the last layer's) add into the stream and leave the next product's input
+        assert calls == {"plain": layers + 1, "gated": layers, "residual": 2 * layers - 1}
+    else:
+        assert calls == {"plain": layers, "gated": 2 * layers, "residual": 0}
 
 
 def test_generation_at_real_size_graph_against_eager(real_model):
