@@ -18,12 +18,12 @@ general attention kernel.
 
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Optional, Sequence, Union
 
 import torch
 
 from .. import kernels
-from .base import POSITIONS, FoldedInput, NormFold, PagedKVNeed, ParamSpec, Part, register_mixer
+from .base import POSITIONS, FoldedInput, NormFold, PagedKVNeed, ParamSpec, Part, ResidualAdd, register_mixer
 from .context import PagedKVView, StepContext
 from .spec import PartSpec
 
@@ -94,9 +94,10 @@ class Attention(Part):
         return self.o_weight
 
     # ------------------------------------------------------------------ work
-    def forward(self, x, ctx: StepContext, cache: PagedKVView, fold: Optional[NormFold] = None):
-        """``x``: the normed input, or a :class:`FoldedInput`.  With ``fold`` the output projection adds into the
-        residual stream and a :class:`FoldedInput` for the part behind the following norm is returned."""
+    def forward(self, x, ctx: StepContext, cache: PagedKVView, fold: Union[None, NormFold, ResidualAdd] = None):
+        """``x``: the normed input, or a :class:`FoldedInput`.  With a :class:`NormFold` the output projection adds
+        into the residual stream and a :class:`FoldedInput` for the part behind the following norm is returned;
+        with a :class:`ResidualAdd` it adds into the stream and nothing is returned."""
         stats = None
         if isinstance(x, FoldedInput):
             x, stats = x.x, x.stats
@@ -127,6 +128,9 @@ class Attention(Part):
                                     ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
                                     ctx.max_context_len, self.scale, self.window, attended,
                                     ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
+        if isinstance(fold, ResidualAdd):
+            kernels.linear_add(attended.view(n, n_q * d), self.o_weight, fold.residual)
+            return None
         out = ctx.buffer("attention.out", (n, self.hidden_size), x.dtype)
         if fold is not None:
             partials = ctx.buffer("attention.partials", kernels.residual_partials_shape(n, *self.o_weight.shape), torch.float32)

@@ -79,6 +79,16 @@ class NormFold:
 
 
 @dataclass
+class ResidualAdd:
+    """Handed to a mixer or feed-forward as ``fold=`` where the norm behind it is not folded but the part's last
+    product can add its results into ``residual`` (float32, in place) as it stores them
+    (``kernels.add_in_product_supported``): the part returns None, and the norm that follows reads the stream
+    alone instead of adding a separate output into it first."""
+
+    residual: torch.Tensor
+
+
+@dataclass
 class FoldedInput:
     """What a part receives as ``x`` where the norm before it was folded: ``x = residual * norm weight`` and the
     statistics that its first product completes the norm with (``kernels.RowStats``)."""

@@ -21,7 +21,7 @@ from typing import Any, Optional, Union
 import torch
 
 from .. import kernels
-from .base import FoldedInput, NormFold, register_block
+from .base import FoldedInput, NormFold, ResidualAdd, register_block
 from .context import StepContext
 
 Pending = Union[None, torch.Tensor, FoldedInput]     # what a block hands on: nothing, an output still to add, or a folded input
@@ -41,6 +41,13 @@ def fold_between(producer, norm, consumer, ctx: StepContext) -> Optional[tuple]:
     if not kernels.fold_supported(ctx.n_tokens, ctx.dtype, out_weight, in_weight, gated):
         return None
     return norm.fold()
+
+
+def adds_into_stream(producer, ctx: StepContext) -> bool:
+    """Whether ``producer``'s last product can add its results into the residual stream itself in this step."""
+    offer = getattr(producer, "fold_output_weight", None)
+    weight = offer(ctx) if offer is not None else None
+    return weight is not None and kernels.add_in_product_supported(ctx.n_tokens, ctx.dtype, weight)
 
 
 @register_block("pre_norm")
@@ -69,11 +76,16 @@ class PreNormBlock:
         if fold is not None:
             normed = self.mixer.forward(normed, ctx, cache, fold=NormFold(residual, *fold))
         else:
-            delta = self.mixer.forward(normed, ctx, cache)
+            if adds_into_stream(self.mixer, ctx):
+                delta = self.mixer.forward(normed, ctx, cache, fold=ResidualAdd(residual))      # None: added already
+            else:
+                delta = self.mixer.forward(normed, ctx, cache)
             normed = ctx.buffer("block.normed", tuple(residual.shape), ctx.dtype)      # (the mixer has read the first)
             self.feed_forward_norm.add_and_norm(residual, delta, normed)
         if next_block is not None and getattr(next_block, "takes_next_block", False):
             fold = fold_between(self.feed_forward, getattr(next_block, "mixer_norm", None), getattr(next_block, "mixer", None), ctx)
             if fold is not None:
                 return self.feed_forward.forward(normed, ctx, fold=NormFold(residual, *fold))
+        if adds_into_stream(self.feed_forward, ctx):
+            return self.feed_forward.forward(normed, ctx, fold=ResidualAdd(residual))
         return self.feed_forward.forward(normed, ctx)

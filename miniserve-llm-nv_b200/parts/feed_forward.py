@@ -6,12 +6,12 @@ product of a decode step apply the activation as it stores; else the up rows fol
 
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Union
 
 import torch
 
 from .. import kernels
-from .base import FoldedInput, NormFold, ParamSpec, Part, register_feed_forward
+from .base import FoldedInput, NormFold, ParamSpec, Part, ResidualAdd, register_feed_forward
 from .context import StepContext
 
 
@@ -52,9 +52,10 @@ class GatedMLP(Part):
     def fold_output_weight(self, ctx: StepContext) -> Optional[torch.Tensor]:
         return self.down_weight if self.paired else None
 
-    def forward(self, x, ctx: StepContext, fold: Optional[NormFold] = None):
-        """``x``: the normed input, or a :class:`FoldedInput`.  With ``fold`` the down projection adds into the
-        residual stream and a :class:`FoldedInput` for the part behind the following norm is returned."""
+    def forward(self, x, ctx: StepContext, fold: Union[None, NormFold, ResidualAdd] = None):
+        """``x``: the normed input, or a :class:`FoldedInput`.  With a :class:`NormFold` the down projection adds into
+        the residual stream and a :class:`FoldedInput` for the part behind the following norm is returned; with a
+        :class:`ResidualAdd` it adds into the stream and nothing is returned."""
         stats = None
         if isinstance(x, FoldedInput):
             x, stats = x.x, x.stats
@@ -63,6 +64,9 @@ class GatedMLP(Part):
         if self.paired:
             hidden = ctx.buffer("gated_mlp.hidden", (n, self.intermediate_size), x.dtype)
             kernels.gated_up(x, self.gate_up_weight, hidden, row_stats=stats)
+            if isinstance(fold, ResidualAdd):
+                kernels.linear_add(hidden, self.down_weight, fold.residual)
+                return None
             if fold is not None:
                 partials = ctx.buffer("gated_mlp.partials", kernels.residual_partials_shape(n, *self.down_weight.shape), torch.float32)
                 stats = kernels.linear_residual(hidden, self.down_weight, fold.residual, fold.weight, fold.eps, out,

@@ -132,6 +132,10 @@ def linear_residual(x, weight, residual, norm_weight, eps, x_next, partials):
     return kernels.RowStats(partials, FOLD_BLOCKS, eps, per_row=partials.shape[1] != 8)
 
 
+def linear_add(x, weight, residual):
+    residual += (x.double() @ weight.double().T).to(residual.dtype)
+
+
 def paged_attention(q, k_pool, v_pool, block_tables, request_of_token, positions, query_start, context_lens,
                     max_query_len, max_context_len, scale, window, out, host_query_start=None, softcap=None,
                     bias_slopes=None):
@@ -198,3 +202,6 @@ def install(monkeypatch) -> None:
     monkeypatch.setattr(kernels, "linear_residual", linear_residual)
     monkeypatch.setattr(kernels, "residual_partials_shape", lambda rows, n, k: (FOLD_BLOCKS, 8 if rows <= 8 else rows))
     monkeypatch.setattr(kernels, "fold_supported", lambda rows, dtype, producer, consumer, gated=False: 0 < rows <= 8 or rows >= 24)
+    # products that add into the residual stream themselves: offered for steps of 12 to 23 rows
+    monkeypatch.setattr(kernels, "linear_add", linear_add)
+    monkeypatch.setattr(kernels, "add_in_product_supported", lambda rows, dtype, weight: 12 <= rows < 24)

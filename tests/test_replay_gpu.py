@@ -151,11 +151,11 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     import plain_qwen3 as plain
     from miniserve_b200 import kernels
 
-    calls = {"plain": 0, "gated": 0, "residual": 0}
+    calls = {"plain": 0, "gated": 0, "added": 0, "residual": 0}
     inner, inner_residual = kernels.linear_pair, kernels.linear_pair_residual
 
     def counted(x, weight, out, add=False, gated=False, row_stats=None):
-        calls["gated" if gated else "plain"] += 1
+        calls["gated" if gated else "added" if add else "plain"] += 1
         return inner(x, weight, out, add=add, gated=gated, row_stats=row_stats)
 
     def counted_residual(*args):
@@ -184,16 +184,16 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     assert sorted(got["long"]) == wanted
     check_against(request, got, lambda rid: expected, "bfloat16", wanted={"long": wanted})
     layers = REAL["num_hidden_layers"]
-    # whole: every product of a layer.  Two portions: 1,100 rows fill the pairs of multiprocessors only with the
-    # gate/up product's tiles, 1,000 rows with those of q/k/v as well (the rest goes to cuBLAS).  No norm is folded:
-    # at these lengths a pair has one tile of the o and down products, and nothing to overlap the longer epilogue with
+    # whole: every product of a layer, o and down adding into the residual stream as they store.  With the norms
+    # folded, o and down (but for the last layer's) also leave the next product's input.  Two portions: 1,100 rows
+    # fill the pairs of multiprocessors only with the gate/up product's tiles, 1,000 rows with those of q/k/v as
+    # well (the rest goes to cuBLAS)
     if cutting == "whole":
-        assert calls == {"plain": 3 * layers, "gated": layers, "residual": 0}
+        assert calls == {"plain": layers, "gated": layers, "added": 2 * layers, "residual": 0}
     elif cutting == "whole, norms folded":
-        # o and down (but for the last layer's) add into the stream and leave the next product's input
-        assert calls == {"plain": layers + 1, "gated": layers, "residual": 2 * layers - 1}
+        assert calls == {"plain": layers, "gated": layers, "added": 1, "residual": 2 * layers - 1}
     else:
-        assert calls == {"plain": layers, "gated": 2 * layers, "residual": 0}
+        assert calls == {"plain": layers, "gated": 2 * layers, "added": 0, "residual": 0}
 
 
 def test_generation_at_real_size_graph_against_eager(real_model):
