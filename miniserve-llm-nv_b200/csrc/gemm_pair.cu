@@ -36,6 +36,13 @@
 // third buffer, and then every instruction handles four whole rows of the box (eight lanes x 16 bytes each), so
 // that the stream and the next input are written in whole lines.
 //
+// The q/k/v epilogue (heads of 128): a thread holds one head of its row at a time (128 accumulators), rounds it to
+// bfloat16 as the storing epilogue would and applies the per-head RMSNorm of q and k; the head then goes through
+// shared memory to eight lanes per row, which apply the half-split rotation (cosine and sine of the row's position
+// from the step's table, read in whole lines) and store q heads to the query matrix and k and v heads to their
+// slots of the paged cache, a row's 128 bytes at a time.  That is what the separate norm + rotation + append kernel
+// does, without writing the projection out and reading it back.
+//
 // Every wait on an mbarrier is bounded: a wait that does not finish within the limit sets the error flag that the
 // host checks, and the kernel drains and returns (tensor memory is freed on every path; both blocks meet before).
 #include "wide_common.cuh"
@@ -48,15 +55,34 @@ using namespace ms::t5;
 constexpr int HALF = 128;                    // rows of X, and rows of W, that one block of the pair loads
 constexpr int TILE = 2 * HALF;               // the pair's tile: 256 x 256
 constexpr int BK = 64, UMMA_K = 16;
-constexpr int THREADS = 192;                 // warps 0..5
+// warps 0 and 1 load and multiply; four read-out warps, or eight in the q/k/v epilogue (a head of the tile for each
+// four, two warps per scheduler: the epilogue is long chains of dependent instructions)
+__host__ __device__ constexpr int read_warps(int epilogue) { return epilogue == 4 ? 8 : 4; }
+__host__ __device__ constexpr int threads(int epilogue) { return 32 * (2 + read_warps(epilogue)); }
 constexpr int ACCUMULATORS = 2;
 constexpr int STAGE_BYTES = 2 * HALF * BK * 2;     // this block's halves of X and W for one k-block
 constexpr int OUT_BUFFER = 32 * 128;               // 32 rows x 128 bytes: what one read-out warp stores at a time
-// A read-out warp's buffers: two to store from; in the residual epilogue two boxes of the stream and one of results.
+// A read-out warp's buffers: two to store from; in the residual epilogue two boxes of the stream and one of results;
+// in the q/k/v epilogue 32 rows of a head in bfloat16.
 __host__ __device__ constexpr int warp_bytes(int epilogue) { return (epilogue == 3 ? 3 : 2) * OUT_BUFFER; }
 
-enum : int { EPI_STORE = 0, EPI_ADD_F32 = 1, EPI_GATED = 2, EPI_RESIDUAL = 3 };
+enum : int { EPI_STORE = 0, EPI_ADD_F32 = 1, EPI_GATED = 2, EPI_RESIDUAL = 3, EPI_QKV = 4 };
 static_assert(warp_bytes(EPI_RESIDUAL) == 3 * OUT_BUFFER, "the residual epilogue has three buffers per warp");
+
+constexpr int HEAD = 128;      // head size of the q/k/v epilogue
+
+// What the q/k/v epilogue needs: N = (n_q + 2 n_kv) * 128 columns, q heads first, then k, then v.
+struct Heads {
+  const int* slots;             // [M] page * page_size + offset of each row's token (negative: k and v are not stored)
+  const void* q_weight;         // [128] norm weights of q and k heads (null: no norm)
+  const void* k_weight;
+  int weight_dtype;
+  float eps;
+  const float* cos_sin;         // [M, 64, 2] cosine and sine of each row's position (null: no rotation)
+  __nv_bfloat16* k_pool;        // [pages, n_kv, page_size, 128]
+  __nv_bfloat16* v_pool;
+  int page_size, n_q, n_kv;
+};
 
 // What a norm folded into the products needs beside the operands.
 struct Fold {
@@ -108,15 +134,17 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 }
 
 template <int STAGES, int EPILOGUE, typename OutT>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(threads(EPILOGUE), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_residual,
-                 int through_tma, OutT* __restrict__ out, int M, int N, int K, Fold fold, int* __restrict__ error_flag) {
+                 int through_tma, OutT* __restrict__ out, int M, int N, int K, Fold fold, Heads heads,
+                 int* __restrict__ error_flag) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACCUMULATORS], acc_empty[ACCUMULATORS];
   __shared__ uint64_t residual_bar[4][2];      // residual epilogue: a read-out warp's two boxes of the stream
   __shared__ unsigned tmem_base_s;
+  __shared__ float head_weight[2][HEAD];       // q/k/v epilogue: the norm weights of q and of k heads
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned rank = cluster_rank();                 // 0: issues the MMAs
@@ -134,11 +162,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 #pragma unroll
     for (int b = 0; b < ACCUMULATORS; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);           // four read-out warps in each block
+      mbar_init(&acc_empty[b], 2 * read_warps(EPILOGUE));      // the read-out warps of both blocks
     }
 #pragma unroll
     for (int w = 0; w < 8; ++w) mbar_init(&residual_bar[w >> 1][w & 1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (EPILOGUE == EPI_QKV && warp >= 2 && warp < 6) {
+    const int i = threadIdx.x - 64;          // 0..127
+    head_weight[0][i] = heads.q_weight ? load_as_float(heads.q_weight, heads.weight_dtype, (size_t)i) : 1.f;
+    head_weight[1][i] = heads.k_weight ? load_as_float(heads.k_weight, heads.weight_dtype, (size_t)i) : 1.f;
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(ACCUMULATORS * TILE) : "memory");
@@ -231,7 +264,101 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         for (int i = 0; i < fold.in_count; ++i) total += fold.in_partials[(size_t)i * M + row];
         scale = rsqrtf(total / (float)K + fold.eps);
       }
-      if (EPILOGUE == EPI_RESIDUAL) {
+      if (EPILOGUE == EPI_QKV) {
+        // A head of the tile for each four warps.  A row per thread first: the head's 128 results are rounded to
+        // bfloat16 (as the storing epilogue would), their squares summed (the thread's own sum), and they go as rows of
+        // 256 bytes into shared memory (16-byte pieces swizzled by the row's low bits).  Then eight lanes per row:
+        // lane j of a row has elements 8 j .. 8 j + 7 and their partners 64 + 8 j .., applies the norm (the row's
+        // factor comes by shuffle), reads its 64 bytes of the row's cosines and sines, rotates, and stores two
+        // pieces of 16 bytes; four rows per instruction, every row's 128 bytes in one piece.
+        const int h = (warp - 2) >> 2;
+        const int head = tile_n * (TILE / HEAD) + h;
+        if (head < heads.n_q + 2 * heads.n_kv) {
+          unsigned char* staging = out_s + (warp - 2) * warp_bytes(EPILOGUE);     // 32 rows x 256 bytes
+          const bool is_query = head < heads.n_q, is_value = head >= heads.n_q + heads.n_kv;
+          const bool normed = !is_value && (is_query ? heads.q_weight : heads.k_weight) != nullptr;
+          float sum_sq = 0.f;
+#pragma unroll
+          for (int part = 0; part < HEAD / 32; ++part) {
+            float v[32];
+            tmem_load_32(lanes + (unsigned)(h * HEAD + 32 * part), v);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v[i] = round_bf16(v[i] * scale);
+              sum_sq += v[i] * v[i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              *reinterpret_cast<uint4*>(staging + lane * 256 + (((4 * part + i) ^ (lane & 7)) << 4)) = pack8(v + 8 * i);
+          }
+          const float factor = normed ? 1.0f / sqrtf(sum_sq / (float)HEAD + heads.eps) : 1.0f;
+          // where this row's k or v head goes, in elements from the pool's start (negative: nowhere)
+          long long cache_at = -1;
+          if (!is_query && row < M) {
+            const int slot = heads.slots[row];
+            const int kv_head = head - heads.n_q - (is_value ? heads.n_kv : 0);
+            if (slot >= 0)
+              cache_at = (((long long)(slot / heads.page_size) * heads.n_kv + kv_head) * heads.page_size + slot % heads.page_size) * HEAD;
+          }
+          __syncwarp();
+          const int group = lane >> 3, j = lane & 7;
+          const bool rotate = heads.cos_sin != nullptr && !is_value;
+          __nv_bfloat16* pool = is_value ? heads.v_pool : heads.k_pool;
+          float wa[8], wb[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            wa[e] = normed ? head_weight[is_query ? 0 : 1][8 * j + e] : 1.f;
+            wb[e] = normed ? head_weight[is_query ? 0 : 1][HEAD / 2 + 8 * j + e] : 1.f;
+          }
+#pragma unroll 2
+          for (int pass = 0; pass < 8; ++pass) {
+            const int r = 4 * pass + group;
+            const long long at = __shfl_sync(0xffffffffu, cache_at, r);
+            const float inv = __shfl_sync(0xffffffffu, factor, r);
+            const int out_r = out_row + r;
+            const unsigned char* from = staging + r * 256;
+            const uint4 first = *reinterpret_cast<const uint4*>(from + ((j ^ (r & 7)) << 4));
+            const uint4 second = *reinterpret_cast<const uint4*>(from + (((8 + j) ^ (r & 7)) << 4));
+            float a[8], b[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 fa = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&first)[e]);
+              const float2 fb = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&second)[e]);
+              a[2 * e] = fa.x; a[2 * e + 1] = fa.y;
+              b[2 * e] = fb.x; b[2 * e + 1] = fb.y;
+            }
+            if (normed) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                a[e] = a[e] * inv * wa[e];
+                b[e] = b[e] * inv * wb[e];
+              }
+            }
+            if (rotate && out_r < M) {
+              const float4* table = reinterpret_cast<const float4*>(heads.cos_sin + (size_t)out_r * HEAD + 16 * j);
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const float4 cs = table[q4];              // (cos, sin) of elements 8 j + 2 q4 and 8 j + 2 q4 + 1
+                const float a0 = a[2 * q4], b0 = b[2 * q4], a1 = a[2 * q4 + 1], b1 = b[2 * q4 + 1];
+                a[2 * q4] = a0 * cs.x - b0 * cs.y;
+                b[2 * q4] = b0 * cs.x + a0 * cs.y;
+                a[2 * q4 + 1] = a1 * cs.z - b1 * cs.w;
+                b[2 * q4 + 1] = b1 * cs.z + a1 * cs.w;
+              }
+            }
+            __nv_bfloat16* dst = nullptr;
+            if (is_query) {
+              if (out_r < M) dst = reinterpret_cast<__nv_bfloat16*>(out) + ((size_t)out_r * heads.n_q + head) * HEAD;
+            } else if (at >= 0) {
+              dst = pool + at;
+            }
+            if (dst != nullptr) {
+              *reinterpret_cast<uint4*>(dst + 8 * j) = pack8(a);
+              *reinterpret_cast<uint4*>(dst + HEAD / 2 + 8 * j) = pack8(b);
+            }
+          }
+        }
+      } else if (EPILOGUE == EPI_RESIDUAL) {
         unsigned char* mine = out_s + quarter * warp_bytes(EPILOGUE);
         unsigned char* results = mine + 2 * OUT_BUFFER;
         const int group = lane >> 3, piece = lane & 7;       // this lane's row of every four, and its 16 bytes of a row
@@ -434,14 +561,14 @@ static bool out_map(CUtensorMap* map, void* base, int rows, int cols, bool float
 
 template <int STAGES, int EPILOGUE, typename OutT>
 int launch(const void* X, const void* W, void* out, int M, int N, int K, const Fold& fold, float* residual, int* error_flag,
-           cudaStream_t stream) {
+           cudaStream_t stream, const Heads& heads = Heads{}) {
   CUtensorMap map_x, map_w, map_out, map_residual;
   MS_REQUIRE(wide::cached_map(&map_x, X, M, K, HALF) && wide::cached_map(&map_w, W, N, K, HALF),
              "gemm_pair: cuTensorMapEncodeTiled failed (M %d N %d K %d)", M, N, K);
-  const int out_cols = EPILOGUE == EPI_GATED ? N / 2 : N;
+  const int out_cols = EPILOGUE == EPI_GATED ? N / 2 : EPILOGUE == EPI_QKV ? heads.n_q * HEAD : N;
   const int through_tma = ((size_t)out_cols * sizeof(OutT)) % 16 == 0 && (uintptr_t)out % 16 == 0;
   map_out = map_residual = map_x;          // (where they are not used)
-  if (through_tma && EPILOGUE != EPI_RESIDUAL)
+  if (through_tma && EPILOGUE != EPI_RESIDUAL && EPILOGUE != EPI_QKV)
     MS_REQUIRE(out_map(&map_out, out, M, out_cols, sizeof(OutT) == 4),
                "gemm_pair: cuTensorMapEncodeTiled failed for the output (M %d N %d)", M, out_cols);
   if (EPILOGUE == EPI_RESIDUAL) {
@@ -450,7 +577,7 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, const F
     MS_REQUIRE(out_map(&map_residual, residual, M, N, true), "gemm_pair: cuTensorMapEncodeTiled failed for the residual stream");
   }
   auto kernel = gemm_pair_kernel<STAGES, EPILOGUE, OutT>;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + 4 * warp_bytes(EPILOGUE) + 1024;
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + read_warps(EPILOGUE) * warp_bytes(EPILOGUE) + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -469,7 +596,7 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, const F
   const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-  config.blockDim = dim3(THREADS, 1, 1);
+  config.blockDim = dim3(threads(EPILOGUE), 1, 1);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
   cudaLaunchAttribute attribute[2];
@@ -481,7 +608,7 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, const F
   attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = dependent_launch_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_out, map_residual, through_tma, (OutT*)out, M, N, K, fold, error_flag);
+  cudaError_t e = cudaLaunchKernelEx(&config, kernel, map_x, map_w, map_out, map_residual, through_tma, (OutT*)out, M, N, K, fold, heads, error_flag);
   if (e != cudaSuccess) MS_FAIL("gemm_pair: launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -533,6 +660,31 @@ MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtyp
   if (out_dtype == MS_BF16) return pair::launch<STAGES, pair::EPI_STORE, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   if (out_dtype == MS_F32) return pair::launch<STAGES, pair::EPI_STORE, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   MS_FAIL("gemm_pair: unknown output type code %d", out_dtype);
+}
+
+// The q/k/v projection of an attention layer with heads of 128, and what follows it up to the cache: X [M, K],
+// W [(n_q + 2 n_kv) * 128, K] bfloat16 (q heads first, then k, then v).  Every head is rounded to bfloat16; q and k
+// heads get their RMSNorm (weights [128] of type weight_dtype; null: none) and the half-split rotation by
+// cos_sin [M, 64, 2] float32 (null: none); q heads go to q_out [M, n_q * 128], k and v heads to the pools
+// [pages, n_kv, page_size, 128] at slots[M] (page * page_size + offset; negative: not stored).  in_partials as above.
+MS_EXPORT int ms_gemm_pair_qkv(const void* X, const void* W, void* q_out, int M, int K, const float* in_partials, int in_count,
+                               float fold_eps, const int* slots, const void* q_weight, const void* k_weight, int weight_dtype,
+                               float eps, const float* cos_sin, void* k_pool, void* v_pool, int page_size, int n_q, int n_kv,
+                               int* error_flag, cudaStream_t stream) {
+  if (M == 0) return 0;
+  const int N = (n_q + 2 * n_kv) * pair::HEAD;
+  MS_REQUIRE(n_q > 0 && n_kv > 0 && page_size > 0, "gemm_pair_qkv: %d query heads, %d key/value heads, pages of %d", n_q, n_kv, page_size);
+  MS_REQUIRE(K > 0 && K % 8 == 0, "gemm_pair_qkv: inner size %d is not a multiple of 8", K);
+  MS_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)q_out % 16 == 0) &&
+             ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && (cos_sin == nullptr || (uintptr_t)cos_sin % 16 == 0),
+             "gemm_pair_qkv: operands, outputs and the rotation table must be 16-byte aligned");
+  MS_REQUIRE(slots != nullptr && error_flag != nullptr, "gemm_pair_qkv: slots and an error flag on the device are required");
+  MS_REQUIRE(weight_dtype == MS_F32 || weight_dtype == MS_BF16, "gemm_pair_qkv: unknown norm weight type code %d", weight_dtype);
+  MS_REQUIRE(in_partials == nullptr || in_count > 0, "gemm_pair_qkv: row statistics of %d tiles", in_count);
+  const pair::Fold fold{in_partials, in_count, fold_eps, nullptr, 0, nullptr, nullptr};
+  const pair::Heads heads{slots, q_weight, k_weight, weight_dtype, eps, cos_sin, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+                          page_size, n_q, n_kv};
+  return pair::launch<5, pair::EPI_QKV, __nv_bfloat16>(X, W, q_out, M, N, K, fold, nullptr, error_flag, stream, heads);
 }
 
 // Rows of `out_partials` that the residual epilogue writes for a weight of N rows.

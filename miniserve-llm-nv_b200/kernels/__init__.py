@@ -548,6 +548,57 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: b
                                   _i(0), None, _ptr(device_error_flag(x.device)), _stream()))
 
 
+QKV_IN_PRODUCT = __import__("os").environ.get("MINISERVE_B200_QKV_IN_PRODUCT", "1") == "1"
+
+
+def qkv_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor, head_dim: int, cos_sin,
+                             rotary_dim: int, interleaved: bool) -> bool:
+    """Whether a q/k/v projection of ``rows`` rows can norm, rotate and append its heads as it stores them
+    (:func:`linear_pair_qkv`): bfloat16, so many rows that it goes to :func:`linear_pair`, heads of 128, and no
+    rotation or the half-split one over the whole head."""
+    n, k = weight.shape
+    return (QKV_IN_PRODUCT and dtype == torch.bfloat16 and head_dim == 128 and k % 8 == 0
+            and (cos_sin is None or (rotary_dim == head_dim and not interleaved))
+            and pair_preferred(weight.device, rows, n))
+
+
+def linear_pair_qkv(x: torch.Tensor, weight: torch.Tensor, slots: torch.Tensor, q_weight: Optional[torch.Tensor],
+                    k_weight: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], k_pool: torch.Tensor,
+                    v_pool: torch.Tensor, n_q: int, n_kv: int, q_out: torch.Tensor, row_stats: Optional["RowStats"] = None) -> None:
+    """The q/k/v projection ``x @ weight^T`` with :func:`qk_norm_rope_append` applied to the tiles as they leave the
+    tensor cores (heads of 128; the arguments mean what they mean there): q heads to ``q_out``, k and v heads to the
+    pools, and the projection itself is never written out.  ``row_stats`` as in :func:`linear_pair`."""
+    m, k = x.shape
+    d = 128
+    _want(x, "x", torch.bfloat16)
+    _want(weight, "weight", torch.bfloat16, ((n_q + 2 * n_kv) * d, k))
+    _want(slots, "slots", torch.int32, (m,))
+    _want(k_pool, "k_pool", torch.bfloat16)
+    _want(v_pool, "v_pool", torch.bfloat16, k_pool.shape)
+    if k_pool.dim() != 4 or k_pool.shape[1] != n_kv or k_pool.shape[3] != d:
+        raise KernelError(f"pool shape {tuple(k_pool.shape)} is not [pages, {n_kv}, page_size, {d}]")
+    _want(q_out, "q_out", torch.bfloat16, (m, n_q, d))
+    weight_code = 0
+    for name, norm_weight in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if norm_weight is not None:
+            _want(norm_weight, name, None, (d,))
+            weight_code = _code(norm_weight.dtype)
+    if q_weight is not None and k_weight is not None and q_weight.dtype != k_weight.dtype:
+        raise KernelError("q and k norm weights must share one element type")
+    if cos_sin is not None:
+        _want(cos_sin, "cos_sin", torch.float32, (m, d // 2, 2))
+    if row_stats is not None:
+        _want(row_stats.partials, "row_stats.partials", torch.float32)
+        if not row_stats.per_row or row_stats.partials.dim() != 2 or row_stats.partials.shape[1] != m \
+                or row_stats.partials.shape[0] < row_stats.count:
+            raise KernelError(f"linear_pair_qkv: row statistics of shape {tuple(row_stats.partials.shape)} for {m} rows")
+    _check(library().ms_gemm_pair_qkv(
+        _ptr(x), _ptr(weight), _ptr(q_out), _i(m), _i(k), _ptr(row_stats.partials if row_stats else None),
+        _i(row_stats.count if row_stats else 0), _f(row_stats.eps if row_stats else 0.0), _ptr(slots), _ptr(q_weight),
+        _ptr(k_weight), _i(weight_code), _f(eps), _ptr(cos_sin), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[2]), _i(n_q),
+        _i(n_kv), _ptr(device_error_flag(x.device)), _stream()))
+
+
 def pair_column_tiles(n: int) -> int:
     """Rows of ``partials`` that :func:`linear_pair_residual` writes for a weight of ``n`` rows."""
     return (n + 255) // 256

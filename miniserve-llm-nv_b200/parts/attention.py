@@ -103,12 +103,20 @@ class Attention(Part):
             x, stats = x.x, x.stats
         n, d = x.shape[0], self.head_dim
         n_q, n_kv = self.num_heads, self.num_kv_heads
-        qkv = ctx.buffer("attention.qkv", (n, (n_q + 2 * n_kv) * d), x.dtype)
-        kernels.linear(x, self.qkv_weight, qkv, row_stats=stats)
         slots = cache.slots if cache.writable else torch.full_like(cache.slots, -1)
         fused = self.position.fused_args(ctx)
         attended = ctx.buffer("attention.attended", (n, n_q, d), x.dtype)
-        if self._decode_in_the_attention_kernel(ctx, fused, x.dtype):
+        in_product = fused is not None and kernels.qkv_in_product_supported(n, x.dtype, self.qkv_weight, d, *fused)
+        if not in_product:
+            qkv = ctx.buffer("attention.qkv", (n, (n_q + 2 * n_kv) * d), x.dtype)
+            kernels.linear(x, self.qkv_weight, qkv, row_stats=stats)
+        if in_product:
+            # many rows: norm, rotation and append happen as the projection's tiles are stored
+            q = ctx.buffer("attention.q", (n, n_q, d), x.dtype)
+            kernels.linear_pair_qkv(x, self.qkv_weight, slots, self.q_norm_weight, self.k_norm_weight, self.eps, fused[0],
+                                    cache.key_pool, cache.value_pool, n_q, n_kv, q, row_stats=stats)
+            self._attend(q, ctx, cache, attended)
+        elif self._decode_in_the_attention_kernel(ctx, fused, x.dtype):
             # a step of single tokens: norm, rotation and append happen inside the split-key attention kernel
             kernels.decode_attention_fused(qkv, slots, self.q_norm_weight, self.k_norm_weight, self.eps, fused[0],
                                            cache.key_pool, cache.value_pool, cache.block_tables, ctx.query_start,
@@ -122,12 +130,7 @@ class Attention(Part):
                                             rotary_dim, interleaved, cache.key_pool, cache.value_pool, n_q, n_kv, d, q)
             else:
                 self._append_with_external_position(qkv, slots, ctx, cache, q)
-            if self.score_bias_slopes is not None and self._slopes_on_device is None:
-                self._slopes_on_device = torch.tensor(self.score_bias_slopes, dtype=torch.float32, device=x.device)
-            kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
-                                    ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
-                                    ctx.max_context_len, self.scale, self.window, attended,
-                                    ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
+            self._attend(q, ctx, cache, attended)
         if isinstance(fold, ResidualAdd):
             kernels.linear_add(attended.view(n, n_q * d), self.o_weight, fold.residual)
             return None
@@ -139,6 +142,14 @@ class Attention(Part):
             return FoldedInput(out, stats)
         kernels.linear(attended.view(n, n_q * d), self.o_weight, out)
         return out
+
+    def _attend(self, q: torch.Tensor, ctx: StepContext, cache: PagedKVView, attended: torch.Tensor) -> None:
+        if self.score_bias_slopes is not None and self._slopes_on_device is None:
+            self._slopes_on_device = torch.tensor(self.score_bias_slopes, dtype=torch.float32, device=q.device)
+        kernels.paged_attention(q, cache.key_pool, cache.value_pool, cache.block_tables, ctx.request_of_token,
+                                ctx.positions, ctx.query_start, ctx.context_lens, ctx.max_query_len,
+                                ctx.max_context_len, self.scale, self.window, attended,
+                                ctx.host_query_start or None, self.score_softcap, self._slopes_on_device)
 
     def _decode_in_the_attention_kernel(self, ctx: StepContext, fused, dtype: torch.dtype) -> bool:
         """Whether this step's norm, rotation and append run inside the attention kernel

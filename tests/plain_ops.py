@@ -202,6 +202,7 @@ def install(monkeypatch) -> None:
     monkeypatch.setattr(kernels, "linear_residual", linear_residual)
     monkeypatch.setattr(kernels, "residual_partials_shape", lambda rows, n, k: (FOLD_BLOCKS, 8 if rows <= 8 else rows))
     monkeypatch.setattr(kernels, "fold_supported", lambda rows, dtype, producer, consumer, gated=False: 0 < rows <= 8 or rows >= 24)
+    monkeypatch.setattr(kernels, "qkv_in_product_supported", lambda *sizes: False)
     # products that add into the residual stream themselves: offered for steps of 12 to 23 rows
     monkeypatch.setattr(kernels, "linear_add", linear_add)
     monkeypatch.setattr(kernels, "add_in_product_supported", lambda rows, dtype, weight: 12 <= rows < 24)

@@ -647,6 +647,52 @@ def test_norm_folded_into_many_row_products(kernels, norm_dtype, m, hidden, k, n
     assert torch.equal(alone[3], out[first:first + 9])
 
 
+@pytest.mark.parametrize("m,k,n_q,n_kv,norm,rotate,page_size,folded", [
+    (2048, 2048, 16, 8, True, True, 64, False), (300, 136, 3, 1, True, True, 16, False), (1000, 256, 4, 2, False, True, 8, False),
+    (520, 512, 2, 2, True, False, 32, False), (2100, 2048, 16, 8, True, True, 64, True), (257, 64, 5, 1, True, True, 4, True)])
+def test_qkv_projection_with_norm_rotation_and_append_in_its_epilogue(kernels, m, k, n_q, n_kv, norm, rotate, page_size, folded):
+    """The q/k/v projection whose tiles are normed, rotated and appended as they leave the tensor cores, against the
+    same product followed by the separate norm + rotation + append kernel: the same roundings in the same places,
+    so q and both pools agree to a bfloat16 rounding step (the sums of squares are added in another order); head
+    counts that leave a tile half empty or straddle q, k and v inside a tile, ragged rows, rows that are not stored,
+    scattered slots, and a norm folded in before."""
+    d = 128
+    heads = n_q + 2 * n_kv
+    x, w = rand((m, k), torch.bfloat16, 90, 0.5), rand((heads * d, k), torch.bfloat16, 91, 0.2)
+    q_w = (1 + rand((d,), torch.float32, 92, 0.2)).to(torch.bfloat16) if norm else None
+    k_w = (1 + rand((d,), torch.float32, 93, 0.2)).to(torch.bfloat16) if norm else None
+    cos_sin = None
+    if rotate:
+        angles = torch.rand((m, d // 2), generator=torch.Generator().manual_seed(94)) * 6.28
+        cos_sin = torch.stack((torch.cos(angles), torch.sin(angles)), dim=-1).float().cuda().contiguous()
+    pages = (m + page_size - 1) // page_size + 3
+    order = torch.randperm(pages * page_size, generator=torch.Generator().manual_seed(95))[:m].to(torch.int32)
+    order[5] = -1                                           # a row that is computed but not stored
+    slots = order.cuda()
+    stats = None
+    if folded:
+        partials = (rand((3, m), torch.float32, 96).abs() * k / 3).contiguous()
+        stats = kernels.RowStats(partials, 3, 1e-6, per_row=True)
+
+    def pools():
+        return [torch.full((pages, n_kv, page_size, d), 3.0, dtype=torch.bfloat16).cuda() for _ in range(2)]
+
+    k_ref, v_ref = pools()
+    qkv = torch.empty((m, heads * d), dtype=torch.bfloat16).cuda()
+    kernels.linear_pair(x, w, qkv, row_stats=stats)
+    q_ref = torch.empty((m, n_q, d), dtype=torch.bfloat16).cuda()
+    kernels.qk_norm_rope_append(qkv, slots, q_w, k_w, 1e-6, cos_sin, d, False, k_ref, v_ref, n_q, n_kv, d, q_ref)
+    k_pool, v_pool = pools()
+    q = torch.full((m, n_q, d), 7.0, dtype=torch.bfloat16).cuda()
+    kernels.linear_pair_qkv(x, w, slots, q_w, k_w, 1e-6, cos_sin, k_pool, v_pool, n_q, n_kv, q, row_stats=stats)
+    kernels.check_device_errors(x.device)
+    assert torch.equal(v_pool, v_ref)                       # values are only rounded and stored
+    for got, expected in ((q, q_ref), (k_pool, k_ref)):
+        scale = float(expected.float().abs().max())
+        assert torch.allclose(got.float(), expected.float(), atol=scale * 2 ** -8, rtol=2 ** -7)
+        assert float((got != expected).float().mean()) < 0.02          # and nearly all of them exactly
+
+
 def test_many_row_fold_is_offered_where_it_pays(kernels):
     hidden, inter = 2048, 6144
     o, gate_up = rand((hidden, hidden), torch.bfloat16, 1), rand((2 * inter, hidden), torch.bfloat16, 2)

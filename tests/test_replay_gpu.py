@@ -151,8 +151,8 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     import plain_qwen3 as plain
     from miniserve_b200 import kernels
 
-    calls = {"plain": 0, "gated": 0, "added": 0, "residual": 0}
-    inner, inner_residual = kernels.linear_pair, kernels.linear_pair_residual
+    calls = {"plain": 0, "gated": 0, "added": 0, "residual": 0, "qkv": 0}
+    inner, inner_residual, inner_qkv = kernels.linear_pair, kernels.linear_pair_residual, kernels.linear_pair_qkv
 
     def counted(x, weight, out, add=False, gated=False, row_stats=None):
         calls["gated" if gated else "added" if add else "plain"] += 1
@@ -162,8 +162,13 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
         calls["residual"] += 1
         return inner_residual(*args)
 
+    def counted_qkv(*args, **named):
+        calls["qkv"] += 1
+        return inner_qkv(*args, **named)
+
     monkeypatch.setattr(kernels, "linear_pair", counted)
     monkeypatch.setattr(kernels, "linear_pair_residual", counted_residual)
+    monkeypatch.setattr(kernels, "linear_pair_qkv", counted_qkv)
     if cutting == "whole, norms folded":
         # as for prompts of 4,096 tokens and more, where a pair of multiprocessors has a next tile to accumulate
         # while the longer epilogue of a folded norm runs
@@ -184,16 +189,17 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     assert sorted(got["long"]) == wanted
     check_against(request, got, lambda rid: expected, "bfloat16", wanted={"long": wanted})
     layers = REAL["num_hidden_layers"]
-    # whole: every product of a layer, o and down adding into the residual stream as they store.  With the norms
-    # folded, o and down (but for the last layer's) also leave the next product's input.  Two portions: 1,100 rows
-    # fill the pairs of multiprocessors only with the gate/up product's tiles, 1,000 rows with those of q/k/v as
-    # well (the rest goes to cuBLAS)
+    # whole: every product of a layer: q/k/v with norm, rotation and append in its epilogue, gate/up with the
+    # activation, o and down adding into the residual stream as they store.  With the norms folded, o and down (but
+    # for the last layer's) also leave the next product's input.  Two portions: 1,100 rows fill the pairs of
+    # multiprocessors only with the gate/up product's tiles, 1,000 rows with those of q/k/v as well (the rest goes
+    # to cuBLAS and the separate kernels)
     if cutting == "whole":
-        assert calls == {"plain": layers, "gated": layers, "added": 2 * layers, "residual": 0}
+        assert calls == {"plain": 0, "gated": layers, "added": 2 * layers, "residual": 0, "qkv": layers}
     elif cutting == "whole, norms folded":
-        assert calls == {"plain": layers, "gated": layers, "added": 1, "residual": 2 * layers - 1}
+        assert calls == {"plain": 0, "gated": layers, "added": 1, "residual": 2 * layers - 1, "qkv": layers}
     else:
-        assert calls == {"plain": layers, "gated": 2 * layers, "added": 0, "residual": 0}
+        assert calls == {"plain": 0, "gated": 2 * layers, "added": 0, "residual": 0, "qkv": layers}
 
 
 def test_generation_at_real_size_graph_against_eager(real_model):
