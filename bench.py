@@ -439,13 +439,16 @@ def mixed_workload(bench: Bench, args) -> int:
                        f"at context {manager.length('c')}, layers {args.layers}")
     step_function.use_graphs = graphs
     decode_bytes = bench.weight_bytes + bench.kv_bytes_per_token * CONTEXT * args.batch
+    from miniserve_b200 import kernels
     print(json.dumps({
         "workload": "mixed", "impl": "ours", "dtype": "bf16",
         "config": config_record(args.shape, bench.shape, args.layers, args.batch, "eager (mixed steps), cuda_graph (decode alone)"),
         "decode_streams": args.batch, "stream_context": CONTEXT, "chunk_tokens": chunk,
         "ms_decode_alone_graph": round(decode_alone_graph * 1e3, 3), "ms_decode_alone_eager": round(decode_alone_eager * 1e3, 3),
         "decode_alone_roofline_frac": round(decode_bytes / decode_alone_graph / 1e9 / bench.peak["hbm_gbs"], 4),
-        "steps": rows, "peak_source": bench.peak_source}))
+        "steps": rows, "peak_source": bench.peak_source,
+        "many_row_products": {f"{kind} {tiles} row tiles {n}x{k}": [choice, times]
+                              for (_, kind, tiles, n, k), (choice, times) in sorted(kernels.many_row_choices().items())}}))
     return 0
 
 
@@ -618,6 +621,8 @@ def main() -> int:
         "few_row_products": {**{f"{n}x{k}": choice for (_, n, k), choice in sorted(kernels.linear_choices().items())},
                              **{"gated " + "x".join(str(size) for size in key[1:]): choice
                                 for key, choice in sorted(kernels.gated_choices().items())}},
+        "many_row_products": {f"{kind} {tiles} row tiles {n}x{k}": [choice, times]
+                              for (_, kind, tiles, n, k), (choice, times) in sorted(kernels.many_row_choices().items())},
         "few_row_us": {("gated " if len(key) > 3 else "") + f"{key[1]}x{key[2]}": times
                        for key, times in sorted(kernels.choice_times().items(), key=lambda item: item[0][:3])},
     }

@@ -427,7 +427,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: 
         if choice == "wide":
             linear_wide(x, weight, out)
             return
-    if k % 8 == 0 and pair_preferred(x.device, m, n):
+    if k % 8 == 0 and out.dtype == torch.bfloat16 and pair_preferred(x.device, m, n) and _pair_or_library("plain", m, weight) == "pair":
         linear_pair(x, weight, out)
         return
     if USE_TCGEN05_GEMM and m >= 128 and k % 8 == 0:
@@ -449,6 +449,91 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: 
 USE_PAIR_GEMM = __import__("os").environ.get("MINISERVE_B200_PAIR_GEMM", "1") == "1"
 USE_TCGEN05_GEMM = __import__("os").environ.get("MINISERVE_B200_TCGEN05_GEMM", "0") == "1"
 PAIR_MIN_FILL = 0.8            # of the pairs' time in use, by the count of tiles
+
+
+_many_row_choices: dict = {}         # (device index, kind, row tiles, N, K) -> "pair" | "library"
+_many_row_times: dict = {}           # the same keys -> {candidate: microseconds} as measured
+
+
+def many_row_choices() -> dict:
+    """What was chosen for the many-row products so far, with the measured times in microseconds."""
+    return {key: (choice, _many_row_times.get(key)) for key, choice in _many_row_choices.items()}
+
+
+def _pair_or_library(kind: str, rows: int, weight: torch.Tensor, n_q: int = 0, n_kv: int = 0) -> str:
+    """For a product of ``rows`` rows that :func:`pair_preferred` lets through: the two-block kernel with the
+    element-wise work of ``kind`` in its epilogue ("pair"), or cuBLAS followed by the separate kernel ("library").
+    Measured once per kind, count of 256-row tiles and weight shape, on the weight itself, at the first eager call
+    that meets it (kept in the choices file like the few-row choices); with MINISERVE_B200_LINEAR_TUNING=0 it is
+    the two-block kernel.  Kinds: "plain" (store), "gated" (against the product and the activation kernel), "add"
+    (product adding into the residual stream and the norm that reads it, against product, and norm that adds),
+    "qkv" (against product and the norm + rotation + append kernel)."""
+    n, k = weight.shape
+    tiles_m = (rows + 255) // 256
+    key = (torch.device(weight.device).index or 0, kind, tiles_m, n, k)
+    choice = _many_row_choices.get(key)
+    if choice is None:
+        if not LINEAR_TUNING or torch.cuda.is_current_stream_capturing():
+            return "pair"
+        stored_as = f"rows{tiles_m} {kind}"
+        choice = _stored_choice(stored_as, n, k)
+        if choice is None:
+            choice = _measure_many_rows(key, rows, weight, n_q, n_kv)
+            _store_choice(stored_as, n, k, choice)
+            log.info("%s products of %d rows with a %d x %d weight run %s (measured, us: %s)", kind, rows, n, k,
+                     "the two-block kernel" if choice == "pair" else "cuBLAS and the separate kernel", _many_row_times.get(key))
+        _many_row_choices[key] = choice
+    return choice
+
+
+def _measure_many_rows(key: tuple, rows: int, weight: torch.Tensor, n_q: int, n_kv: int) -> str:
+    kind = key[1]
+    n, k = weight.shape
+    device = weight.device
+    generator = torch.Generator(device=device).manual_seed(0)
+    source = torch.randn((rows, k), dtype=torch.float32, device=device, generator=generator).to(torch.bfloat16)
+    x = torch.empty_like(source)
+    whole = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
+    if kind == "plain":
+        candidates = {"pair": lambda: linear_pair(x, weight, whole), "library": lambda: torch.mm(x, weight.t(), out=whole)}
+    elif kind == "gated":
+        half = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=device)
+
+        def by_library() -> None:
+            torch.mm(x, weight.t(), out=whole)
+            silu_mul(whole, half, paired=True)
+        candidates = {"pair": lambda: linear_pair(x, weight, half, gated=True), "library": by_library}
+    elif kind == "add":
+        residual = torch.zeros((rows, n), dtype=torch.float32, device=device)
+        norm_weight = torch.ones(n, dtype=torch.bfloat16, device=device)
+
+        def by_pair() -> None:
+            linear_pair(x, weight, residual, add=True)
+            add_rmsnorm(residual, None, norm_weight, 1e-6, whole)
+
+        def by_library() -> None:
+            delta = torch.mm(x, weight.t())
+            add_rmsnorm(residual, delta, norm_weight, 1e-6, whole)
+        candidates = {"pair": by_pair, "library": by_library}
+    elif kind == "qkv":
+        d, page = 128, 64
+        q = torch.empty((rows, n_q, d), dtype=torch.bfloat16, device=device)
+        pools = [torch.empty(((rows + page - 1) // page, n_kv, page, d), dtype=torch.bfloat16, device=device) for _ in range(2)]
+        slots = torch.arange(rows, dtype=torch.int32, device=device)
+        norm_weight = torch.ones(d, dtype=torch.bfloat16, device=device)
+        cos_sin = torch.zeros((rows, d // 2, 2), dtype=torch.float32, device=device)
+
+        def by_library() -> None:
+            torch.mm(x, weight.t(), out=whole)
+            qk_norm_rope_append(whole, slots, norm_weight, norm_weight, 1e-6, cos_sin, d, False, pools[0], pools[1], n_q, n_kv, d, q)
+        candidates = {"pair": lambda: linear_pair_qkv(x, weight, slots, norm_weight, norm_weight, 1e-6, cos_sin, pools[0],
+                                                      pools[1], n_q, n_kv, q),
+                      "library": by_library}
+    else:
+        raise KernelError(f"no many-row product of kind {kind!r}")
+    times = _sample_times(candidates, x, rounds=4, source=source)
+    _many_row_times[key] = {name: round(1e3 * t, 1) for name, t in times.items()}
+    return "pair" if times["pair"] <= times["library"] else "library"
 
 
 def pair_fill(device: torch.device, m: int, n: int) -> float:
@@ -551,15 +636,15 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: b
 QKV_IN_PRODUCT = __import__("os").environ.get("MINISERVE_B200_QKV_IN_PRODUCT", "1") == "1"
 
 
-def qkv_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor, head_dim: int, cos_sin,
-                             rotary_dim: int, interleaved: bool) -> bool:
+def qkv_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor, head_dim: int, n_q: int, n_kv: int,
+                             cos_sin, rotary_dim: int, interleaved: bool) -> bool:
     """Whether a q/k/v projection of ``rows`` rows can norm, rotate and append its heads as it stores them
     (:func:`linear_pair_qkv`): bfloat16, so many rows that it goes to :func:`linear_pair`, heads of 128, and no
     rotation or the half-split one over the whole head."""
     n, k = weight.shape
     return (QKV_IN_PRODUCT and dtype == torch.bfloat16 and head_dim == 128 and k % 8 == 0
             and (cos_sin is None or (rotary_dim == head_dim and not interleaved))
-            and pair_preferred(weight.device, rows, n))
+            and pair_preferred(weight.device, rows, n) and _pair_or_library("qkv", rows, weight, n_q, n_kv) == "pair")
 
 
 def linear_pair_qkv(x: torch.Tensor, weight: torch.Tensor, slots: torch.Tensor, q_weight: Optional[torch.Tensor],
@@ -710,7 +795,8 @@ def _stored_choice(kind: str, n: int, k: int) -> Optional[str]:
             value = json.load(handle).get(f"{kind} {n}x{k}")
     except (OSError, ValueError):
         return None
-    allowed = ("skinny", "stream", "wide", "library") if kind == "linear" else ("wide", "separate")
+    allowed = (("skinny", "stream", "wide", "library") if kind == "linear" else ("pair", "library") if kind.startswith("rows")
+               else ("wide", "separate"))
     return value if value in allowed else None
 
 
@@ -737,7 +823,7 @@ def _store_choice(kind: str, n: int, k: int, choice: str) -> None:
 TUNING_REPEATS = 8      # a candidate this many times in one captured graph
 
 
-def _sample_times(candidates: dict, x: torch.Tensor, rounds: int = 7) -> dict:
+def _sample_times(candidates: dict, x: torch.Tensor, rounds: int = 7, source: Optional[torch.Tensor] = None) -> dict:
     """Device time in milliseconds of each of ``candidates`` (name -> callable reading ``x``), measured the way
     a decode step runs them: in a captured graph, after a small kernel of this library that writes ``x`` (so
     that a candidate which can start before its predecessor ends does so), with the L2 cache overwritten
@@ -746,7 +832,10 @@ def _sample_times(candidates: dict, x: torch.Tensor, rounds: int = 7) -> dict:
     meets all of them alike; the figure is the lower quartile of a graph's samples."""
     device = x.device
     flush = torch.empty(FLUSH_BYTES // 4, dtype=torch.float32, device=device)
-    source, weight = torch.zeros_like(x), torch.ones(x.shape[-1], dtype=x.dtype, device=device)
+    # (``source``: what ``x`` is made from before every run; zeros unless the candidates' speed depends on the data,
+    # as that of tensor-core products under the power limit does)
+    source = torch.zeros_like(x) if source is None else source
+    weight = torch.ones(x.shape[-1], dtype=x.dtype, device=device)
 
     def capture(run) -> torch.cuda.CUDAGraph:
         def sequence() -> None:
@@ -925,7 +1014,7 @@ def add_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor
     25 MB instead of 50 MB a norm)."""
     n, k = weight.shape
     return (ADD_IN_PRODUCT and dtype == torch.bfloat16 and rows > SKINNY_MAX_ROWS and n % 4 == 0 and k % 8 == 0
-            and pair_preferred(weight.device, rows, n))
+            and pair_preferred(weight.device, rows, n) and _pair_or_library("add", rows, weight) == "pair")
 
 
 def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> None:
@@ -964,7 +1053,9 @@ def fold_supported(rows: int, dtype: torch.dtype, producer: torch.Tensor, consum
         # the norm kernel, 8,192 rows 71.9 against 89.4 us; 2,048 rows, one tile per pair, 25.8 against 26.1 us)
         return (pair_preferred(producer.device, rows, producer.shape[0])
                 and pair_rounds(producer.device, rows, producer.shape[0]) >= 2
-                and pair_preferred(consumer.device, rows, consumer.shape[0], gated=consumer_gated))
+                and pair_preferred(consumer.device, rows, consumer.shape[0], gated=consumer_gated)
+                and _pair_or_library("add", rows, producer) == "pair"
+                and _pair_or_library("gated" if consumer_gated else "plain", rows, consumer) == "pair")
     for weight, gated in ((producer, False), (consumer, consumer_gated)):
         n, k = weight.shape
         if k % 8 or wide_supports(n, k) != 2:
@@ -1018,7 +1109,8 @@ def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats
     if x.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and _gated_choice(x, weight) == "wide":
         linear_wide(x, weight, out, gated=True)
         return
-    if x.dtype == torch.bfloat16 and k % 8 == 0 and pair_preferred(x.device, m, two_i, gated=True):
+    if (x.dtype == torch.bfloat16 and k % 8 == 0 and pair_preferred(x.device, m, two_i, gated=True)
+            and _pair_or_library("gated", m, weight) == "pair"):
         linear_pair(x, weight, out, gated=True)      # many rows: the activation is applied as the tiles are stored
         return
     gate_up = torch.empty((m, two_i), dtype=x.dtype, device=x.device)

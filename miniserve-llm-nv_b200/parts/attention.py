@@ -106,7 +106,7 @@ class Attention(Part):
         slots = cache.slots if cache.writable else torch.full_like(cache.slots, -1)
         fused = self.position.fused_args(ctx)
         attended = ctx.buffer("attention.attended", (n, n_q, d), x.dtype)
-        in_product = fused is not None and kernels.qkv_in_product_supported(n, x.dtype, self.qkv_weight, d, *fused)
+        in_product = fused is not None and kernels.qkv_in_product_supported(n, x.dtype, self.qkv_weight, d, n_q, n_kv, *fused)
         if not in_product:
             qkv = ctx.buffer("attention.qkv", (n, (n_q + 2 * n_kv) * d), x.dtype)
             kernels.linear(x, self.qkv_weight, qkv, row_stats=stats)

@@ -693,7 +693,34 @@ def test_qkv_projection_with_norm_rotation_and_append_in_its_epilogue(kernels, m
         assert float((got != expected).float().mean()) < 0.02          # and nearly all of them exactly
 
 
-def test_many_row_fold_is_offered_where_it_pays(kernels):
+def test_many_row_products_choose_between_the_own_kernel_and_the_library_by_measurement(kernels, monkeypatch):
+    """Every kind of many-row product is timed both ways once per count of row tiles and weight shape, the faster way
+    is kept with the times, and a second question measures nothing."""
+    monkeypatch.setattr(kernels, "LINEAR_TUNING", True)
+    monkeypatch.setattr(kernels, "_many_row_choices", {})
+    n_q, n_kv = 4, 2
+    weights = {"plain": rand((1024, 512), torch.bfloat16, 1, 0.1), "gated": rand((2048, 512), torch.bfloat16, 2, 0.1),
+               "add": rand((512, 1024), torch.bfloat16, 3, 0.1), "qkv": rand(((n_q + 2 * n_kv) * 128, 512), torch.bfloat16, 4, 0.1)}
+    first = {kind: kernels._pair_or_library(kind, 600, weight, n_q, n_kv) for kind, weight in weights.items()}
+    kernels.check_device_errors(torch.device("cuda"))
+    assert set(first.values()) <= {"pair", "library"}
+    recorded = kernels.many_row_choices()
+    for kind, weight in weights.items():
+        choice, times = recorded[(0, kind, 3, weight.shape[0], weight.shape[1])]
+        assert choice == first[kind] == min(times, key=times.get) and set(times) == {"pair", "library"}
+        assert all(0 < t < 1000 for t in times.values())
+
+    def never(*args):
+        raise AssertionError("measured twice")
+
+    monkeypatch.setattr(kernels, "_measure_many_rows", never)
+    assert {kind: kernels._pair_or_library(kind, 700, weight, n_q, n_kv) for kind, weight in weights.items()} == first
+    monkeypatch.setattr(kernels, "LINEAR_TUNING", False)
+    assert kernels._pair_or_library("plain", 5000, weights["plain"]) == "pair"        # no measurement: the own kernel
+
+
+def test_many_row_fold_is_offered_where_it_pays(kernels, monkeypatch):
+    monkeypatch.setattr(kernels, "LINEAR_TUNING", False)        # the rule alone
     hidden, inter = 2048, 6144
     o, gate_up = rand((hidden, hidden), torch.bfloat16, 1), rand((2 * inter, hidden), torch.bfloat16, 2)
     assert kernels.fold_supported(4096, torch.bfloat16, o, gate_up, True)

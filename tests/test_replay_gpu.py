@@ -166,6 +166,7 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
         calls["qkv"] += 1
         return inner_qkv(*args, **named)
 
+    monkeypatch.setattr(kernels, "LINEAR_TUNING", False)        # the rule decides, not a measurement on this box
     monkeypatch.setattr(kernels, "linear_pair", counted)
     monkeypatch.setattr(kernels, "linear_pair_residual", counted_residual)
     monkeypatch.setattr(kernels, "linear_pair_qkv", counted_qkv)
