@@ -303,7 +303,7 @@ class Bench:
 
         for _ in range(self.warmup):
             once()
-        return sorted(self.event_time(once) for _ in range(5))[2]
+        return sorted(self.event_time(once) for _ in range(11))[5]
 
     def prefill_flops(self, tokens: int) -> float:
         c = self.config

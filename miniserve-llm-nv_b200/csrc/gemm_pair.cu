@@ -9,7 +9,10 @@
 // block's.  Nothing is loaded for both blocks at once: every block fetches its own halves.
 //
 // A pair walks over the tiles (pair index, then every (number of pairs)-th; neighbours in this order share their W
-// tile).  In each block:
+// tile).  In the wide form a tile is 256 x 512: the same rows of X meet two W tiles of 256 rows, one accumulator each,
+// so that a block loads 48 KB per k-block for twice the MMAs (24 KB per 256 x 256 of work instead of 32 KB: what the
+// blocks fetch from the L2 cache is what bounds the kernel); both accumulators are complete together, so only the
+// second one's read-out overlaps nothing.  In each block:
 //   warp 0      one thread issues the TMA loads of this block's halves into a ring of stages; their arrival is
 //               counted on the EVEN block's "full" barrier of the stage;
 //   warp 1      allocates tensor memory for two accumulators (both blocks, together); in the even block one thread
@@ -60,7 +63,6 @@ constexpr int BK = 64, UMMA_K = 16;
 __host__ __device__ constexpr int read_warps(int epilogue) { return epilogue == 4 ? 8 : 4; }
 __host__ __device__ constexpr int threads(int epilogue) { return 32 * (2 + read_warps(epilogue)); }
 constexpr int ACCUMULATORS = 2;
-constexpr int STAGE_BYTES = 2 * HALF * BK * 2;     // this block's halves of X and W for one k-block
 constexpr int OUT_BUFFER = 32 * 128;               // 32 rows x 128 bytes: what one read-out warp stores at a time
 // A read-out warp's buffers: two to store from; in the residual epilogue two boxes of the stream and one of results;
 // in the q/k/v epilogue 32 rows of a head in bfloat16.
@@ -133,12 +135,13 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
   return packed;
 }
 
-template <int STAGES, int EPILOGUE, typename OutT>
+template <int STAGES, int EPILOGUE, typename OutT, bool WIDE>
 __global__ void __launch_bounds__(threads(EPILOGUE), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                  const __grid_constant__ CUtensorMap map_out, const __grid_constant__ CUtensorMap map_residual,
                  int through_tma, OutT* __restrict__ out, int M, int N, int K, Fold fold, Heads heads,
                  int* __restrict__ error_flag) {
+  static_assert(!(WIDE && EPILOGUE == EPI_RESIDUAL), "the residual epilogue's boxes run on over tiles of 256 columns");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACCUMULATORS], acc_empty[ACCUMULATORS];
@@ -149,7 +152,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned rank = cluster_rank();                 // 0: issues the MMAs
   const int pair_index = (int)cluster_id_x(), pairs = (int)(gridDim.x / 2);
-  const int tiles_m = (M + TILE - 1) / TILE, tiles_n = (N + TILE - 1) / TILE;
+  constexpr int PARTS = WIDE ? 2 : 1;                   // W tiles of 256 rows (accumulators) per tile
+  constexpr int STAGE = (1 + PARTS) * HALF * BK * 2;    // this block's rows of X and of each W tile for one k-block
+  const int tiles_m = (M + TILE - 1) / TILE, tiles_n = (N + PARTS * TILE - 1) / (PARTS * TILE);
   const int n_tiles = tiles_m * tiles_n;
   const int num_k = (K + BK - 1) / BK;
 
@@ -193,17 +198,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       bool ok = true;
       for (int tile = pair_index; tile < n_tiles && ok; tile += pairs) {
         const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
-        const int x_row = tile_m * TILE + (int)rank * HALF, w_row = tile_n * TILE + (int)rank * HALF;
+        const int x_row = tile_m * TILE + (int)rank * HALF, w_row = tile_n * PARTS * TILE + (int)rank * HALF;
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int stage = it % STAGES;
           const unsigned phase = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, error_flag, 1))) break;
-          unsigned char* a_s = smem + (size_t)stage * STAGE_BYTES;
-          unsigned char* b_s = a_s + HALF * BK * 2;
-          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          unsigned char* a_s = smem + (size_t)stage * STAGE;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * STAGE);
           const unsigned full = address_in_rank(smem_u32(&full_bar[stage]), 0);
           tma_load_2d_pair(a_s, &map_x, full, kb * BK, x_row);
-          tma_load_2d_pair(b_s, &map_w, full, kb * BK, w_row);
+#pragma unroll
+          for (int part = 0; part < PARTS; ++part)
+            tma_load_2d_pair(a_s + (1 + part) * HALF * BK * 2, &map_w, full, kb * BK, w_row + part * TILE);
         }
       }
     }
@@ -213,31 +219,43 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       constexpr unsigned idesc = umma_idesc(TILE, TILE);
       int it = 0, done = 0;
       bool ok = true;
-      for (int tile = pair_index; tile < n_tiles && ok; tile += pairs, ++done) {
-        const int buf = done % ACCUMULATORS;
-        if (!(ok = mbar_wait(&acc_empty[buf], ((done / ACCUMULATORS) & 1) ^ 1, error_flag, 4))) break;
+      for (int tile = pair_index; tile < n_tiles && ok; tile += pairs, done += PARTS) {
+        // (wide: both accumulators, which the read-out of the tile before frees one after the other)
+#pragma unroll
+        for (int part = 0; part < PARTS; ++part) {
+          const int buf = (done + part) % ACCUMULATORS;
+          ok = ok && mbar_wait(&acc_empty[buf], (((done + part) / ACCUMULATORS) & 1) ^ 1, error_flag, 4);
+        }
+        if (!ok) break;
         tmem_fence_after();
-        const unsigned accumulator = tmem_base + buf * TILE;
         for (int kb = 0; kb < num_k; ++kb, ++it) {
           const int stage = it % STAGES;
           const unsigned phase = (it / STAGES) & 1;
           if (!(ok = mbar_wait(&full_bar[stage], phase, error_flag, 2))) break;
           tmem_fence_after();
-          unsigned char* a_s = smem + (size_t)stage * STAGE_BYTES;
-          unsigned char* b_s = a_s + HALF * BK * 2;
-          const uint64_t a_desc = umma_desc(a_s), b_desc = umma_desc(b_s);
+          unsigned char* a_s = smem + (size_t)stage * STAGE;
+          const uint64_t a_desc = umma_desc(a_s);
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)     // 16 elements (32 bytes) further inside the swizzled row: +2 units
-            umma_bf16_pair(accumulator, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int part = 0; part < PARTS; ++part) {
+            const unsigned accumulator = tmem_base + ((done + part) % ACCUMULATORS) * TILE;
+            const uint64_t b_desc = umma_desc(a_s + (1 + part) * HALF * BK * 2);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)     // 16 elements (32 bytes) further inside the swizzled row: +2 units
+              umma_bf16_pair(accumulator, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
           umma_commit_pair(&empty_bar[stage]);      // both blocks' stage is free once these MMAs have read it
         }
-        if (ok) umma_commit_pair(&acc_full[buf]);   // the accumulator is complete in both blocks
+        if (ok) {
+#pragma unroll
+          for (int part = 0; part < PARTS; ++part)
+            umma_commit_pair(&acc_full[(done + part) % ACCUMULATORS]);   // the accumulators are complete in both blocks
+        }
       }
     }
   } else {
     // ---------------- read-out: warps 2..5 own the tensor-memory lane quarters 2, 3, 0, 1 of this block
     const int quarter = warp & 3;
-    unsigned char* out_s = smem + (size_t)STAGES * STAGE_BYTES;
+    unsigned char* out_s = smem + (size_t)STAGES * STAGE;
     int done = 0, stores = 0;
     bool ok = true;
     unsigned boxes = 0;                      // residual epilogue: boxes of the stream taken so far (they alternate between two buffers)
@@ -247,8 +265,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         tma_load_box(out_s + quarter * warp_bytes(EPILOGUE) + b * OUT_BUFFER, &map_residual, &residual_bar[quarter][b],
                      (pair_index / tiles_m) * TILE + 32 * b, (pair_index % tiles_m) * TILE + (int)rank * HALF + quarter * 32);
     }
-    for (int tile = pair_index; tile < n_tiles; tile += pairs, ++done) {
-      const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+    for (int tile = pair_index; tile < n_tiles && ok; tile += pairs)
+    for (int part = 0; part < PARTS; ++part, ++done) {
+      // (wide: a tile's two accumulators one after the other, each read out like a tile of 256 columns)
+      const int tile_m = tile % tiles_m, tile_n = (tile / tiles_m) * PARTS + part;     // tile_n: in tiles of 256 columns
       const int buf = done % ACCUMULATORS;
       const int row = tile_m * TILE + (int)rank * HALF + quarter * 32 + lane;
       ok = ok && mbar_wait(&acc_full[buf], (done / ACCUMULATORS) & 1, error_flag, 3);
@@ -559,7 +579,7 @@ static bool out_map(CUtensorMap* map, void* base, int rows, int cols, bool float
   return true;
 }
 
-template <int STAGES, int EPILOGUE, typename OutT>
+template <int STAGES, int EPILOGUE, typename OutT, bool WIDE = false>
 int launch(const void* X, const void* W, void* out, int M, int N, int K, const Fold& fold, float* residual, int* error_flag,
            cudaStream_t stream, const Heads& heads = Heads{}) {
   CUtensorMap map_x, map_w, map_out, map_residual;
@@ -576,8 +596,8 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, const F
                "gemm_pair: the residual epilogue wants N %d a multiple of 8 and 16-byte aligned matrices", N);
     MS_REQUIRE(out_map(&map_residual, residual, M, N, true), "gemm_pair: cuTensorMapEncodeTiled failed for the residual stream");
   }
-  auto kernel = gemm_pair_kernel<STAGES, EPILOGUE, OutT>;
-  const size_t smem = (size_t)STAGES * STAGE_BYTES + read_warps(EPILOGUE) * warp_bytes(EPILOGUE) + 1024;
+  auto kernel = gemm_pair_kernel<STAGES, EPILOGUE, OutT, WIDE>;
+  const size_t smem = (size_t)STAGES * (WIDE ? 3 : 2) * HALF * BK * 2 + read_warps(EPILOGUE) * warp_bytes(EPILOGUE) + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -591,7 +611,8 @@ int launch(const void* X, const void* W, void* out, int M, int N, int K, const F
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
       sms = 2;
   }
-  const long long tiles = (long long)((N + TILE - 1) / TILE) * ((M + TILE - 1) / TILE);
+  const int tile_columns = WIDE ? 2 * TILE : TILE;
+  const long long tiles = (long long)((N + tile_columns - 1) / tile_columns) * ((M + TILE - 1) / TILE);
   MS_REQUIRE(tiles <= 1073741823LL, "gemm_pair: %lld tiles in one launch is too many", tiles);
   const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
   cudaLaunchConfig_t config = {};
@@ -628,10 +649,11 @@ using namespace ms;
 //               receives the rows' sums of squares over each tile's columns (N a multiple of 8).
 // in_partials [in_count, M] (epilogues 0 and 2; null: none): sums of squares of X's rows before they were scaled
 // by a norm weight; the results are multiplied by 1 / sqrt(total / K + eps) before they are rounded.
+// wide != 0 (not with epilogue 3): tiles of 256 x 512 (two accumulators side by side) instead of 256 x 256.
 // error_flag: one int on the device, zero before the first call; a kernel that gave up waiting writes a
 // non-zero code there (1 producer, 2 MMA issue, 3 read-out, 4 accumulator, 5 residual box), which the caller
 // checks when it synchronises.
-MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtype, int epilogue, int M, int N, int K,
+MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtype, int epilogue, int wide, int M, int N, int K,
                            const float* in_partials, int in_count, float eps, float* residual, const void* norm_weight,
                            int norm_dtype, float* out_partials, int* error_flag, cudaStream_t stream) {
   if (M == 0 || N == 0) return 0;
@@ -640,7 +662,7 @@ MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtyp
   MS_REQUIRE(error_flag != nullptr, "gemm_pair: an error flag on the device is required");
   MS_REQUIRE(in_partials == nullptr || (in_count > 0 && (epilogue == pair::EPI_STORE || epilogue == pair::EPI_GATED)),
              "gemm_pair: row statistics go with the storing and the gated epilogue (count %d, epilogue %d)", in_count, epilogue);
-  constexpr int STAGES = 6, STAGES_RESIDUAL = 5;      // what fits beside the read-out warps' buffers
+  constexpr int STAGES = 6, STAGES_RESIDUAL = 5, STAGES_WIDE = 4;      // what fits beside the read-out warps' buffers
   const pair::Fold fold{in_partials, in_count, eps, norm_weight, norm_dtype, out_partials, residual};
   if (epilogue == pair::EPI_RESIDUAL) {
     MS_REQUIRE(out_dtype == MS_BF16 && residual != nullptr && norm_weight != nullptr && out_partials != nullptr &&
@@ -650,15 +672,21 @@ MS_EXPORT int ms_gemm_pair(const void* X, const void* W, void* out, int out_dtyp
   }
   if (epilogue == pair::EPI_ADD_F32) {
     MS_REQUIRE(out_dtype == MS_F32, "gemm_pair: the adding epilogue works on a float32 matrix");
-    return pair::launch<STAGES, pair::EPI_ADD_F32, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
+    return wide ? pair::launch<STAGES_WIDE, pair::EPI_ADD_F32, float, true>(X, W, out, M, N, K, fold, nullptr, error_flag, stream)
+                : pair::launch<STAGES, pair::EPI_ADD_F32, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   }
   if (epilogue == pair::EPI_GATED) {
     MS_REQUIRE(out_dtype == MS_BF16 && N % 16 == 0, "gemm_pair: the gated epilogue stores bfloat16 and wants N %d a multiple of 16", N);
-    return pair::launch<STAGES, pair::EPI_GATED, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
+    return wide ? pair::launch<STAGES_WIDE, pair::EPI_GATED, __nv_bfloat16, true>(X, W, out, M, N, K, fold, nullptr, error_flag, stream)
+                : pair::launch<STAGES, pair::EPI_GATED, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   }
   MS_REQUIRE(epilogue == pair::EPI_STORE, "gemm_pair: unknown epilogue %d", epilogue);
-  if (out_dtype == MS_BF16) return pair::launch<STAGES, pair::EPI_STORE, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
-  if (out_dtype == MS_F32) return pair::launch<STAGES, pair::EPI_STORE, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
+  if (out_dtype == MS_BF16)
+    return wide ? pair::launch<STAGES_WIDE, pair::EPI_STORE, __nv_bfloat16, true>(X, W, out, M, N, K, fold, nullptr, error_flag, stream)
+                : pair::launch<STAGES, pair::EPI_STORE, __nv_bfloat16>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
+  if (out_dtype == MS_F32)
+    return wide ? pair::launch<STAGES_WIDE, pair::EPI_STORE, float, true>(X, W, out, M, N, K, fold, nullptr, error_flag, stream)
+                : pair::launch<STAGES, pair::EPI_STORE, float>(X, W, out, M, N, K, fold, nullptr, error_flag, stream);
   MS_FAIL("gemm_pair: unknown output type code %d", out_dtype);
 }
 

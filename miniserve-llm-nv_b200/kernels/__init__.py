@@ -427,9 +427,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats: 
         if choice == "wide":
             linear_wide(x, weight, out)
             return
-    if k % 8 == 0 and out.dtype == torch.bfloat16 and pair_preferred(x.device, m, n) and _pair_or_library("plain", m, weight) == "pair":
-        linear_pair(x, weight, out)
-        return
+    if k % 8 == 0 and out.dtype == torch.bfloat16 and pair_preferred(x.device, m, n):
+        choice = _pair_or_library("plain", m, weight)
+        if choice != "library":
+            linear_pair(x, weight, out, wide=choice == "wide")
+            return
     if USE_TCGEN05_GEMM and m >= 128 and k % 8 == 0:
         linear_tcgen05(x, weight, out)
         return
@@ -451,7 +453,7 @@ USE_TCGEN05_GEMM = __import__("os").environ.get("MINISERVE_B200_TCGEN05_GEMM", "
 PAIR_MIN_FILL = 0.8            # of the pairs' time in use, by the count of tiles
 
 
-_many_row_choices: dict = {}         # (device index, kind, row tiles, N, K) -> "pair" | "library"
+_many_row_choices: dict = {}         # (device index, kind, row tiles, N, K) -> "pair" | "wide" | "library"
 _many_row_times: dict = {}           # the same keys -> {candidate: microseconds} as measured
 
 
@@ -462,7 +464,8 @@ def many_row_choices() -> dict:
 
 def _pair_or_library(kind: str, rows: int, weight: torch.Tensor, n_q: int = 0, n_kv: int = 0) -> str:
     """For a product of ``rows`` rows that :func:`pair_preferred` lets through: the two-block kernel with the
-    element-wise work of ``kind`` in its epilogue ("pair"), or cuBLAS followed by the separate kernel ("library").
+    element-wise work of ``kind`` in its epilogue ("pair"; "wide": with tiles of 256 x 512, which fetch a quarter less
+    from the L2 cache but are fewer), or cuBLAS followed by the separate kernel ("library").
     Measured once per kind, count of 256-row tiles and weight shape, on the weight itself, at the first eager call
     that meets it (kept in the choices file like the few-row choices); with MINISERVE_B200_LINEAR_TUNING=0 it is
     the two-block kernel.  Kinds: "plain" (store), "gated" (against the product and the activation kernel), "add"
@@ -495,26 +498,29 @@ def _measure_many_rows(key: tuple, rows: int, weight: torch.Tensor, n_q: int, n_
     x = torch.empty_like(source)
     whole = torch.empty((rows, n), dtype=torch.bfloat16, device=device)
     if kind == "plain":
-        candidates = {"pair": lambda: linear_pair(x, weight, whole), "library": lambda: torch.mm(x, weight.t(), out=whole)}
+        candidates = {"pair": lambda: linear_pair(x, weight, whole, wide=False),
+                      "wide": lambda: linear_pair(x, weight, whole, wide=True),
+                      "library": lambda: torch.mm(x, weight.t(), out=whole)}
     elif kind == "gated":
         half = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=device)
 
         def by_library() -> None:
             torch.mm(x, weight.t(), out=whole)
             silu_mul(whole, half, paired=True)
-        candidates = {"pair": lambda: linear_pair(x, weight, half, gated=True), "library": by_library}
+        candidates = {"pair": lambda: linear_pair(x, weight, half, gated=True, wide=False),
+                      "wide": lambda: linear_pair(x, weight, half, gated=True, wide=True), "library": by_library}
     elif kind == "add":
         residual = torch.zeros((rows, n), dtype=torch.float32, device=device)
         norm_weight = torch.ones(n, dtype=torch.bfloat16, device=device)
 
-        def by_pair() -> None:
-            linear_pair(x, weight, residual, add=True)
+        def by_pair(wide: bool) -> None:
+            linear_pair(x, weight, residual, add=True, wide=wide)
             add_rmsnorm(residual, None, norm_weight, 1e-6, whole)
 
         def by_library() -> None:
             delta = torch.mm(x, weight.t())
             add_rmsnorm(residual, delta, norm_weight, 1e-6, whole)
-        candidates = {"pair": by_pair, "library": by_library}
+        candidates = {"pair": lambda: by_pair(False), "wide": lambda: by_pair(True), "library": by_library}
     elif kind == "qkv":
         d, page = 128, 64
         q = torch.empty((rows, n_q, d), dtype=torch.bfloat16, device=device)
@@ -533,7 +539,7 @@ def _measure_many_rows(key: tuple, rows: int, weight: torch.Tensor, n_q: int, n_
         raise KernelError(f"no many-row product of kind {kind!r}")
     times = _sample_times(candidates, x, rounds=4, source=source)
     _many_row_times[key] = {name: round(1e3 * t, 1) for name, t in times.items()}
-    return "pair" if times["pair"] <= times["library"] else "library"
+    return min(times, key=times.get)
 
 
 def pair_fill(device: torch.device, m: int, n: int) -> float:
@@ -603,8 +609,11 @@ def linear_tcgen05(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add
                                      _i(n), _i(k), _ptr(device_error_flag(x.device)), _stream()))
 
 
+PAIR_WIDE = __import__("os").environ.get("MINISERVE_B200_PAIR_WIDE", "0") == "1"
+
+
 def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: bool = False, gated: bool = False,
-                row_stats: Optional["RowStats"] = None) -> None:
+                row_stats: Optional["RowStats"] = None, wide: Optional[bool] = None) -> None:
     """``out = x @ weight^T`` by the kernel in which two thread blocks share each 256 x 256 tile (tcgen05 with
     ``cta_group::2``).  ``add``: ``out += ...`` on a float32 ``out``.  ``gated``: ``weight`` is
     :func:`interleave_gate_up` of a gate and an up projection and ``out [M, N / 2] = silu(gate) * up``.
@@ -628,6 +637,7 @@ def linear_pair(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, add: b
             raise KernelError(f"linear_pair: row statistics of shape {tuple(row_stats.partials.shape)} for {m} rows, "
                               f"{row_stats.count} tiles")
     _check(library().ms_gemm_pair(_ptr(x), _ptr(weight), _ptr(out), _i(_code(out.dtype)), _i(2 if gated else 1 if add else 0),
+                                  _i(1 if (PAIR_WIDE if wide is None else wide) else 0),
                                   _i(m), _i(n), _i(k), _ptr(row_stats.partials if row_stats else None),
                                   _i(row_stats.count if row_stats else 0), _f(row_stats.eps if row_stats else 0.0), None, None,
                                   _i(0), None, _ptr(device_error_flag(x.device)), _stream()))
@@ -706,7 +716,7 @@ def linear_pair_residual(x: torch.Tensor, weight: torch.Tensor, residual: torch.
     if n % 8 or partials.dim() != 2 or partials.shape[1] != m or partials.shape[0] < tiles:
         raise KernelError(f"linear_pair_residual: weight {tuple(weight.shape)}, partials {tuple(partials.shape)} for {tiles} "
                           f"tiles of {m} rows")
-    _check(library().ms_gemm_pair(_ptr(x), _ptr(weight), _ptr(x_next), _i(1), _i(3), _i(m), _i(n), _i(k), None, _i(0),
+    _check(library().ms_gemm_pair(_ptr(x), _ptr(weight), _ptr(x_next), _i(1), _i(3), _i(0), _i(m), _i(n), _i(k), None, _i(0),
                                   _f(0.0), _ptr(residual), _ptr(norm_weight), _i(_code(norm_weight.dtype)), _ptr(partials),
                                   _ptr(device_error_flag(x.device)), _stream()))
     return RowStats(partials, tiles, eps, per_row=True)
@@ -795,7 +805,7 @@ def _stored_choice(kind: str, n: int, k: int) -> Optional[str]:
             value = json.load(handle).get(f"{kind} {n}x{k}")
     except (OSError, ValueError):
         return None
-    allowed = (("skinny", "stream", "wide", "library") if kind == "linear" else ("pair", "library") if kind.startswith("rows")
+    allowed = (("skinny", "stream", "wide", "library") if kind == "linear" else ("pair", "wide", "library") if kind.startswith("rows")
                else ("wide", "separate"))
     return value if value in allowed else None
 
@@ -1014,12 +1024,12 @@ def add_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor
     25 MB instead of 50 MB a norm)."""
     n, k = weight.shape
     return (ADD_IN_PRODUCT and dtype == torch.bfloat16 and rows > SKINNY_MAX_ROWS and n % 4 == 0 and k % 8 == 0
-            and pair_preferred(weight.device, rows, n) and _pair_or_library("add", rows, weight) == "pair")
+            and pair_preferred(weight.device, rows, n) and _pair_or_library("add", rows, weight) != "library")
 
 
 def linear_add(x: torch.Tensor, weight: torch.Tensor, residual: torch.Tensor) -> None:
     """``residual += x @ weight^T`` (float32, in place), where :func:`add_in_product_supported` said so."""
-    linear_pair(x, weight, residual, add=True)
+    linear_pair(x, weight, residual, add=True, wide=_pair_or_library("add", x.shape[0], weight) == "wide")
 
 
 def residual_partials_shape(rows: int, n: int, k: int) -> tuple:
@@ -1054,8 +1064,8 @@ def fold_supported(rows: int, dtype: torch.dtype, producer: torch.Tensor, consum
         return (pair_preferred(producer.device, rows, producer.shape[0])
                 and pair_rounds(producer.device, rows, producer.shape[0]) >= 2
                 and pair_preferred(consumer.device, rows, consumer.shape[0], gated=consumer_gated)
-                and _pair_or_library("add", rows, producer) == "pair"
-                and _pair_or_library("gated" if consumer_gated else "plain", rows, consumer) == "pair")
+                and _pair_or_library("add", rows, producer) != "library"
+                and _pair_or_library("gated" if consumer_gated else "plain", rows, consumer) != "library")
     for weight, gated in ((producer, False), (consumer, consumer_gated)):
         n, k = weight.shape
         if k % 8 or wide_supports(n, k) != 2:
@@ -1109,10 +1119,11 @@ def gated_up(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, row_stats
     if x.dtype == torch.bfloat16 and 0 < m <= SKINNY_MAX_ROWS and _gated_choice(x, weight) == "wide":
         linear_wide(x, weight, out, gated=True)
         return
-    if (x.dtype == torch.bfloat16 and k % 8 == 0 and pair_preferred(x.device, m, two_i, gated=True)
-            and _pair_or_library("gated", m, weight) == "pair"):
-        linear_pair(x, weight, out, gated=True)      # many rows: the activation is applied as the tiles are stored
-        return
+    if x.dtype == torch.bfloat16 and k % 8 == 0 and pair_preferred(x.device, m, two_i, gated=True):
+        choice = _pair_or_library("gated", m, weight)
+        if choice != "library":
+            linear_pair(x, weight, out, gated=True, wide=choice == "wide")    # many rows: the activation is applied as the tiles are stored
+            return
     gate_up = torch.empty((m, two_i), dtype=x.dtype, device=x.device)
     linear(x, weight, gate_up)
     silu_mul(gate_up, out, paired=True)

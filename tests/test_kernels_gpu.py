@@ -703,11 +703,12 @@ def test_many_row_products_choose_between_the_own_kernel_and_the_library_by_meas
                "add": rand((512, 1024), torch.bfloat16, 3, 0.1), "qkv": rand(((n_q + 2 * n_kv) * 128, 512), torch.bfloat16, 4, 0.1)}
     first = {kind: kernels._pair_or_library(kind, 600, weight, n_q, n_kv) for kind, weight in weights.items()}
     kernels.check_device_errors(torch.device("cuda"))
-    assert set(first.values()) <= {"pair", "library"}
+    assert set(first.values()) <= {"pair", "wide", "library"}
     recorded = kernels.many_row_choices()
     for kind, weight in weights.items():
         choice, times = recorded[(0, kind, 3, weight.shape[0], weight.shape[1])]
-        assert choice == first[kind] == min(times, key=times.get) and set(times) == {"pair", "library"}
+        assert choice == first[kind] == min(times, key=times.get)
+        assert set(times) == ({"pair", "library"} if kind == "qkv" else {"pair", "wide", "library"})
         assert all(0 < t < 1000 for t in times.values())
 
     def never(*args):
@@ -796,7 +797,8 @@ def test_linear_tcgen05(kernels, m, n, k, out_dtype, add):
     (300, 331, 200, torch.float32, "store"), (2048, 4096, 2048, torch.bfloat16, "store"), (257, 6144, 520, torch.bfloat16, "store"),
     (5000, 2048, 256, torch.bfloat16, "store"), (512, 2048, 6144, torch.float32, "add"), (150, 96, 224, torch.float32, "add"),
     (2048, 12288, 2048, torch.bfloat16, "gated"), (300, 656, 136, torch.bfloat16, "gated"), (40, 16, 64, torch.bfloat16, "gated")])
-def test_linear_pair(kernels, m, n, k, out_dtype, mode):
+@pytest.mark.parametrize("wide", [False, True])
+def test_linear_pair(kernels, m, n, k, out_dtype, mode, wide):
     """The product in which two thread blocks share a 256 x 256 tile (tcgen05 with cta_group::2): whole and ragged
     tiles, more tiles than pairs of multiprocessors, every epilogue, no wait given up."""
     x, w = rand((m, k), torch.bfloat16, 48, 0.5), rand((n, k), torch.bfloat16, 49, 0.1)
@@ -810,7 +812,7 @@ def test_linear_pair(kernels, m, n, k, out_dtype, mode):
         expected = (torch.nn.functional.silu(blocks[:, :, 0]) * blocks[:, :, 1]).reshape(m, n // 2)
     else:
         out = torch.full((m, n), 7.0, dtype=out_dtype).cuda()
-    kernels.linear_pair(x, w, out, add=mode == "add", gated=mode == "gated")
+    kernels.linear_pair(x, w, out, add=mode == "add", gated=mode == "gated", wide=wide)     # wide: tiles of 256 x 512
     kernels.check_device_errors(x.device)
     bound = 1e-3 if out_dtype == torch.float32 else 1.5e-2
     assert torch.allclose(out.double(), expected, atol=bound * max(1.0, float(expected.abs().max())), rtol=bound)

@@ -154,9 +154,9 @@ def test_long_prompt_at_real_size(request, real_model, monkeypatch, cutting):
     calls = {"plain": 0, "gated": 0, "added": 0, "residual": 0, "qkv": 0}
     inner, inner_residual, inner_qkv = kernels.linear_pair, kernels.linear_pair_residual, kernels.linear_pair_qkv
 
-    def counted(x, weight, out, add=False, gated=False, row_stats=None):
+    def counted(x, weight, out, add=False, gated=False, row_stats=None, wide=None):
         calls["gated" if gated else "added" if add else "plain"] += 1
-        return inner(x, weight, out, add=add, gated=gated, row_stats=row_stats)
+        return inner(x, weight, out, add=add, gated=gated, row_stats=row_stats, wide=wide)
 
     def counted_residual(*args):
         calls["residual"] += 1
