@@ -64,7 +64,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   auto k_stage = [&](int s) { return smem + L::Q_BYTES + (size_t)s * 2 * L::TILE_BYTES; };
   auto v_stage = [&](int s) { return k_stage(s) + L::TILE_BYTES; };
   __shared__ uint64_t q_full, k_full[KV_STAGES], v_full[KV_STAGES], kv_empty[KV_STAGES];
-  __shared__ uint64_t s_full[2], p_full[2], pv_done;
+  // pv_done[j & 1]: the output is complete up to key tile j.  (A wait by parity only tells the completion that comes
+  // next from the one before it: whoever waits for tile j's must know that the same barrier's last but one, tile
+  // j - 2's, has happened.  The scores of tile j are multiplied behind the output of tile j - 2, so having seen them
+  // is enough for tiles j - 1 and j; at the end the outputs are waited for in their order.)
+  __shared__ uint64_t s_full[2], p_full[2], pv_done[2];
   __shared__ unsigned tmem_base_s;
   // [tile parity][half][row]: the two threads of a row agree on its maximum.  Shared memory is full to the
   // last kilobyte, so the maxima are exchanged as bfloat16, rounded up (any bound above the true maximum
@@ -107,7 +111,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], 2 * ROWS);
     }
-    mbar_init(&pv_done, 1);
+    mbar_init(&pv_done[0], 1);
+    mbar_init(&pv_done[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -199,7 +204,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             umma_bf16_a_tmem(tmem_base + o_column, tmem_base + s_column(b) + kk * 8, b_desc, idesc_pv,
                              (j | kk) != 0 ? 1u : 0u);
           }
-          umma_commit(&pv_done);
+          umma_commit(&pv_done[j & 1]);
           umma_commit(&kv_empty[stage]);
         }
       }
@@ -272,7 +277,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           if (grow) m_used = candidate;
           l *= factor;
           if (j > 0) {
-            ok = mbar_wait(&pv_done, (j - 1) & 1, error_flag, 19);     // the output must be complete up to tile j - 1
+            ok = mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) / 2) & 1, error_flag, 19);     // the output must be complete up to tile j - 1
             ok = __all_sync(0xffffffffu, ok);
             if (ok) {
               tmem_fence_after();
@@ -315,7 +320,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
           l += sum;
         }
       }
-      if (ok) ok = mbar_wait(&pv_done, (n_tiles - 1) & 1, error_flag, 20);
+      if (ok && n_tiles > 1) ok = mbar_wait(&pv_done[(n_tiles - 2) & 1], ((n_tiles - 2) / 2) & 1, error_flag, 20);
+      if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) / 2) & 1, error_flag, 20);
       ok = __all_sync(0xffffffffu, ok);
       ok = all_ok(ok);                                 // nobody reads the maxima any more
       float* half_sum_s = reinterpret_cast<float*>(&half_max_s[0][0][0]);      // [half][row]

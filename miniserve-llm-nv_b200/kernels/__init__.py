@@ -288,8 +288,10 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         group = n_q // n_kv
         if (USE_TCGEN05_ATTENTION and longest * group > 16
                 and lib.ms_attention_tcgen05_supports(_i(head_dim), _i(n_q), _i(n_kv), _i(k_pool.shape[2]))):
-            # prompt portions: the TMA + tcgen05 + tensor-memory kernel
-            _check(lib.ms_paged_attention_tcgen05(
+            # prompt portions: the TMA + tcgen05 + tensor-memory kernel, its softmax groups taking the key tiles in
+            # turn or working on each together
+            entry = lib.ms_paged_attention_turns if ATTENTION_IN_TURNS else lib.ms_paged_attention_tcgen05
+            _check(entry(
                 _ptr(q), _ptr(k_pool), _ptr(v_pool), _i(k_pool.shape[0]), _ptr(tables), _i(block_tables.shape[1]),
                 _ptr(starts), _ptr(lens), _i(k_pool.shape[2]), _i(n_q), _i(n_kv), _i(head_dim), _f(scale),
                 _i(window if window else 0), _ptr(out), _i(count), _i(longest), _i(n),
@@ -570,6 +572,9 @@ def pair_preferred(device: torch.device, m: int, n: int, gated: bool = False) ->
 # group size dividing 128, pages of 8..128 tokens); MINISERVE_B200_TCGEN05_ATTENTION=0 keeps them on the
 # mma.sync kernel.
 USE_TCGEN05_ATTENTION = __import__("os").environ.get("MINISERVE_B200_TCGEN05_ATTENTION", "1") == "1"
+# ... in the form in which two groups of softmax threads take the key tiles in turn, one thread per query row, with
+# three score buffers; MINISERVE_B200_ATTENTION_IN_TURNS=0: all softmax threads on every tile, two per row.
+ATTENTION_IN_TURNS = __import__("os").environ.get("MINISERVE_B200_ATTENTION_IN_TURNS", "1") == "1"
 
 _error_flags: dict = {}
 

@@ -382,18 +382,20 @@ def test_decode_attention_with_norm_rotation_and_append_inside(kernels, lengths,
         assert torch.allclose(out[n - 1, 0].float(), v_pool[dominated[0], 0, dominated[1]].float(), atol=3e-2)
 
 
-@pytest.mark.parametrize("tcgen05", [True, False])
+@pytest.mark.parametrize("tcgen05", ["in turn", "together", False])
 @pytest.mark.parametrize("window", [None, 100])
 @pytest.mark.parametrize("d,n_q,n_kv,page_size", [(64, 8, 2, 16), (128, 4, 2, 64), (128, 16, 8, 16)])
 @pytest.mark.parametrize("query_len", [64, 300])
 def test_prompt_attention_finds_single_keys(kernels, monkeypatch, query_len, d, n_q, n_kv, page_size, window, tcgen05):
-    """Prompt portions (the tcgen05 kernel, and the four-warp mma.sync kernel in its place): one key is made to
+    """Prompt portions (the tcgen05 kernel, its softmax groups taking the key tiles in turn or working on each together,
+    and the four-warp mma.sync kernel in its place): one key is made to
     dominate one query row, and the output of that row must be that key's value row when the key is visible
     and must not be when the causal mask or the window hides it.  Keys at the places where an index can be
     off by one: key 0, both sides of a 128-key tile edge, a page's last slot, the diagonal, one past the
     diagonal, and both sides of the window's far edge; for the first and the last row of a portion that
     starts in the middle of a page."""
-    monkeypatch.setattr(kernels, "USE_TCGEN05_ATTENTION", tcgen05)
+    monkeypatch.setattr(kernels, "USE_TCGEN05_ATTENTION", bool(tcgen05))
+    monkeypatch.setattr(kernels, "ATTENTION_IN_TURNS", tcgen05 == "in turn")
     dtype, length = torch.bfloat16, 707
     case = _attention_case(dtype, n_q, n_kv, d, page_size, [length, 90], [query_len, 17], 33)
     q, k_pool, v_pool, tables, request_of_token, positions, query_start, context_lens, max_q, max_ctx = case
