@@ -260,11 +260,15 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int i = 0; i < BN; ++i) part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
         } else {
+          // key key0 + i is visible to this row if first <= i <= last (causal: last = pos - key0; a window cuts
+          // below): one subtraction and one unsigned comparison per score
+          const int last = pos - key0;
+          const int first = window > 0 ? max(0, pos - window + 1 - key0) : 0;
+          const int below = last >= first ? -first : -(1 << 20);           // (nothing visible: no i passes)
+          const unsigned span = last >= first ? (unsigned)(last - first) : 0u;
 #pragma unroll
           for (int i = 0; i < BN; ++i) {
-            const int key = key0 + i;
-            const bool visible = key <= pos && (window <= 0 || key > pos - window);
-            if (!visible) v[i] = -INFINITY;
+            if ((unsigned)(i + below) > span) v[i] = -INFINITY;
             part_max[i & 7] = fmaxf(part_max[i & 7], v[i]);
           }
         }
