@@ -656,8 +656,10 @@ def qkv_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor
     """Whether a q/k/v projection of ``rows`` rows can norm, rotate and append its heads as it stores them
     (:func:`linear_pair_qkv`): bfloat16, so many rows that it goes to :func:`linear_pair`, heads of 128, and no
     rotation or the half-split one over the whole head."""
+    if rows < 256 or not QKV_IN_PRODUCT or dtype != torch.bfloat16:
+        return False
     n, k = weight.shape
-    return (QKV_IN_PRODUCT and dtype == torch.bfloat16 and head_dim == 128 and k % 8 == 0
+    return (head_dim == 128 and k % 8 == 0
             and (cos_sin is None or (rotary_dim == head_dim and not interleaved))
             and pair_preferred(weight.device, rows, n) and _pair_or_library("qkv", rows, weight, n_q, n_kv) == "pair")
 
@@ -1027,8 +1029,10 @@ def add_in_product_supported(rows: int, dtype: torch.dtype, weight: torch.Tensor
     its tiles to TMA as additions.  The norm that follows then reads the residual stream and writes its output,
     and no longer reads a separate output, adds it and writes the stream back (at Qwen3-1.7B sizes and 2,048 rows:
     25 MB instead of 50 MB a norm)."""
+    if rows < 256 or not ADD_IN_PRODUCT or dtype != torch.bfloat16:      # (what decides for steps of few rows, first)
+        return False
     n, k = weight.shape
-    return (ADD_IN_PRODUCT and dtype == torch.bfloat16 and rows > SKINNY_MAX_ROWS and n % 4 == 0 and k % 8 == 0
+    return (n % 4 == 0 and k % 8 == 0
             and pair_preferred(weight.device, rows, n) and _pair_or_library("add", rows, weight) != "library")
 
 
