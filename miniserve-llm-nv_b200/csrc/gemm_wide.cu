@@ -2,7 +2,7 @@
 // a block owns groups of up to 128 rows of W for the whole of K.
 //
 //   - the grid is one block per multiprocessor where the weight allows it (16 to 128 rows a block); a block
-//     has eight computing warps and one that copies: one thread of it issues TMA loads (cp.async.bulk.tensor,
+//     has sixteen computing warps and one that copies: one thread of it issues TMA loads (cp.async.bulk.tensor,
 //     128-byte swizzle) of the block's rows into a ring of shared-memory slots, each slot several pieces of
 //     64 k (one copy per slot through a three-dimensional map where K is a multiple of 64, else one per
 //     piece).  As many slots as the ring holds are requested BEFORE the kernel waits for its predecessor on
@@ -14,8 +14,14 @@
 //   - the computing warps split a piece by k: each reads 16 x 16 parts of W for all of the block's rows and
 //     one 16 x 8 part of X with ldmatrix and multiplies them with mma.sync.m16n8k16 (rows of W on the M
 //     side, tokens on the N side), float32 accumulation, one independent chain per 16 rows; four warps take
-//     the even pieces of a slot and four the odd ones; every warp waits for every slot and frees it.  The
-//     eight partial sums meet in shared memory at the end.  The number of 16-row tiles per block is a
+//     the even pieces of a slot and four the odd ones.  Two such teams of eight warps take the ring's slots in
+//     turn, each waiting for and freeing its own: what a warp does for a slot is a short chain of waits (the
+//     barrier, the loads, the products, the arrival: 0.32 to 0.38 us whatever the slot holds), and with one team
+//     that chain was all a multiprocessor could take in, 43 to 50 GB/s, however early the slots had arrived; two
+//     chains side by side made a decode step of the 1.7B sizes 3 % faster.  The ring has an even number of slots
+//     where slots are used again, so that a slot always comes back to the same team (a wait by the parity of a
+//     barrier's phase tells only neighbouring phases apart).  The sixteen partial sums meet in shared memory at
+//     the end.  The number of 16-row tiles per block is a
 //     template parameter of that loop: as a variable it leaves every tile's loads and products in the code
 //     as branches, and a block with one tile, which has the most pieces to walk, pays for eight;
 //   - plain mode stores the 16 x 8 results.  Gated mode expects the weight of a gated feed-forward with its
@@ -95,17 +101,18 @@ struct Consumer {
   uint64_t *full_bar, *empty_bar, *x_full, *x_empty;
   int stages, slot_bytes;
   unsigned ring_u32, x_u32, a_offset, b_offset;
-  int warp, lane, half;            // half: the even or the odd pieces of a slot
+  int warp, lane, half, team;      // half: the even or the odd pieces of a slot; team: the even or the odd slots of the ring
   int* error_flag;
   float* row_scale;                // [X_ROWS] in shared memory: what a token's sums are multiplied by (folded norm)
   float* tile_squares;             // [MAX_TILES][X_ROWS] in shared memory: residual mode's sums of squares per tile
 };
 
 // The computing warps' side for blocks of TILES tiles of 16 rows.  For each of the block's groups of rows: the
-// parts of K in turn (X for a part waits in its buffer), the part's slots from the ring, then the eight warps'
-// partial sums meet in `scratch` and the warp that owns a tile (warp < TILES) stores it.  Every computing warp
-// waits for every slot and frees it, whether it has a piece in it or not, so all of them see every phase of a
-// slot's barriers.  The number of tiles is a template parameter: with it as a variable every tile's loads and
+// parts of K in turn (X for a part waits in its buffer), the part's slots from the ring, then all warps'
+// partial sums meet in `scratch` and the warp that owns a tile (warp < TILES) stores it.  A warp waits for and
+// frees the slots of its team (every other slot of a group of rows, counted from the group's start, so that the
+// k a team sums do not depend on what else the block walks), whether it has a piece in them or not, and only
+// counts past the others.  The number of tiles is a template parameter: with it as a variable every tile's loads and
 // products stay in the code as branches, and a block of one tile, which has the most pieces to walk, pays for
 // eight.
 template <int TILES, int MODE, typename OutT, bool MANY>
@@ -145,6 +152,7 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
   const int my_groups = MANY ? walk.my_groups : 1, x_parts = MANY ? plan.x_parts : 1;   // (compile-time ones shorten the code)
   for (int gi = 0; gi < my_groups; ++gi) {
     const int group = (int)blockIdx.x + gi * (int)gridDim.x;
+    int walked = 0;                                 // slots of this group so far: which team sums which k must not depend on the block's other groups
     float acc[TILES][4];
 #pragma unroll
     for (int t = 0; t < TILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
@@ -158,23 +166,25 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
       }
       const unsigned x_part = c.x_u32 + (unsigned)(buf * plan.x_pieces * (X_ROWS * 128)) + c.b_offset;
       const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
-      for (int slot = 0; slot < slots; ++slot) {
-        ok = mbar_wait(&c.full_bar[stage], parity, c.error_flag, 3);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
-        const unsigned w_slot = c.ring_u32 + (unsigned)(stage * c.slot_bytes) + c.a_offset;
-        const unsigned x_slot = x_part + (unsigned)(piece0 * (X_ROWS * 128));
-        for (int j = c.half; j < pieces; j += 2) {
-          unsigned a[TILES][4], b[2];
-          ldmatrix_x2(b, x_slot + j * (X_ROWS * 128));
+      for (int slot = 0; slot < slots; ++slot, ++walked) {
+        if ((walked & 1) == c.team) {               // the other team has the slots in between
+          ok = mbar_wait(&c.full_bar[stage], parity, c.error_flag, 3);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
+          const unsigned w_slot = c.ring_u32 + (unsigned)(stage * c.slot_bytes) + c.a_offset;
+          const unsigned x_slot = x_part + (unsigned)(piece0 * (X_ROWS * 128));
+          for (int j = c.half; j < pieces; j += 2) {
+            unsigned a[TILES][4], b[2];
+            ldmatrix_x2(b, x_slot + j * (X_ROWS * 128));
 #pragma unroll
-          for (int t = 0; t < TILES; ++t) ldmatrix_x4(a[t], w_slot + j * piece_bytes + t * 2048);   // sixteen rows further: the swizzle repeats
+            for (int t = 0; t < TILES; ++t) ldmatrix_x4(a[t], w_slot + j * piece_bytes + t * 2048);   // sixteen rows further: the swizzle repeats
 #pragma unroll
-          for (int t = 0; t < TILES; ++t) mma_16816(acc[t], a[t], b);
+            for (int t = 0; t < TILES; ++t) mma_16816(acc[t], a[t], b);
+          }
+          __syncwarp();
+          if (c.lane == 0) mbar_arrive(&c.empty_bar[stage]);
         }
-        __syncwarp();
-        if (c.lane == 0) mbar_arrive(&c.empty_bar[stage]);
         if (++stage == c.stages) {
           stage = 0;
           parity ^= 1u;
@@ -268,7 +278,7 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
 // MANY: a block may walk several groups of rows, and K in parts; without it (one group per block, X whole in
 // shared memory: the products of a small model's layers) those loops are gone at compile time.
 template <int MODE, typename OutT, bool MANY>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 1)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  OutT* __restrict__ out, int M, int N, int K, const __grid_constant__ Plan plan,
                  const __grid_constant__ Fold fold, int* __restrict__ error_flag) {
@@ -292,7 +302,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], COMPUTE_WARPS);
+      mbar_init(&empty_bar[s], COMPUTE_WARPS / 2);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&x_full[i], 1);
@@ -403,7 +413,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   c.x_u32 = smem_u32(x_s);
   c.warp = warp;
   c.lane = lane;
-  c.half = warp >> 2;
+  c.half = (warp >> 2) & 1;
+  c.team = warp >> 3;
   const int kk = warp & 3;                         // which 16 of a piece's 64 k
   c.a_offset = swizzled((lane & 7) + ((lane >> 3) & 1) * 8, 2 * kk + (lane >> 4));
   c.b_offset = swizzled(lane & 7, 2 * kk + ((lane >> 3) & 1));
@@ -481,6 +492,10 @@ static bool plan_for(int N, int K, int budget, bool persistent, Plan* plan) {
   long long stages = (budget - 1024 - x_bytes - scratch) / slot;
   if (stages > MAX_STAGES) stages = MAX_STAGES;
   if (stages > total_slots) stages = total_slots;
+  // A slot that is used again must come back to the same team of warps: a team waits for its slots by the parity of
+  // their barrier's phase, and that tells only neighbouring phases apart.  With an even number of slots in the
+  // ring the even ones are always the first team's.
+  if (stages < total_slots && stages % 2 != 0) stages -= 1;
   if (stages < 2 && stages < total_slots) return false;
   long long ring = stages * slot;
   if (scratch == 0 && ring < partial) ring = partial;

@@ -13,7 +13,7 @@ namespace wide {
 
 using namespace ms::t5;
 
-constexpr int BK = 64, MAX_TILES = 8, X_ROWS = 8, COMPUTE_WARPS = 8, THREADS = 32 * (COMPUTE_WARPS + 1);
+constexpr int BK = 64, MAX_TILES = 8, X_ROWS = 8, COMPUTE_WARPS = 16, THREADS = 32 * (COMPUTE_WARPS + 1);
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], unsigned address) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
