@@ -530,6 +530,26 @@ def test_linear_wide_gated(kernels, m, n, k):
     assert torch.allclose(out.double(), expected, atol=1.5e-2 * max(1.0, float(expected.abs().max())), rtol=1.5e-2)
 
 
+def test_linear_wide_ring_slots_return_to_the_same_team(kernels):
+    """A weight whose blocks take eight tiles has room for five 32 KB slots in its ring and sixteen slots to walk: the
+    ring keeps an even number of them, so that a slot always comes back to the team of warps that had it (a team
+    waits by the parity of the barrier's phase, which cannot tell the phase after next from this one).  Many runs,
+    all with the same bits, against float64."""
+    m, n, k = 8, 40960, 2048
+    x, w = rand((m, k), torch.bfloat16, 76, 0.5), rand((n, k), torch.bfloat16, 77, 0.1)
+    expected = x.double() @ w.double().T
+    first = None
+    for _ in range(20):
+        out = torch.full((m, n), 7.0, dtype=torch.float32).cuda()
+        kernels.linear_wide(x, w, out)
+        kernels.check_device_errors(x.device)
+        if first is None:
+            first = out
+            assert torch.allclose(out.double(), expected, atol=2e-3 * max(1.0, float(expected.abs().max())), rtol=2e-3)
+        else:
+            assert torch.equal(out, first)
+
+
 @pytest.mark.parametrize("m,n,k", [(8, 24576, 4096), (5, 40000, 264)])
 def test_linear_wide_blocks_that_walk_many_groups(kernels, monkeypatch, m, n, k):
     """With the switch on, a weight of more rows than one wave of blocks takes is walked by one block per
