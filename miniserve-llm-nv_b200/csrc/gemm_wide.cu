@@ -18,9 +18,10 @@
 //     turn, each waiting for and freeing its own: what a warp does for a slot is a short chain of waits (the
 //     barrier, the loads, the products, the arrival: 0.32 to 0.38 us whatever the slot holds), and with one team
 //     that chain was all a multiprocessor could take in, 43 to 50 GB/s, however early the slots had arrived; two
-//     chains side by side made a decode step of the 1.7B sizes 3 % faster.  The ring has an even number of slots
-//     where slots are used again, so that a slot always comes back to the same team (a wait by the parity of a
-//     barrier's phase tells only neighbouring phases apart).  The sixteen partial sums meet in shared memory at
+//     chains side by side made a decode step of the 1.7B sizes 3 % faster.  A slot that is used again always comes
+//     back to the same team (a wait by the parity of a barrier's phase tells only neighbouring phases apart): the
+//     teams take the slots by their count where the ring has an even number of them, by their place in the ring
+//     where it is odd.  The sixteen partial sums meet in shared memory at
 //     the end.  The number of 16-row tiles per block is a
 //     template parameter of that loop: as a variable it leaves every tile's loads and products in the code
 //     as branches, and a block with one tile, which has the most pieces to walk, pays for eight;
@@ -78,6 +79,7 @@ struct Plan {
   int groups, grid;                // groups of `tiles` 16-row tiles; blocks (each takes every grid-th group)
   int x_pieces, x_parts, x_bufs;   // 64-k pieces of X held at once, how many such parts K has, buffers for them
   int scratch_bytes;               // room of its own for the partial sums (0: they meet in the ring)
+  int odd_ring;                    // slots are used again and their number is odd: see the teams in compute()
   int slots_per_group, part_slots; // ring slots that a group of rows takes in all, and in one full part of K
 };
 
@@ -167,7 +169,7 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
       const unsigned x_part = c.x_u32 + (unsigned)(buf * plan.x_pieces * (X_ROWS * 128)) + c.b_offset;
       const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
       for (int slot = 0; slot < slots; ++slot, ++walked) {
-        if ((walked & 1) == c.team) {               // the other team has the slots in between
+        if (((plan.odd_ring ? stage : walked) & 1) == c.team) {   // the other team has the slots in between
           ok = mbar_wait(&c.full_bar[stage], parity, c.error_flag, 3);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -494,8 +496,10 @@ static bool plan_for(int N, int K, int budget, bool persistent, Plan* plan) {
   if (stages > total_slots) stages = total_slots;
   // A slot that is used again must come back to the same team of warps: a team waits for its slots by the parity of
   // their barrier's phase, and that tells only neighbouring phases apart.  With an even number of slots in the
-  // ring the even ones are always the first team's.
-  if (stages < total_slots && stages % 2 != 0) stages -= 1;
+  // ring the even ones are always the first team's; with an odd number the teams take the slots by their place in
+  // the ring instead of by their count (three of five and two of five, say: uneven, but a ring-ful of 32B q/k/v
+  // weights one slot shorter cost more, 1.6 % of a decode step).
+  const bool odd_ring = stages < total_slots && stages % 2 != 0;
   if (stages < 2 && stages < total_slots) return false;
   long long ring = stages * slot;
   if (scratch == 0 && ring < partial) ring = partial;
@@ -512,6 +516,7 @@ static bool plan_for(int N, int K, int budget, bool persistent, Plan* plan) {
   plan->x_parts = (int)x_parts;
   plan->x_bufs = (int)x_bufs;
   plan->scratch_bytes = (int)scratch;
+  plan->odd_ring = odd_ring ? 1 : 0;
   plan->slots_per_group = (int)slots_per_group;
   plan->part_slots = (int)((x_pieces + pieces - 1) / pieces);
   return true;

@@ -531,10 +531,10 @@ def test_linear_wide_gated(kernels, m, n, k):
 
 
 def test_linear_wide_ring_slots_return_to_the_same_team(kernels):
-    """A weight whose blocks take eight tiles has room for five 32 KB slots in its ring and sixteen slots to walk: the
-    ring keeps an even number of them, so that a slot always comes back to the team of warps that had it (a team
-    waits by the parity of the barrier's phase, which cannot tell the phase after next from this one).  Many runs,
-    all with the same bits, against float64."""
+    """A weight whose blocks take eight tiles has room for five 32 KB slots in its ring and sixteen slots to walk: a
+    slot must always come back to the team of warps that had it (a team waits by the parity of the barrier's phase,
+    which cannot tell the phase after next from this one), so with an odd ring the teams take the slots by their
+    place in it.  Many runs, all with the same bits, against float64."""
     m, n, k = 8, 40960, 2048
     x, w = rand((m, k), torch.bfloat16, 76, 0.5), rand((n, k), torch.bfloat16, 77, 0.1)
     expected = x.double() @ w.double().T
