@@ -55,6 +55,16 @@ namespace ms {
 namespace wide {
 
 constexpr int MAX_STAGES = 16;
+
+// The bounded wait in two parts: the first try where it is used, the spinning and the error flag in one place out
+// of line.  These kernels run for a few microseconds, and instructions that are seldom needed still have to be
+// fetched past.
+__device__ __noinline__ bool wait_longer(uint64_t* bar, unsigned parity, int* error_flag, int code) {
+  return mbar_wait(bar, parity, error_flag, code);
+}
+__device__ __forceinline__ bool wait_for(uint64_t* bar, unsigned parity, int* error_flag, int code) {
+  return mbar_try_wait(bar, parity) ? true : wait_longer(bar, parity, error_flag, code);
+}
 constexpr int SMEM_LIMIT = 226 * 1024;       // dynamic shared memory a block may ask for
 constexpr int SLOT_TARGET = 16 * 1024;       // a slot is about this large (and two pieces at least)
 constexpr int X_WHOLE_LIMIT = 96 * 1024;     // activations up to this size stay in shared memory whole
@@ -162,7 +172,7 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
       const bool fresh_x = x_parts > 1 || gi == 0;    // X whole in shared memory is fetched once
       const int buf = x_parts > 1 ? x_seen % plan.x_bufs : 0;
       if (fresh_x) {
-        ok = mbar_wait(&c.x_full[buf], (unsigned)(x_seen / plan.x_bufs) & 1u, c.error_flag, 2);
+        ok = wait_for(&c.x_full[buf], (unsigned)(x_seen / plan.x_bufs) & 1u, c.error_flag, 2);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
       }
@@ -170,7 +180,7 @@ __device__ __forceinline__ void compute(const Consumer& c, const Plan& plan, con
       const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
       for (int slot = 0; slot < slots; ++slot, ++walked) {
         if (((plan.odd_ring ? stage : walked) & 1) == c.team) {   // the other team has the slots in between
-          ok = mbar_wait(&c.full_bar[stage], parity, c.error_flag, 3);
+          ok = wait_for(&c.full_bar[stage], parity, c.error_flag, 3);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
@@ -338,7 +348,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           waited = true;
         }
         const int buf = x_sent % plan.x_bufs;
-        if (x_sent >= plan.x_bufs && !mbar_wait(&x_empty[buf], ((unsigned)(x_sent / plan.x_bufs) & 1u) ^ 1u, error_flag, 1)) {
+        if (x_sent >= plan.x_bufs && !wait_for(&x_empty[buf], ((unsigned)(x_sent / plan.x_bufs) & 1u) ^ 1u, error_flag, 1)) {
           ok = false;
           return;
         }
@@ -361,7 +371,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (fresh_x && (gi > 0 || part > 0)) send_x(part);
           const int part_pieces = walk.part_pieces(plan, part), slots = walk.part_slots(plan, part);
           for (int slot = 0; slot < slots && ok; ++slot, ++g) {
-            if (g >= stages && !(ok = mbar_wait(&empty_bar[stage], parity ^ 1u, error_flag, 1))) break;
+            if (g >= stages && !(ok = wait_for(&empty_bar[stage], parity ^ 1u, error_flag, 1))) break;
             const int piece0 = slot * plan.pieces, pieces = min(plan.pieces, part_pieces - piece0);
             unsigned char* dst = ring + (size_t)stage * slot_bytes;
             if (plan.bulk) {                       // one copy; pieces past the end arrive as zeros and count
@@ -382,9 +392,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       if (!waited) grid_dependency_wait();
       if (!ok || *reinterpret_cast<volatile int*>(error_flag) != 0) {
         // something gave up: let the copies still in flight land before the block may exit
-        for (int j = g - 1; j >= 0 && j >= g - stages; --j) mbar_wait(&full_bar[j % stages], (j / stages) & 1, error_flag, 4);
+        for (int j = g - 1; j >= 0 && j >= g - stages; --j) wait_for(&full_bar[j % stages], (j / stages) & 1, error_flag, 4);
         for (int j = x_sent - 1; j >= 0 && j >= x_sent - plan.x_bufs; --j)
-          mbar_wait(&x_full[j % plan.x_bufs], (unsigned)(j / plan.x_bufs) & 1u, error_flag, 4);
+          wait_for(&x_full[j % plan.x_bufs], (unsigned)(j / plan.x_bufs) & 1u, error_flag, 4);
       }
     }
     // The other lanes of this warp do nothing, and must not wait for the predecessor here: a warp that
