@@ -361,7 +361,7 @@ int launch(const void* qkv, const int* slots, const void* q_weight, const void* 
   if (e != cudaSuccess) MS_FAIL("attention_decode: launch failed: %s", cudaGetErrorString(e));
   if (num_splits > 1) {
     const int items = n_requests * n_q;
-    ms::launch(attention_combine_kernel<D>, items, 128, 0, stream, part_o, part_lse, (__nv_bfloat16*)out, num_splits, items);
+    launch_attention_combine<D>(part_o, part_lse, (__nv_bfloat16*)out, num_splits, items, stream);
     MS_CHECK_LAUNCH("attention_combine");
   }
   return 0;

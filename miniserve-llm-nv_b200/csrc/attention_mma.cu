@@ -378,8 +378,7 @@ int launch_attention_mma(const void* q, const void* k_pool, const void* v_pool, 
   MS_CHECK_LAUNCH("attention_mma");
   if (num_splits > 1) {
     const int items = n_tokens * n_q;
-    ms::launch(attention_combine_kernel<D>, items, 128, 0, stream, part_o, part_lse, (__nv_bfloat16*)out,
-                                                                     num_splits, items);
+    launch_attention_combine<D>(part_o, part_lse, (__nv_bfloat16*)out, num_splits, items, stream);
     MS_CHECK_LAUNCH("attention_combine");
   }
   return 0;
