@@ -16,15 +16,15 @@
 //     side, tokens on the N side), float32 accumulation, one independent chain per 16 rows; four warps take
 //     the even pieces of a slot and four the odd ones.  Two such teams of eight warps take the ring's slots in
 //     turn, each waiting for and freeing its own: what a warp does for a slot is a short chain of waits (the
-//     barrier, the loads, the products, the arrival: 0.32 to 0.38 us whatever the slot holds), and with one team
-//     that chain was all a multiprocessor could take in, 43 to 50 GB/s, however early the slots had arrived; two
-//     chains side by side made a decode step of the 1.7B sizes 3 % faster.  A slot that is used again always comes
-//     back to the same team (a wait by the parity of a barrier's phase tells only neighbouring phases apart): the
-//     teams take the slots by their count where the ring has an even number of them, by their place in the ring
-//     where it is odd.  The sixteen partial sums meet in shared memory at
-//     the end.  The number of 16-row tiles per block is a
-//     template parameter of that loop: as a variable it leaves every tile's loads and products in the code
-//     as branches, and a block with one tile, which has the most pieces to walk, pays for eight;
+//     barrier, the loads, the products, the arrival: 0.32 to 0.38 us whatever the slot holds), and with one
+//     team that chain was all a multiprocessor could take in, 43 to 50 GB/s, however early the slots had
+//     arrived; two chains side by side made a decode step of the 1.7B sizes 3 % faster.  A slot that is used
+//     again always comes back to the same team (a wait by the parity of a barrier's phase tells only
+//     neighbouring phases apart): the teams take the slots by their count where the ring has an even number
+//     of them, by their place in the ring where it is odd.  The sixteen partial sums meet in shared memory at
+//     the end.  The number of 16-row tiles per block is a template parameter of that loop: as a variable it
+//     leaves every tile's loads and products in the code as branches, and a block with one tile, which has
+//     the most pieces to walk, pays for eight;
 //   - plain mode stores the 16 x 8 results.  Gated mode expects the weight of a gated feed-forward with its
 //     rows in blocks of sixteen, eight of the gate projection followed by the same eight of the up
 //     projection, and stores silu(gate) * up for the eight features: the activation costs no kernel and no
