@@ -70,11 +70,14 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   auto v_stage = [&](int s) { return smem + L::Q_BYTES + (size_t)(K_STAGES + s) * L::TILE_BYTES; };
   __shared__ uint64_t q_full, k_full[K_STAGES], k_empty[K_STAGES], v_full[V_STAGES], v_empty[V_STAGES];
   __shared__ uint64_t s_full[S_BUFFERS], p_full[S_BUFFERS];
-  // pv_done[j & 1]: the output is complete up to key tile j.  (A wait by parity only tells the completion that comes
-  // next from the one before it: whoever waits for tile j's must know that tile j - 2's has happened.  The scores of
-  // tile j are multiplied behind the output of tile j - 3, and the outputs complete in their order: having seen a
-  // tile's scores is enough to wait for the outputs of the two tiles before it.)
-  __shared__ uint64_t pv_done[2];
+  // pv_done[j & 1]: the output is complete up to key tile j.  A wait by parity only tells the completion that comes
+  // next from the one before it: whoever waits for tile j's must know that tile j - 2's has happened AND that tile
+  // j + 2's cannot have (a waiter that comes too late sees the parity it waits for flipped back, and waits for good).
+  // Only the softmax groups' wait for tile j - 1's output at tile j is of that kind (they have seen tile j's scores,
+  // which came behind tile j - 3's output, and tile j + 1 needs their own maxima first).  The score buffers are
+  // handed back through s_free[buffer], which like every ring here cannot run ahead of its waiter; the end of all
+  // outputs has a barrier of its own, all_done.
+  __shared__ uint64_t pv_done[2], s_free[S_BUFFERS], all_done;
   __shared__ uint64_t m_ready[2];              // the rows' maxima after an even / an odd tile are in place
   __shared__ float m_shared[ROWS];
   __shared__ float sums[2][ROWS];              // the two groups' sums, at the end
@@ -118,12 +121,14 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int b = 0; b < S_BUFFERS; ++b) {
       mbar_init(&s_full[b], 1);
       mbar_init(&p_full[b], ROWS);
+      mbar_init(&s_free[b], 1);
     }
 #pragma unroll
     for (int b = 0; b < 2; ++b) {
       mbar_init(&pv_done[b], 1);
       mbar_init(&m_ready[b], ROWS);
     }
+    mbar_init(&all_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -193,7 +198,7 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       bool ok = mbar_wait(&q_full, 0, error_flag, 12);
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int stage = j % K_STAGES, b = j % S_BUFFERS;
-        if (j >= S_BUFFERS) ok = mbar_wait(&pv_done[(j - S_BUFFERS) & 1], ((j - S_BUFFERS) / 2) & 1, error_flag, 13);
+        if (j >= S_BUFFERS) ok = mbar_wait(&s_free[b], (unsigned)(j / S_BUFFERS - 1) & 1u, error_flag, 13);
         ok = ok && mbar_wait(&k_full[stage], (j / K_STAGES) & 1, error_flag, 14);
         if (!ok) break;
         tmem_fence_after();
@@ -224,7 +229,9 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int kk = 0; kk < BN / 16; ++kk)      // sixteen keys further: 16 rows of 128 bytes in V, 8 columns of packed P
           umma_bf16_a_tmem(tmem_base + o_column, p + kk * 8, values + kk * (16 * 128 / 16), idesc_pv, (j | kk) != 0 ? 1u : 0u);
         umma_commit(&pv_done[j & 1]);
+        umma_commit(&s_free[b]);              // (P of this tile is consumed: its buffer may take the scores of tile j + 3)
         umma_commit(&v_empty[stage]);
+        if (j == n_tiles - 1) umma_commit(&all_done);
       }
     }
   } else {
@@ -343,14 +350,8 @@ attention_turns_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                      : "=r"(result) : "r"((unsigned)mine) : "memory");
         return result != 0;
       };
-      // the outputs in their order: this group's last but one tile (the scores of its last tile came behind the output
-      // three tiles before, and with that the one four before, which is what makes this wait by parity safe), its
-      // last tile, then the last of all
-      const int last_mine = n_tiles - 1 - ((n_tiles - 1 - turn) & 1);
-      if (ok && last_mine >= 2) ok = mbar_wait(&pv_done[last_mine & 1], ((last_mine - 2) / 2) & 1, error_flag, 22);
-      if (ok && last_mine >= 0 && last_mine != n_tiles - 1)
-        ok = mbar_wait(&pv_done[last_mine & 1], (last_mine / 2) & 1, error_flag, 20);
-      if (ok) ok = mbar_wait(&pv_done[(n_tiles - 1) & 1], ((n_tiles - 1) / 2) & 1, error_flag, 20);
+      // every output is complete (a barrier that completes once: nothing to tell apart)
+      if (ok) ok = mbar_wait(&all_done, 0u, error_flag, 20);
       ok = __all_sync(0xffffffffu, ok);
       ok = all_ok(ok);                  // every maximum is final
       const float m_final = m_shared[local_row];
